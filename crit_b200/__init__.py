@@ -1,0 +1,388 @@
+"""crit_b200: the paged KV-cache hot path of crit, hand-written for B200 (sm_100a).
+
+This module is the kernel-module boundary: the object crit's KVPool and DeviceAttention take as `kernels=`
+(reference: kernels/techniques/attention/paged-kv-attention/torch-ext/paged_kv_attention/__init__.py, loaded by
+crit_plugins.kernels.load_kernel("paged-kv-attention")).  It keeps that module's names, argument meanings and errors
+for write / attend / prefill / partitions / piece_size / tile_for / workspace_floats / owner / release, and reaches
+the CUDA kernels through the C ABI of include/crit_b200.h (ctypes, as the reference binds its own CUDA tile).  There
+is no Triton, no torch fallback and no CPU path: without the native library, or on a tensor that is not on a CUDA
+device, every entry point raises.
+
+Page kinds: the reference's "bf16", "fp16", "fp8", "fp8:row", "int8", and "fp8:page": E4M3 codes with one FP32 scale
+per (page, kv head), scales [pages][kv_heads] (scale = amax / 448 over the page's rows of that head).
+
+A row's positions are read in contiguous splits of `chunk` positions (one per cache geometry, chunk_for()); the splits'
+states are folded in split order.  This is the reference's "flash" split shape (contiguous splits, __init__.py:580-612)
+rather than its interleaved pieces; attention outputs agree with the reference's within its own kernel-vs-torch
+tolerance, integer and byte results (slots, codes, scales) bit for bit.
+"""
+import contextlib
+import ctypes
+import math
+import threading
+
+import torch
+
+from . import _lib
+
+__all__ = ["KINDS", "MAX_COLUMNS", "attend", "chunk_for", "gather", "merge_shards", "owner", "partitions", "parts_for",
+           "piece_size", "prefill", "release", "slots_at", "tile_for", "workspace_floats", "write"]
+
+KINDS = {"bf16": 0, "fp16": 0, "fp8": 1, "fp8:row": 2, "int8": 3, "fp8:page": 4}
+MAX_COLUMNS = 64            # columns of one row a launch reads
+TILE = 16                   # positions a warp reads per step: chunks and pages are multiples of it
+DEFAULT_CHUNK = 1024
+
+_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16, torch.float32: _lib.DTYPE_FP32}
+_PAGE_DTYPES = {"bf16": _lib.DTYPE_BF16, "fp16": _lib.DTYPE_FP16}
+
+
+def _check_kind(kind, key_scales):
+    if kind not in KINDS:
+        raise ValueError(f"page kinds are {', '.join(KINDS)}, not {kind!r}")
+    if (KINDS[kind] >= 2) != (key_scales is not None):
+        raise ValueError(f"{kind} pages {'take' if KINDS[kind] >= 2 else 'have no'} scales beside their codes")
+    return KINDS[kind]
+
+
+def _cuda(tensor, what):
+    if not tensor.is_cuda:
+        raise RuntimeError(f"crit_b200 runs on CUDA devices only: {what} is on {tensor.device} (there is no CPU path)")
+    return tensor
+
+
+def _ptr(tensor):
+    return ctypes.c_void_p(tensor.data_ptr()) if tensor is not None else None
+
+
+def _stream(device):
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _page_dtype(kind, pages):
+    if KINDS[kind] != 0:
+        return _lib.DTYPE_BF16
+    if pages.dtype not in _DTYPES:
+        raise ValueError(f"{kind} pages are 16-bit tensors, not {pages.dtype}")
+    return _DTYPES[pages.dtype]
+
+
+# -- workspaces -----------------------------------------------------------------------------------------------------------
+# One per (device, owner): a launch writes its partials and the merge reads them back, so two engines of one process
+# never share one (reference: paged_kv_attention/__init__.py:129-171).  A workspace a launch outgrew is kept: a CUDA
+# graph captured over it replays into it.
+_workspaces, _retired = {}, []
+_owner = threading.local()
+
+
+@contextlib.contextmanager
+def owner(key):
+    """Launches inside this block take a workspace of their own, apart from every other owner's."""
+    before = getattr(_owner, "key", None)
+    _owner.key = key
+    try:
+        yield
+    finally:
+        _owner.key = before
+
+
+def release(key):
+    """Drop an owner's workspaces (its captured graphs must be gone: they replay into them)."""
+    for at in [at for at in _workspaces if at[1] == key]:
+        del _workspaces[at]
+    _retired[:] = [(k, found) for k, found in _retired if k != key]
+
+
+def _workspace(device, floats, given):
+    if given is not None:
+        if given.dtype != torch.float32 or given.numel() < floats or not given.is_contiguous():
+            raise ValueError(f"attend's workspace holds {given.numel()} floats; this launch needs {floats} "
+                             "(workspace_floats)")
+        return given
+    at = (str(device), getattr(_owner, "key", None))
+    found = _workspaces.get(at)
+    if found is None or found.numel() < floats:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("crit_b200.attend: run a launch of this size once before capturing it (its partials' "
+                               "workspace is allocated outside the capture)")
+        if found is not None:
+            _retired.append((at[1], found))
+        found = _workspaces[at] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+    return found
+
+
+# -- geometry rules -----------------------------------------------------------------------------------------------------
+def chunk_for(head_dim, value_dim, heads, kv_heads, page, kind="bf16"):
+    """Positions per split of every launch over a cache of this geometry (a multiple of 16): fixed per cache, never by
+    the batch, so a column's bits are the same alone and in any window."""
+    return DEFAULT_CHUNK
+
+
+def parts_for(positions, chunk):
+    """Splits a partial row takes over page tables holding `positions` positions a row."""
+    return max(1, -(-int(positions) // int(chunk)))
+
+
+def partitions(device, kv_heads, kind, head_dim=None, value_dim=None):
+    """The most splits a partial row takes in a launch whose caller sizes the workspace by a count per cache
+    (reference: paged_kv_attention/__init__.py:260-273).  attend(partitions=P) never makes more than P splits: it
+    raises the chunk where a row's tables hold more than P * chunk positions."""
+    return 64
+
+
+def piece_size(head_dim, value_dim, kind="bf16", kv_heads=None):
+    """Positions a warp reads per step (reference: __init__.py:276-286; here the tile is 16 for every geometry)."""
+    return TILE
+
+
+def tile_for(columns, group, capability, fused=False):
+    """(rows, warps, stages) of a launch's query tile: 16 query rows (columns x the group's heads), 32 where they pass
+    16 and the heads are up to 128 wide; four warps, each with its own ring of stages (reference: __init__.py:335-356)."""
+    return (32 if columns * group > 16 else 16), 4, 4
+
+
+def workspace_floats(tokens, heads, partitions, value_dim):
+    """FP32 floats of the partials a launch needs for `tokens` partial rows (reference: __init__.py:359-362)."""
+    return tokens * heads * partitions * (value_dim + 2)
+
+
+# -- KV append ----------------------------------------------------------------------------------------------------------
+def write(keys, values, slots, key_pages, value_pages, kind, key_scales=None, value_scales=None,
+          multipliers=(1.0, 1.0)):
+    """A step's keys [tokens][kv_heads][dim] and values [tokens][kv_heads][value_dim] (bf16, fp16 or fp32) into their
+    slots ([tokens] int64; a slot below 0 is skipped) of one layer's pages (any view whose storage is
+    [slots][kv_heads][dim]), encoded for the page kind, in one launch.  values and value_pages None: keys only; keys
+    and key_pages None: values only, at the value multiplier.  "fp8:page" takes scales [pages][kv_heads] and the page
+    size from the pages' shape ([pages][page][kv_heads][dim]).  Reference: paged_kv_attention/__init__.py:289-324."""
+    if keys is None:
+        if values is None:
+            raise ValueError("write takes keys, values or both")
+        return write(values, None, slots, value_pages, None, kind, value_scales, None,
+                     multipliers=(multipliers[1], multipliers[1]))
+    k_kind = _check_kind(kind, key_scales)
+    _cuda(keys, "keys")
+    T, hkv, d = keys.shape
+    if T == 0:
+        return
+    if keys.dtype not in _DTYPES or (values is not None and values.dtype != keys.dtype):
+        raise ValueError("keys and values are bf16, fp16 or fp32 tensors of one dtype")
+    if keys.stride(-1) != 1:
+        keys = keys.contiguous()
+    if values is not None and values.stride(-1) != 1:
+        values = values.contiguous()
+    if slots.dtype != torch.int64 or not slots.is_contiguous() or slots.numel() != T:
+        raise ValueError(f"slots are contiguous int64 [{T}]")
+    if not key_pages.is_contiguous() or (value_pages is not None and not value_pages.is_contiguous()):
+        raise ValueError("pages are contiguous [slots][kv_heads][dim] storage")
+    page = 1
+    if k_kind == 4:
+        if key_pages.dim() != 4:
+            raise ValueError("fp8:page pages are given as [pages][page][kv_heads][dim]")
+        page = key_pages.shape[1]
+    p = _lib.AppendParams()
+    p.keys, p.values, p.slots = _ptr(keys), _ptr(values), _ptr(slots)
+    p.key_pages, p.value_pages = _ptr(key_pages), _ptr(value_pages)
+    p.key_scales, p.value_scales = _ptr(key_scales), _ptr(value_scales)
+    p.tokens = T
+    p.key_stride_token, p.key_stride_head = keys.stride(0), keys.stride(1)
+    if values is not None:
+        p.value_stride_token, p.value_stride_head = values.stride(0), values.stride(1)
+    p.kv_heads, p.head_dim, p.page = hkv, d, page
+    p.value_dim = values.shape[-1] if values is not None else d
+    p.kind, p.in_dtype, p.page_dtype = k_kind, _DTYPES[keys.dtype], _page_dtype(kind, key_pages)
+    p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])
+    with torch.cuda.device(keys.device):
+        _lib.check(_lib.load().crit_b200_append(ctypes.byref(p), _stream(keys.device)), "crit_b200.write")
+
+
+# -- gather and slots ---------------------------------------------------------------------------------------------------
+def gather(pages, kind, page, *, table=None, slots=None, count=None, scales=None, multiplier=1.0, dtype=torch.bfloat16):
+    """Rows of one page tensor ([pages][page][kv_heads][dim] or [slots][kv_heads][dim]) dequantised to `dtype`: the
+    first `count` positions of the page table `table` (int32), or the rows at `slots` (int64, any shape).
+    -> [count][kv_heads][dim] (or slots' shape + [kv_heads][dim]).  Reference: pages.py:455-493."""
+    _cuda(pages, "pages")
+    k_kind = _check_kind(kind, scales)
+    hkv, dim = pages.shape[-2], pages.shape[-1]
+    shape = None
+    if slots is not None:
+        shape, slots = tuple(slots.shape), slots.reshape(-1).contiguous()
+        count = slots.numel()
+    elif table is None or count is None:
+        raise ValueError("gather reads a page table's first `count` positions, or rows at `slots`")
+    out = torch.empty((count, hkv, dim), dtype=dtype, device=pages.device)
+    if count == 0:
+        return out if shape is None else out.view(*shape, hkv, dim)
+    p = _lib.GatherParams()
+    p.pages, p.scales, p.out = _ptr(pages), _ptr(scales), _ptr(out)
+    p.table = _ptr(table.contiguous()) if table is not None else None
+    p.slots = _ptr(slots)
+    p.count, p.kv_heads, p.dim, p.page = count, hkv, dim, int(page)
+    p.kind, p.page_dtype, p.out_dtype = k_kind, _page_dtype(kind, pages), _DTYPES[dtype]
+    p.multiplier = float(multiplier)
+    with torch.cuda.device(pages.device):
+        _lib.check(_lib.load().crit_b200_gather(ctypes.byref(p), _stream(pages.device)), "crit_b200.gather")
+    return out if shape is None else out.view(*shape, hkv, dim)
+
+
+def slots_at(tables, rows, positions, page, dump, capacity=None, out=None):
+    """Each position's slot through its table row, on the device: tables [S][width] int32, rows and positions int64 of
+    one shape; with capacity [S] int64 a position outside [0, capacity[row]) gets the dump page's first slot.
+    Reference: pages.py:653-660."""
+    _cuda(tables, "tables")
+    shape = tuple(positions.shape)
+    rows, positions = rows.reshape(-1).contiguous(), positions.reshape(-1).contiguous()
+    if rows.dtype != torch.int64 or positions.dtype != torch.int64 or tables.dtype != torch.int32:
+        raise ValueError("tables are int32, rows and positions int64")
+    out = torch.empty(positions.numel(), dtype=torch.int64, device=tables.device) if out is None else out
+    p = _lib.SlotsParams()
+    p.tables, p.rows, p.positions, p.capacity, p.slots = _ptr(tables), _ptr(rows), _ptr(positions), _ptr(capacity), _ptr(out)
+    p.n, p.table_stride, p.table_width = positions.numel(), tables.stride(0), tables.shape[1]
+    p.page, p.dump = int(page), int(dump)
+    with torch.cuda.device(tables.device):
+        _lib.check(_lib.load().crit_b200_slots(ctypes.byref(p), _stream(tables.device)), "crit_b200.slots_at")
+    return out.view(shape)
+
+
+# -- decode and verify windows ------------------------------------------------------------------------------------------
+def _refuse(**given):
+    asked = [name for name, value in given.items()
+             if value is not None and value is not False and not (isinstance(value, int) and value == 0)]
+    if asked:
+        raise NotImplementedError(f"crit_b200.attend does not serve {', '.join(asked)} yet: causal windows over the "
+                                  "whole context only")
+
+
+def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, columns, page, *, counts=None,
+           offsets=None, tokens=None, key_scales=None, value_scales=None, multipliers=(1.0, 1.0), scale=None,
+           partitions=None, parents=None, blocks=None, block_size=None, out=None, lse=None, workspace=None, piece=None,
+           fused=False, fresh=None, vsplit=None, tile=None, num_warps=None, num_stages=None, maxnreg=None,
+           flash=False, chunk=None, ramp=None, sinks=None, sliding=0, derive=None, launch="both"):
+    """Decode and verify windows over paged KV (reference: paged_kv_attention/__init__.py:396-445, same arguments).
+
+    q [tokens][heads][dim] bf16 or fp16 (fp16 for "fp16" pages); key_pages / value_pages one layer's pages
+    ([pages][page][kv_heads][dim]), key_scales / value_scales their scales; tables [S][width] int32; rows [R] int32 the
+    table row of each batch row; starts [R] int32 its first token in q; firsts [R] int64 its column 0's position;
+    counts [R] int32 its columns (None: `columns` each; more read as `columns`); columns the widest row (<= 64).
+    offsets [R] int32 and tokens: each row's first partial row and the partial rows the launch takes.  Writes
+    out [tokens][heads][value_dim] (q's dtype) at the rows' tokens and lse [tokens][heads] FP32 when given; returns out.
+    chunk: positions per split (default chunk_for()); partitions: the most splits a partial row may take (the
+    workspace's, see partitions()).  piece, fused, vsplit, tile, num_warps, num_stages, maxnreg, flash and ramp are
+    accepted and change nothing (one launch shape per geometry).  parents, blocks, fresh, sinks, sliding and derive
+    are not served.  launch: "both", or "decode" / "merge" alone (a measurement's)."""
+    _refuse(parents=parents, blocks=blocks, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
+    k_kind = _check_kind(kind, key_scales)
+    _cuda(q, "q")
+    T, hq, d = q.shape
+    hkv, dv = key_pages.shape[-2], value_pages.shape[-1]
+    R = int(starts.shape[0])
+    if hq % hkv or not 1 <= columns <= MAX_COLUMNS or R == 0:
+        raise ValueError("query heads a multiple of the KV heads, 1..64 columns a row, one row or more")
+    if q.stride(-1) != 1:
+        raise ValueError("q's last dimension is contiguous")
+    if q.dtype not in (torch.bfloat16, torch.float16):
+        raise ValueError("q is bf16 or fp16")
+    if (offsets is None) != (tokens is None):
+        raise ValueError("offsets come with the partial rows they take (tokens)")
+    if tables.dtype != torch.int32 or tables.stride(-1) != 1 or rows.dtype != torch.int32 or \
+            starts.dtype != torch.int32 or firsts.dtype != torch.int64:
+        raise ValueError("tables, rows and starts are int32, firsts int64")
+    page = int(page)
+    if page % TILE:
+        raise ValueError(f"crit_b200 reads pages of a multiple of {TILE} positions, not {page}")
+    device = q.device
+    positions = tables.shape[1] * page
+    chunk = int(chunk or chunk_for(d, dv, hq, hkv, page, kind))
+    if partitions:
+        chunk = max(chunk, -(-positions // int(partitions)))
+    chunk = -(-chunk // TILE) * TILE
+    splits = parts_for(positions, chunk)
+    partial_rows = R * columns if offsets is None else int(tokens)
+    out = torch.empty(T, hq, dv, dtype=q.dtype, device=device) if out is None else out
+    if out.dtype != q.dtype or out.stride(-1) != 1:
+        raise ValueError("out is in q's dtype, its last dimension contiguous")
+    p = _lib.AttendParams()
+    if splits > 1:
+        floats = workspace_floats(partial_rows, hq, splits, dv)
+        space = _workspace(device, floats, workspace)
+        p.workspace, p.workspace_floats = _ptr(space), space.numel()
+    p.q, p.out, p.lse = _ptr(q), _ptr(out), _ptr(lse)
+    if lse is not None and (lse.dtype != torch.float32 or not lse.is_contiguous() or tuple(lse.shape) != (T, hq)):
+        raise ValueError(f"lse is contiguous FP32 [{T}][{hq}]")
+    p.key_pages, p.value_pages = _ptr(key_pages), _ptr(value_pages)
+    p.key_scales, p.value_scales = _ptr(key_scales), _ptr(value_scales)
+    p.tables, p.rows, p.starts, p.counts = _ptr(tables), _ptr(rows), _ptr(starts), _ptr(counts)
+    p.firsts, p.offsets = _ptr(firsts), _ptr(offsets)
+    p.q_stride_token, p.q_stride_head = q.stride(0), q.stride(1)
+    p.out_stride_token, p.out_stride_head = out.stride(0), out.stride(1)
+    p.table_stride = tables.stride(0)
+    p.n_rows, p.columns, p.partial_rows = R, int(columns), partial_rows
+    p.q_heads, p.kv_heads, p.head_dim, p.value_dim, p.page = hq, hkv, d, dv, page
+    p.kind, p.page_dtype, p.q_dtype = k_kind, _page_dtype(kind, key_pages), _DTYPES[q.dtype]
+    p.chunk, p.max_splits = chunk, splits
+    p.scale = float(scale if scale is not None else d ** -0.5)
+    p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])
+    lib = _lib.load()
+    call = {"both": lib.crit_b200_attend, "decode": lib.crit_b200_decode, "merge": lib.crit_b200_merge}[launch]
+    with torch.cuda.device(device):
+        _lib.check(call(ctypes.byref(p), _stream(device)), "crit_b200.attend")
+    return out
+
+
+def merge_shards(outs, lses, dtype=None):
+    """Partials of the same queries over disjoint keys (outs [parts][tokens][heads][dim], lses [parts][tokens][heads]
+    FP32, -inf for a part with no key) -> (out [tokens][heads][dim], lse): the parts weighted by exp(lse - max); a
+    token no part saw gets zeros and -inf.  Reference: inference/partitioned-attention/plugin.py:52-64."""
+    if not torch.is_tensor(outs):
+        outs = torch.stack(list(outs))
+    if not torch.is_tensor(lses):
+        lses = torch.stack(list(lses))
+    _cuda(outs, "outs")
+    outs, lses = outs.contiguous(), lses.float().contiguous()
+    if outs.dtype not in _DTYPES:
+        outs = outs.float()
+    parts, dim = outs.shape[0], outs.shape[-1]
+    n = lses[0].numel()
+    dtype = dtype or torch.float32
+    out = torch.empty(outs.shape[1:], dtype=dtype, device=outs.device)
+    lse = torch.empty(lses.shape[1:], dtype=torch.float32, device=outs.device)
+    p = _lib.MergeShardsParams()
+    p.outs, p.lses, p.out, p.lse = _ptr(outs), _ptr(lses), _ptr(out), _ptr(lse)
+    p.n, p.parts, p.dim, p.in_dtype, p.out_dtype = n, parts, dim, _DTYPES[outs.dtype], _DTYPES[dtype]
+    with torch.cuda.device(outs.device):
+        _lib.check(_lib.load().crit_b200_merge_shards(ctypes.byref(p), _stream(outs.device)), "crit_b200.merge_shards")
+    return out, lse
+
+
+# -- prompt chunks ------------------------------------------------------------------------------------------------------
+def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scales=None, value_scales=None,
+            multipliers=(1.0, 1.0), scale=None, out=None, lse=None, int8_qk=False, fresh=None, flash=False,
+            sinks=None, sliding=0, splits=None, workspace=None, derive=None):
+    """A prompt chunk of one sequence: q [T][heads][dim] at positions position.. (their keys and values written),
+    table [pages] int32 -> out [T][heads][dim] in q's dtype (and lse [T][heads] FP32 when given), causal.  position: an
+    int, or a one-element int64 device tensor read on the device.  Reference: paged_kv_attention/__init__.py:1245-1332."""
+    _refuse(int8_qk=int8_qk, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
+    k_kind = _check_kind(kind, key_scales)
+    _cuda(q, "q")
+    T, hq, d = q.shape
+    hkv = key_pages.shape[-2]
+    if value_pages.shape[-1] != d:
+        raise ValueError("prompt chunks read keys and values of one width")
+    out = torch.empty_like(q) if out is None else out
+    p = _lib.PrefillParams()
+    p.q, p.out, p.lse = _ptr(q), _ptr(out), _ptr(lse)
+    p.key_pages, p.value_pages = _ptr(key_pages), _ptr(value_pages)
+    p.key_scales, p.value_scales = _ptr(key_scales), _ptr(value_scales)
+    p.table = _ptr(table)
+    if torch.is_tensor(position):
+        p.position_ptr = _ptr(position)
+    else:
+        p.position = int(position)
+    p.q_stride_token, p.q_stride_head = q.stride(0), q.stride(1)
+    p.out_stride_token, p.out_stride_head = out.stride(0), out.stride(1)
+    p.tokens, p.q_heads, p.kv_heads, p.head_dim, p.value_dim, p.page = T, hq, hkv, d, d, int(page)
+    p.kind, p.page_dtype, p.q_dtype = k_kind, _page_dtype(kind, key_pages), _DTYPES[q.dtype]
+    p.scale = float(scale if scale is not None else d ** -0.5)
+    p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])
+    with torch.cuda.device(q.device):
+        _lib.check(_lib.load().crit_b200_prefill(ctypes.byref(p), _stream(q.device)), "crit_b200.prefill")
+    return out

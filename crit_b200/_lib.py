@@ -1,0 +1,117 @@
+"""ctypes binding of libcrit_b200.so (include/crit_b200.h).  There is no fallback: without the library every call
+raises."""
+import ctypes
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
+from pathlib import Path
+
+LIBRARY = Path(__file__).resolve().parent / "_native" / "libcrit_b200.so"
+ABI_VERSION = 1
+
+KIND_16BIT, KIND_FP8, KIND_FP8_ROW, KIND_INT8, KIND_FP8_PAGE = range(5)
+DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = range(3)
+
+
+class AppendParams(Structure):
+    _fields_ = [("keys", c_void_p), ("values", c_void_p), ("slots", c_void_p), ("key_pages", c_void_p),
+                ("value_pages", c_void_p), ("key_scales", c_void_p), ("value_scales", c_void_p),
+                ("tokens", c_int64), ("key_stride_token", c_int64), ("key_stride_head", c_int64),
+                ("value_stride_token", c_int64), ("value_stride_head", c_int64),
+                ("kv_heads", c_int32), ("head_dim", c_int32), ("value_dim", c_int32), ("page", c_int32),
+                ("kind", c_int32), ("in_dtype", c_int32), ("page_dtype", c_int32),
+                ("key_multiplier", c_float), ("value_multiplier", c_float)]
+
+
+class GatherParams(Structure):
+    _fields_ = [("pages", c_void_p), ("scales", c_void_p), ("table", c_void_p), ("slots", c_void_p), ("out", c_void_p),
+                ("count", c_int64), ("kv_heads", c_int32), ("dim", c_int32), ("page", c_int32),
+                ("kind", c_int32), ("page_dtype", c_int32), ("out_dtype", c_int32), ("multiplier", c_float)]
+
+
+class SlotsParams(Structure):
+    _fields_ = [("tables", c_void_p), ("rows", c_void_p), ("positions", c_void_p), ("capacity", c_void_p),
+                ("slots", c_void_p), ("n", c_int64), ("table_stride", c_int64),
+                ("table_width", c_int32), ("page", c_int32), ("dump", c_int32)]
+
+
+class AttendParams(Structure):
+    _fields_ = [("q", c_void_p), ("out", c_void_p), ("lse", c_void_p), ("key_pages", c_void_p),
+                ("value_pages", c_void_p), ("key_scales", c_void_p), ("value_scales", c_void_p),
+                ("tables", c_void_p), ("rows", c_void_p), ("starts", c_void_p), ("counts", c_void_p),
+                ("firsts", c_void_p), ("offsets", c_void_p), ("workspace", c_void_p),
+                ("workspace_floats", c_int64), ("q_stride_token", c_int64), ("q_stride_head", c_int64),
+                ("out_stride_token", c_int64), ("out_stride_head", c_int64), ("table_stride", c_int64),
+                ("n_rows", c_int32), ("columns", c_int32), ("partial_rows", c_int32),
+                ("q_heads", c_int32), ("kv_heads", c_int32), ("head_dim", c_int32), ("value_dim", c_int32),
+                ("page", c_int32), ("kind", c_int32), ("page_dtype", c_int32), ("q_dtype", c_int32),
+                ("chunk", c_int32), ("max_splits", c_int32),
+                ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float)]
+
+
+class MergeShardsParams(Structure):
+    _fields_ = [("outs", c_void_p), ("lses", c_void_p), ("out", c_void_p), ("lse", c_void_p), ("n", c_int64),
+                ("parts", c_int32), ("dim", c_int32), ("in_dtype", c_int32), ("out_dtype", c_int32)]
+
+
+class PrefillParams(Structure):
+    _fields_ = [("q", c_void_p), ("out", c_void_p), ("lse", c_void_p), ("key_pages", c_void_p),
+                ("value_pages", c_void_p), ("key_scales", c_void_p), ("value_scales", c_void_p),
+                ("table", c_void_p), ("position_ptr", c_void_p), ("position", c_int64),
+                ("q_stride_token", c_int64), ("q_stride_head", c_int64), ("out_stride_token", c_int64),
+                ("out_stride_head", c_int64), ("tokens", c_int32), ("q_heads", c_int32), ("kv_heads", c_int32),
+                ("head_dim", c_int32), ("value_dim", c_int32), ("page", c_int32), ("kind", c_int32),
+                ("page_dtype", c_int32), ("q_dtype", c_int32),
+                ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float)]
+
+
+STRUCTS = (AppendParams, GatherParams, SlotsParams, AttendParams, MergeShardsParams, PrefillParams)
+
+# name -> (restype, argtypes): every symbol include/crit_b200.h declares
+SYMBOLS = {
+    "crit_b200_append": (c_int, [POINTER(AppendParams), c_void_p]),
+    "crit_b200_gather": (c_int, [POINTER(GatherParams), c_void_p]),
+    "crit_b200_slots": (c_int, [POINTER(SlotsParams), c_void_p]),
+    "crit_b200_attend_plan": (c_int, [c_int32] * 8 + [POINTER(c_int32)]),
+    "crit_b200_decode": (c_int, [POINTER(AttendParams), c_void_p]),
+    "crit_b200_merge": (c_int, [POINTER(AttendParams), c_void_p]),
+    "crit_b200_attend": (c_int, [POINTER(AttendParams), c_void_p]),
+    "crit_b200_merge_shards": (c_int, [POINTER(MergeShardsParams), c_void_p]),
+    "crit_b200_prefill": (c_int, [POINTER(PrefillParams), c_void_p]),
+    "crit_b200_abi_version": (c_int, []),
+    "crit_b200_params_size": (c_int, [c_int32]),
+    "crit_b200_error": (c_char_p, [c_int32]),
+    "crit_b200_device_sms": (c_int, []),
+}
+
+_lib = None
+
+
+def load():
+    """The library, loaded once; raises when it is not built or its ABI is not this binding's."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIBRARY.exists():
+        raise RuntimeError(f"crit_b200's native library is not built ({LIBRARY}): run `python -m crit_b200.build` "
+                           "(nvcc for sm_100a); there is no CPU or torch fallback")
+    lib = ctypes.CDLL(str(LIBRARY))
+    for name, (restype, argtypes) in SYMBOLS.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = restype, argtypes
+    if lib.crit_b200_abi_version() != ABI_VERSION:
+        raise RuntimeError(f"libcrit_b200.so speaks ABI {lib.crit_b200_abi_version()}, this binding {ABI_VERSION}: rebuild")
+    for which, struct in enumerate(STRUCTS):
+        if lib.crit_b200_params_size(which) != ctypes.sizeof(struct):
+            raise RuntimeError(f"{struct.__name__} is {ctypes.sizeof(struct)} bytes here and "
+                               f"{lib.crit_b200_params_size(which)} in libcrit_b200.so: rebuild")
+    _lib = lib
+    return lib
+
+
+def check(code, what):
+    """0 passes; a negative code is a ValueError (the parameters), a positive one a RuntimeError (CUDA)."""
+    if code == 0:
+        return
+    text = load().crit_b200_error(code).decode()
+    if code < 0:
+        raise ValueError(f"{what}: {text}")
+    raise RuntimeError(f"{what}: CUDA error {code}: {text}")

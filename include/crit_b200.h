@@ -1,0 +1,194 @@
+/* crit_b200: C ABI of the B200-native paged KV-cache hot path (KV append into pages, block-table gather, split-K
+ * decode / speculative-verify attention with its log-sum-exp merge, chunked prefill).
+ *
+ * Conventions (they mirror the reference's one native boundary on this path, crit's CUDA flash tile:
+ * kernels/techniques/attention/paged-kv-attention/torch-ext/paged_kv_attention/cuda_window.cu:1482-1535, bound by
+ * ctypes in paged_kv_attention/__init__.py:807-883):
+ *   - plain pointers and sizes, parameter blocks are POD structs passed by address and copied by the call;
+ *   - every pointer is DEVICE memory of the thread's current device unless its comment says "host";
+ *   - the caller owns every buffer; a call allocates nothing and never waits for the host;
+ *   - work is queued on `stream` (a cudaStream_t as void*; NULL is the legacy default stream) and may be captured
+ *     in a CUDA graph;
+ *   - the return value is 0 on success, a cudaError_t (> 0) when the runtime refused a launch, or a negative
+ *     CRIT_B200_E* code when the parameters describe something the kernels do not serve; crit_b200_error() names it.
+ */
+#ifndef CRIT_B200_H
+#define CRIT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CRIT_B200_ABI_VERSION 1
+
+/* Page kinds (the reference's KINDS, paged_kv_attention/__init__.py:78, plus the per-page FP8 scale). */
+#define CRIT_B200_KIND_16BIT    0   /* bf16 or fp16 pages (page_dtype says which) */
+#define CRIT_B200_KIND_FP8      1   /* E4M3 codes, one multiplier per layer for keys and one for values */
+#define CRIT_B200_KIND_FP8_ROW  2   /* E4M3 codes, FP32 scale per (slot, kv head): scales [slots][kv_heads] */
+#define CRIT_B200_KIND_INT8     3   /* INT8 codes, FP32 scale per (slot, kv head) */
+#define CRIT_B200_KIND_FP8_PAGE 4   /* E4M3 codes, FP32 scale per (page, kv head): scales [pages][kv_heads] */
+
+#define CRIT_B200_DTYPE_BF16 0
+#define CRIT_B200_DTYPE_FP16 1
+#define CRIT_B200_DTYPE_FP32 2
+
+#define CRIT_B200_EINVAL      (-1)  /* a size, stride or pointer the call cannot take */
+#define CRIT_B200_EUNSUPPORTED (-2) /* a geometry no kernel was built for (head widths, page size, page kind) */
+#define CRIT_B200_EWORKSPACE  (-3)  /* the workspace is smaller than crit_b200_attend_plan said */
+#define CRIT_B200_EALIGN      (-4)  /* a pointer or stride is not aligned as the kernels read it */
+
+/* -- KV append ---------------------------------------------------------------------------------------------------
+ * Replaces paged_kv_attention.write (paged_kv_attention/__init__.py:289-324, kernel _kernels.py:112-150) and the torch
+ * path of KVPool.write (inference/attention-state/code/pages.py:420-453 with fp8_rows/int8_rows :872-895).
+ * keys [tokens][kv_heads][head_dim] and values [tokens][kv_heads][value_dim] (strides in elements, last dimension
+ * contiguous) go to slots[t] of pages laid out [slots][kv_heads][dim]; a slot below 0 is skipped.  values NULL: keys
+ * only.  Codes and scales are bit-exact with the reference's rules. */
+typedef struct crit_b200_append_params {
+    const void* keys;
+    const void* values;
+    const int64_t* slots;
+    void* key_pages;
+    void* value_pages;
+    float* key_scales;           /* kinds 2, 3: [slots][kv_heads]; kind 4: [pages][kv_heads]; else NULL */
+    float* value_scales;
+    int64_t tokens;
+    int64_t key_stride_token, key_stride_head, value_stride_token, value_stride_head;
+    int32_t kv_heads, head_dim, value_dim, page;
+    int32_t kind, in_dtype, page_dtype;
+    float key_multiplier, value_multiplier;     /* kind 1: codes = x / multiplier */
+} crit_b200_append_params;
+
+int crit_b200_append(const crit_b200_append_params* params, void* stream);
+
+/* -- block-table page gather -------------------------------------------------------------------------------------
+ * Replaces KVPool.gather / rows_at (pages.py:455-493): rows of one page tensor, dequantised (code * scale in FP32,
+ * then rounded to out_dtype), read through a page table (slots NULL: positions 0..count-1 of `table`) or at explicit
+ * slots (table NULL).  out [count][kv_heads][dim] contiguous. */
+typedef struct crit_b200_gather_params {
+    const void* pages;
+    const float* scales;
+    const int32_t* table;
+    const int64_t* slots;
+    void* out;
+    int64_t count;
+    int32_t kv_heads, dim, page;
+    int32_t kind, page_dtype, out_dtype;
+    float multiplier;
+} crit_b200_gather_params;
+
+int crit_b200_gather(const crit_b200_gather_params* params, void* stream);
+
+/* -- slot mapping on the device ----------------------------------------------------------------------------------
+ * Replaces KVPool._slots_at (pages.py:653-660) and the per-token host arithmetic of KVPool.reserve (:347, :721-722):
+ * slot = tables[row[i]][clamp(p / page)] * page + p % page; with `capacity` (one per table row) a position outside
+ * [0, capacity[row]) gets dump * page. */
+typedef struct crit_b200_slots_params {
+    const int32_t* tables;
+    const int64_t* rows;         /* [n] table row of each position */
+    const int64_t* positions;    /* [n] */
+    const int64_t* capacity;     /* [table rows] or NULL */
+    int64_t* slots;              /* [n] out */
+    int64_t n, table_stride;
+    int32_t table_width, page, dump;
+} crit_b200_slots_params;
+
+int crit_b200_slots(const crit_b200_slots_params* params, void* stream);
+
+/* -- split-K decode / speculative-verify attention ------------------------------------------------------------------
+ * Replaces paged_kv_attention.attend (paged_kv_attention/__init__.py:396-576; kernels _kernels.py:263-478 and :558-604,
+ * cuda_window.cu:284-1286) behind DeviceAttention._windows (inference/attention-state/code/device_attention.py:659-704).
+ * R window rows; row r is counts[r] (NULL: `columns`; more than `columns` reads as `columns`) tokens starts[r].. of q
+ * over the page table tables[rows[r]]; column c sits at position firsts[r] + c and sees positions 0..firsts[r] + c.
+ * A row's positions are cut into contiguous splits of `chunk` positions; each split writes one partial state per
+ * (token, query head) into `workspace`, and crit_b200_merge folds a row's splits in split order.  A row that fits one
+ * split is written to out / lse by the first launch.  crit_b200_attend runs both launches. */
+typedef struct crit_b200_attend_params {
+    const void* q;               /* [tokens][q_heads][head_dim], bf16 or fp16 (q_dtype) */
+    void* out;                   /* [tokens][q_heads][value_dim], q_dtype */
+    float* lse;                  /* [tokens][q_heads] natural-log sum of exp of the scaled scores, or NULL */
+    const void* key_pages;       /* [slots][kv_heads][head_dim] */
+    const void* value_pages;     /* [slots][kv_heads][value_dim] */
+    const float* key_scales;
+    const float* value_scales;
+    const int32_t* tables;       /* [S][table_stride] page ids */
+    const int32_t* rows;         /* [R] */
+    const int32_t* starts;       /* [R] */
+    const int32_t* counts;       /* [R] or NULL */
+    const int64_t* firsts;       /* [R] */
+    const int32_t* offsets;      /* [R] first partial row of each row, or NULL (r * columns) */
+    float* workspace;            /* crit_b200_attend_plan's floats, or NULL when max_splits is 1 */
+    int64_t workspace_floats;
+    int64_t q_stride_token, q_stride_head, out_stride_token, out_stride_head, table_stride;
+    int32_t n_rows, columns, partial_rows;
+    int32_t q_heads, kv_heads, head_dim, value_dim, page;
+    int32_t kind, page_dtype, q_dtype;
+    int32_t chunk;               /* positions per split: a multiple of 16 */
+    int32_t max_splits;          /* splits a partial row has room for: ceil(positions a row may reach / chunk) */
+    float scale, key_multiplier, value_multiplier;
+} crit_b200_attend_params;
+
+/* out[0] positions per split this library would choose (a multiple of 16), out[1] bytes of dynamic shared memory a
+ * block takes, out[2] query rows a block's tile holds, out[3] blocks resident per SM, out[4] SMs of the device.
+ * The partials of a launch take partial_rows * q_heads * max_splits * (value_dim + 2) floats, the reference's
+ * workspace_floats (paged_kv_attention/__init__.py:359-362).  Returns 0, or CRIT_B200_EUNSUPPORTED. */
+int crit_b200_attend_plan(int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t value_dim, int32_t page,
+                          int32_t kind, int32_t page_dtype, int32_t columns, int32_t* out5);
+
+int crit_b200_decode(const crit_b200_attend_params* params, void* stream);   /* the splits' partials */
+int crit_b200_merge(const crit_b200_attend_params* params, void* stream);    /* the fold in split order */
+int crit_b200_attend(const crit_b200_attend_params* params, void* stream);   /* both */
+
+/* -- merge of shards --------------------------------------------------------------------------------------------
+ * Replaces PartitionedAttention.merge (inference/partitioned-attention/plugin.py:52-64; host form merge_partials,
+ * code/implementation.py:119-138): parts partials of the same n (token, head) rows over disjoint keys,
+ * outs [parts][n][dim] (FP32, or the in_dtype), lses [parts][n] FP32 (-inf: a part that saw no key) ->
+ * out [n][dim] (out_dtype) and lse [n]; a row no part saw gets zeros and -inf. */
+typedef struct crit_b200_merge_shards_params {
+    const void* outs;
+    const float* lses;
+    void* out;
+    float* lse;
+    int64_t n;
+    int32_t parts, dim, in_dtype, out_dtype;
+} crit_b200_merge_shards_params;
+
+int crit_b200_merge_shards(const crit_b200_merge_shards_params* params, void* stream);
+
+/* -- chunked prefill ---------------------------------------------------------------------------------------------
+ * Replaces paged_kv_attention.prefill (paged_kv_attention/__init__.py:1245-1332; kernel _kernels.py:610-726) behind
+ * DeviceAttention._prefill_rows (device_attention.py:901-916): one sequence's chunk of `tokens` queries at positions
+ * position.. (position_ptr, a device int64, wins over position when not NULL) over its page table, causal; the
+ * chunk's keys and values are in the pages already. */
+typedef struct crit_b200_prefill_params {
+    const void* q;
+    void* out;
+    float* lse;                  /* or NULL */
+    const void* key_pages;
+    const void* value_pages;
+    const float* key_scales;
+    const float* value_scales;
+    const int32_t* table;        /* [pages of the sequence] */
+    const int64_t* position_ptr; /* or NULL */
+    int64_t position;
+    int64_t q_stride_token, q_stride_head, out_stride_token, out_stride_head;
+    int32_t tokens, q_heads, kv_heads, head_dim, value_dim, page;
+    int32_t kind, page_dtype, q_dtype;
+    float scale, key_multiplier, value_multiplier;
+} crit_b200_prefill_params;
+
+int crit_b200_prefill(const crit_b200_prefill_params* params, void* stream);
+
+/* -- housekeeping ------------------------------------------------------------------------------------------------ */
+int crit_b200_abi_version(void);
+/* sizeof of each parameter block, in the order append, gather, slots, attend, merge_shards, prefill: a binding checks
+ * its own struct layout against it (the reference's crit_cw_params_size, cuda_window.cu:1495-1497). */
+int crit_b200_params_size(int32_t which);
+const char* crit_b200_error(int32_t code);       /* host string; cudaGetErrorString for codes above 0 */
+int crit_b200_device_sms(void);                  /* SMs of the current device, or a negative error */
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,281 @@
+"""Parity of the CUDA kernels, called through the C ABI, against the CPU oracle and the golden fixtures: appends and
+slot maps bit for bit, attention within max-abs 2e-2 / mean-abs 2e-3 (bf16)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def pk():
+    import crit_b200
+    return crit_b200
+
+
+def _dev():
+    return torch.device("cuda")
+
+
+# -- KV append ----------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "fp8", "fp8:row", "int8"])
+@pytest.mark.parametrize("d,dv", [(128, 128), (64, 128), (256, 256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_writes_encode_as_the_oracle_does_and_skip_negative_slots(pk, kind, d, dv, dtype):
+    from helpers import STORE
+    g = torch.Generator().manual_seed(1)
+    keys, values = (torch.randn(40, 3, d, generator=g) * 3).to(dtype), torch.randn(40, 3, dv, generator=g).to(dtype)
+    keys[5] = 0.0
+    dev = _dev()
+    k = torch.zeros(64, 3, d, dtype=STORE[kind], device=dev)
+    v = torch.zeros(64, 3, dv, dtype=STORE[kind], device=dev)
+    ks = vs = None
+    if kind in ("fp8:row", "int8"):
+        ks, vs = torch.zeros(64, 3, device=dev), torch.zeros(64, 3, device=dev)
+    slots = torch.randperm(64, generator=g)[:40]
+    slots[7] = -1
+    mult = (0.05, 0.07)
+    pk.write(keys.to(dev), values.to(dev), slots.to(dev), k, v, kind, ks, vs, multipliers=mult)
+    keep = (slots >= 0).numpy()
+    at = slots.numpy()[keep]
+    for x, store, scales, m in ((keys, k, ks, mult[0]), (values, v, vs, mult[1])):
+        x = x.float().numpy()[keep]
+        if kind in ("bf16", "fp16"):
+            want = torch.from_numpy(x).to(STORE[kind])
+            assert torch.equal(store.cpu()[at], want)
+        else:
+            want, want_scale = oracle.quantize_rows(x, kind, m)
+            assert np.array_equal(store.view(torch.uint8).cpu().numpy()[at], want)
+            if want_scale is not None:
+                assert np.array_equal(scales.cpu().numpy()[at].view(np.uint32), want_scale.view(np.uint32))
+        untouched = np.ones(64, bool)
+        untouched[at] = False
+        assert not store.view(torch.uint8 if store.element_size() == 1 else torch.int16).cpu().numpy()[untouched].any()
+    if kind == "fp8:row":
+        assert ks.cpu()[slots[5]].tolist() == [float(np.float32(1e-30))] * 3
+
+
+def test_writes_match_the_references_golden_codes(pk, golden):
+    data = golden("quantize.npz")
+    x = torch.from_numpy(data["x"]).cuda()
+    n, h, d = x.shape
+    slots = torch.arange(n, device="cuda")
+    for kind, codes, scales in (("fp8:row", "fp8row_codes", "fp8row_scales"), ("int8", "int8_codes", "int8_scales"),
+                                ("fp8", "static_codes", None)):
+        store = torch.zeros(n, h, d, dtype=torch.uint8, device="cuda")
+        sc = torch.zeros(n, h, device="cuda") if scales else None
+        pages = store.view(torch.float8_e4m3fn) if kind != "int8" else store.view(torch.int8)
+        m = float(data["static_multiplier"])
+        pk.write(x, None, slots, pages, None, kind, sc, None, multipliers=(m, m))
+        assert np.array_equal(store.cpu().numpy(), data[codes].view(np.uint8)), kind
+        if scales:
+            assert np.array_equal(sc.cpu().numpy().view(np.uint32), data[scales].view(np.uint32)), kind
+
+
+def test_page_scaled_writes_follow_the_oracle_through_appends(pk):
+    page, hkv, d = 16, 2, 128
+    g = torch.Generator().manual_seed(4)
+    n_pages = 6
+    k = torch.zeros(n_pages, page, hkv, d, dtype=torch.float8_e4m3fn, device="cuda")
+    v = torch.zeros_like(k)
+    ks, vs = torch.zeros(n_pages, hkv, device="cuda"), torch.zeros(n_pages, hkv, device="cuda")
+    ok, ov = np.zeros((n_pages * page, hkv, d), np.uint8), np.zeros((n_pages * page, hkv, d), np.uint8)
+    oks, ovs = np.zeros((n_pages, hkv), np.float32), np.zeros((n_pages, hkv), np.float32)
+    table = [4, 1, 3, 0]
+    slot = lambda p: table[p // page] * page + p % page
+    at = 0
+    # a prompt of 37 tokens, then decode tokens of growing magnitude (the tail page's scale grows and re-encodes)
+    for count, mag in ((37, 1.0), (1, 0.5), (1, 3.0), (3, 9.0), (1, 1.0), (8, 30.0), (1, 0.1)):
+        keys = (torch.randn(count, hkv, d, generator=g) * mag).bfloat16()
+        values = (torch.randn(count, hkv, d, generator=g) * mag).bfloat16()
+        slots = torch.tensor([slot(p) for p in range(at, at + count)])
+        pk.write(keys.cuda(), values.cuda(), slots.cuda(), k, v, "fp8:page", ks, vs)
+        oracle.quantize_pages(keys.float().numpy(), slots.numpy(), page, ok, oks)
+        oracle.quantize_pages(values.float().numpy(), slots.numpy(), page, ov, ovs)
+        at += count
+        assert np.array_equal(k.view(torch.uint8).cpu().numpy().reshape(-1, hkv, d), ok), (count, mag)
+        assert np.array_equal(v.view(torch.uint8).cpu().numpy().reshape(-1, hkv, d), ov), (count, mag)
+        assert np.array_equal(ks.cpu().numpy().view(np.uint32), oks.view(np.uint32))
+        assert np.array_equal(vs.cpu().numpy().view(np.uint32), ovs.view(np.uint32))
+
+
+# -- gather, slots --------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["bf16", "fp8", "fp8:row", "int8", "fp8:page"])
+def test_gather_reads_pages_back_through_the_table(pk, kind):
+    from helpers import Cache
+    cache = Cache(kind, 2, 64, 64, 16, [70, 33])
+    k, v = cache.stored()
+    for s, n in enumerate(cache.lengths):
+        at = cache.slots(s, torch.arange(n)).cpu().numpy()
+        for pages, scales, want, mult in ((cache.k, cache.ks, k, cache.multipliers[0]),
+                                          (cache.v, cache.vs, v, cache.multipliers[1])):
+            got = pk.gather(pages, kind, 16, table=cache.tables[s], count=n, scales=scales, multiplier=mult,
+                            dtype=torch.float32)
+            assert np.array_equal(got.cpu().numpy(), want[at])
+            rounded = pk.gather(pages, kind, 16, table=cache.tables[s], count=n, scales=scales, multiplier=mult)
+            assert torch.equal(rounded.cpu(), torch.from_numpy(want[at]).bfloat16())
+            picked = pk.gather(pages, kind, 16, slots=torch.from_numpy(at[::3].copy()).cuda().view(-1, 1), scales=scales,
+                               multiplier=mult, dtype=torch.float32)
+            assert np.array_equal(picked.cpu().numpy()[:, 0], want[at[::3]])
+
+
+def test_round_slots_match_the_references(pk, golden):
+    data = golden("round_slots.npz")
+    got = pk.slots_at(torch.from_numpy(data["tables"]).cuda(), torch.from_numpy(data["slot"]).cuda(),
+                      torch.from_numpy(data["positions"]).cuda(), int(data["page"]), int(data["dump"]),
+                      capacity=torch.from_numpy(data["capacity"]).cuda())
+    assert np.array_equal(got.cpu().numpy(), data["slots"])
+
+
+# -- decode and verify windows --------------------------------------------------------------------------------------------
+SHAPES = [(8, 2, 128, 128), (24, 4, 256, 256), (56, 8, 128, 128), (12, 2, 64, 64), (40, 8, 128, 128)]
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "fp8", "fp8:row", "int8", "fp8:page"])
+@pytest.mark.parametrize("hq,hkv,d,dv", SHAPES)
+@pytest.mark.parametrize("page", [16, 48])
+def test_windows_match_the_oracle(pk, kind, hq, hkv, d, dv, page):
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, hkv, d, dv, page, [130, 64, 1, 517])
+    cols = 5
+    rows, starts, firsts, counts = [0, 1, 2, 3], [0, 5, 10, 15], [125, 59, 0, 400], [5, 5, 1, 3]
+    q = queries(20, hq, d, 3, torch.float16 if kind == "fp16" else torch.bfloat16)
+    lse = torch.full((20, hq), 7.0, device="cuda")
+    out = cache.attend(q, rows, starts, firsts, cols, counts=counts, lse=lse, chunk=128)
+    want, want_lse = cache.oracle(q, rows, starts, firsts, cols, counts=counts)
+    tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
+    assert_attention_close(out, lse, want, want_lse, tokens)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8:page"])
+@pytest.mark.parametrize("chunk", [16, 64, 1024])
+def test_splits_of_any_size_fold_to_the_same_attention(pk, kind, chunk):
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, 2, 128, 128, 16, [1000, 37, 16, 2049], outliers=True)
+    q = queries(4, 16, 128, 9)
+    rows, starts, firsts = [0, 1, 2, 3], [0, 1, 2, 3], [999, 36, 15, 2048]
+    lse = torch.empty(4, 16, device="cuda")
+    out = cache.attend(q, rows, starts, firsts, 1, lse=lse, chunk=chunk)
+    want, want_lse = cache.oracle(q, rows, starts, firsts, 1)
+    # outliers x20 in keys and values: outputs reach 30, where a bf16 output is 0.06 from its FP32 value and a bf16
+    # probability 2^-9 of it: the bound is 2e-2 + 2^-7 |want|
+    assert_attention_close(out, lse, want, want_lse, [0, 1, 2, 3], rel=2.0 ** -7)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8:row"])
+def test_a_column_decodes_the_same_alone_and_in_a_window(pk, kind):
+    from helpers import Cache, queries
+    cache = Cache(kind, 4, 128, 128, 16, [700, 300, 2100], spare=8)
+    q = queries(24, 24, 128, 5)
+    together = cache.attend(q, [0, 1, 2], [0, 8, 16], [690, 290, 2090], 8, chunk=256)
+    for s, start, first in zip([0, 1, 2], [0, 8, 16], [690, 290, 2090]):
+        alone = cache.attend(q[start:start + 8], [s], [0], [first], 8, chunk=256)
+        assert torch.equal(alone, together[start:start + 8])
+        for c in range(8):
+            one = cache.attend(q[start + c:start + c + 1], [s], [0], [first + c], 1, chunk=256)
+            assert torch.equal(one[0], together[start + c])
+        wide = cache.attend(q[start:start + 8], [s], [0], [first], 16, counts=[8], chunk=256)
+        assert torch.equal(wide, together[start:start + 8])
+
+
+def test_a_count_past_the_columns_reads_as_the_columns(pk):
+    from helpers import Cache, queries
+    cache = Cache("bf16", 2, 128, 128, 16, [300, 300], spare=8)
+    q = queries(8, 8, 128, 11)
+    want = cache.attend(q, [0, 1], [0, 4], [290, 280], 4)
+    got = cache.attend(q, [0, 1], [0, 4], [290, 280], 4, counts=[9, 4])
+    assert torch.equal(got, want)
+
+
+def test_packed_partial_rows_follow_the_offsets(pk):
+    from helpers import Cache, queries
+    cache = Cache("fp8:row", 4, 128, 128, 16, [700, 300, 2100], spare=8)
+    q = queries(24, 24, 128, 5)
+    together = cache.attend(q, [0, 1, 2], [0, 8, 16], [690, 290, 2090], 8, chunk=128)
+    offsets = torch.tensor([0, 3, 4], dtype=torch.int32, device="cuda")
+    splits = pk.parts_for(cache.tables.shape[1] * 16, 128)
+    space = torch.empty(pk.workspace_floats(8, 24, splits, 128), device="cuda")
+    packed = cache.attend(q, [0, 1, 2], [0, 8, 16], [690, 290, 2090], 8, counts=[3, 1, 4], offsets=offsets, tokens=8,
+                          workspace=space, chunk=128)
+    for start, count in zip([0, 8, 16], [3, 1, 4]):
+        assert torch.equal(packed[start:start + count], together[start:start + count])
+    with pytest.raises(ValueError, match="workspace"):
+        cache.attend(q, [0, 1, 2], [0, 8, 16], [690, 290, 2090], 8, workspace=space[:100], chunk=128)
+
+
+def test_a_nan_query_poisons_only_its_own_token(pk):
+    from helpers import Cache, queries
+    cache = Cache("bf16", 2, 128, 128, 16, [200], spare=8)
+    q = queries(4, 8, 128, 2)
+    clean = cache.attend(q, [0], [0], [196], 4)
+    q2 = q.clone()
+    q2[1, 3, 5] = float("nan")
+    got = cache.attend(q2, [0], [0], [196], 4)
+    assert torch.isnan(got[1, 3]).all()
+    keep = torch.ones(4, 8, dtype=torch.bool)
+    keep[1, 3] = False
+    assert torch.equal(got.cpu()[keep], clean.cpu()[keep])
+
+
+def test_config_1_matches_the_references_outputs(pk, golden):
+    """BASELINE config 1 (the reference's CPU-runnable decode step) on bf16 pages, against the reference's own FP32
+    outputs: slots bit for bit, attention within the north-star bound."""
+    from test_oracle import _c1_inputs
+    from helpers import assert_attention_close
+    data = golden("c1_full.npz")
+    hq, hkv, d, page, pool_pages, _ = (int(x) for x in data["geometry"])
+    lens, keys, values, new_k, new_v, q = _c1_inputs(data)
+    tables = torch.from_numpy(np.where(data["tables"] < 0, pool_pages, data["tables"]).astype(np.int32)).cuda()
+    k = torch.zeros(pool_pages + 1, page, hkv, d, dtype=torch.bfloat16, device="cuda")
+    v = torch.zeros_like(k)
+    rows = torch.arange(len(lens), device="cuda")
+    for s, n in enumerate(lens):
+        at = pk.slots_at(tables, torch.full((n,), s, device="cuda"), torch.arange(n, device="cuda"), page, pool_pages)
+        pk.write(torch.from_numpy(keys[s]).cuda(), torch.from_numpy(values[s]).cuda(), at, k, v, "bf16")
+    slots = pk.slots_at(tables, rows, torch.tensor(lens, device="cuda"), page, pool_pages)
+    assert slots.cpu().tolist() == data["slots"].tolist()
+    pk.write(torch.from_numpy(new_k).cuda(), torch.from_numpy(new_v).cuda(), slots, k, v, "bf16")
+    qd = torch.from_numpy(q).cuda().bfloat16()
+    lse = torch.empty(len(lens), hq, device="cuda")
+    i32 = dict(dtype=torch.int32, device="cuda")
+    out = pk.attend(qd, k, v, "bf16", tables, torch.arange(len(lens), **i32), torch.arange(len(lens), **i32),
+                    torch.tensor(lens, device="cuda"), 1, page, lse=lse)
+    assert_attention_close(out, lse, data["out"], data["lse"], list(range(len(lens))), lse_abs=2e-2)
+
+
+# -- merges ---------------------------------------------------------------------------------------------------------------
+def test_merge_of_shards_matches_the_references(pk, golden):
+    data = golden("merge.npz")
+    out, lse = pk.merge_shards(torch.from_numpy(data["outs"]).cuda(), torch.from_numpy(data["lses"]).cuda())
+    np.testing.assert_allclose(out.cpu().numpy(), data["out"], atol=1e-6, rtol=1e-5)
+    got = lse.cpu().numpy()
+    assert np.array_equal(np.isneginf(got), np.isneginf(data["lse"]))
+    keep = ~np.isneginf(got)
+    np.testing.assert_allclose(got[keep], data["lse"][keep], atol=1e-6, rtol=1e-6)
+    assert not out[4, 1].any()
+
+
+def test_merged_shards_equal_attention_over_the_whole_sequence(pk):
+    """The reference's own device test (inference/partitioned-attention/tests/test_device.py:44-68): a sequence cut in
+    two shards, each attended with its log-sum-exp, merged."""
+    from helpers import Cache, queries
+    g = torch.Generator().manual_seed(1)
+    q = queries(1, 4, 64, 1)
+    whole = Cache("bf16", 2, 64, 64, 16, [300], seed=3)
+    k, v = whole.stored()
+    at = whole.slots(0, torch.arange(300)).cpu().numpy()
+    keys, values = torch.from_numpy(k[at]).cuda().bfloat16(), torch.from_numpy(v[at]).cuda().bfloat16()
+    shards = Cache("bf16", 2, 64, 64, 16, [120, 180], seed=4)
+    shards.write(0, 0, keys[:120], values[:120])
+    shards.write(1, 0, keys[120:], values[120:])
+    lse = torch.empty(1, 4, device="cuda")
+    out = whole.attend(q, [0], [0], [299], 1, lse=lse)
+    parts = []
+    for s, n in ((0, 120), (1, 180)):
+        part_lse = torch.empty(1, 4, device="cuda")
+        parts.append((shards.attend(q, [s], [0], [n - 1], 1, lse=part_lse), part_lse))
+    merged, merged_lse = pk.merge_shards([o for o, _ in parts], [x for _, x in parts])
+    torch.testing.assert_close(merged, out.float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(merged_lse, lse, atol=2e-3, rtol=1e-4)
