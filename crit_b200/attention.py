@@ -1,0 +1,290 @@
+"""The attention slot's device form over a paged KV pool, with the interface of crit's DeviceAttention and
+PartitionedAttention (reference: inference/attention-state/code/device_attention.py:187-441, :659-716, :1082-1105;
+inference/partitioned-attention/plugin.py:15-64).
+
+forward() classifies a step's rows as the reference does (a row of up to pool.window tokens is a window row: decode
+tokens, verify windows; a longer one a prompt row) and launches crit_b200's kernels: window rows through the split-K
+decode/verify kernel and its merge, prompt rows through the prefill kernel where it serves the pool, else as pieces of
+up to 64 columns through the decode kernel (the reference's prompt_reader "decode": one reduction for every row).
+There is no torch fallback.
+
+With crit_b200's own pool the rows' page tables are never rebuilt: the launch reads the pool's block table in place
+and the step's metadata is one small upload of five numbers a row.  Any pool with the reference's attributes
+(table(), layer_pages(), dump, page, window) is served too, through padded tables built per step as the reference
+builds them.
+"""
+import math
+
+from . import partition
+
+TABLE_WIDTH = 16      # a generic pool's per-step tables are this many pages wide or a multiple (reference :1079)
+PIECE_COLUMNS = 64    # columns of a prompt row's piece when it is read by the decode kernel
+
+
+class Windows:
+    """Window rows of one launch as device tensors: tables, each row's table row, first token, column count (None:
+    `columns` each), column 0's position, and with `offsets` its first partial row."""
+
+    def __init__(self, tables, rows, starts, counts, firsts, columns, offsets=None, bounds=None, total=None):
+        self.tables, self.rows, self.starts, self.counts, self.firsts = tables, rows, starts, counts, firsts
+        self.columns, self.offsets, self.bounds, self.total = int(columns), offsets, bounds, total
+
+
+class DeviceAttention:
+    def __init__(self, kernels=None, mode="auto", int8_qk=False, decode="split", partitions=0, piece=0, device=None,
+                 kernels_mib=128, flashinfer="off", flashinfer_mib=128, prompt_reader="prefill", reader="split",
+                 latent=None, scratch=None, chunk=0):
+        """kernels: the crit_b200 module (default).  partitions: the most splits of a partial row (0: what the tables
+        need); chunk: positions per split (0: the kernels' rule).  kernels_mib: the most partials a launch takes from
+        `scratch` (the engine's Scratch, crit_plugins.memory) when one is given.  prompt_reader: "prefill" or "decode".
+        mode "torch", decode "flashinfer", flashinfer "auto", int8_qk and latent are the reference's other readers: not
+        served here."""
+        if mode == "torch" or decode != "split" or flashinfer != "off" or int8_qk or latent is not None:
+            raise ValueError("crit_b200 serves its own CUDA kernels only (mode auto, decode split, flashinfer off)")
+        if prompt_reader not in ("prefill", "decode"):
+            raise ValueError(f"prompt_reader is prefill or decode, not {prompt_reader!r}")
+        if kernels is None:
+            import crit_b200 as kernels
+        self.kernels = kernels
+        self.mode, self.prompt_reader, self.reader = mode, prompt_reader, reader
+        self.partitions, self.chunk, self.device = int(partitions), int(chunk), device
+        self.partial_bytes = (int(kernels_mib) << 20) if scratch is not None else 0
+        self.scratch = scratch
+        self._steps = {}
+        self._prompt_rows = {}
+
+    # -- facts -----------------------------------------------------------------------------------------------------------
+    def facts(self):
+        return {"reader": "crit_b200: a row's positions in contiguous splits of one chunk per pool, folded in split order; "
+                          "a column's bits are the same alone and in any window",
+                "prompt_reads": "through the prefill kernel" if self.prompt_reader == "prefill" else
+                                "in the decode's reduction (pieces of up to 64 columns)",
+                "split_kv_wide_windows": "16- or 32-row tiles; wider windows read their pages once per tile"}
+
+    def exactness(self):
+        return {"decode": "row-exact", "prompt": "exact" if self.prompt_reader == "decode" else "repeatable"}
+
+    def close(self):
+        self._steps.clear()
+        self._prompt_rows.clear()
+
+    # -- the device form -------------------------------------------------------------------------------------------------
+    def forward(self, layer, queries, pool, batch, scale=None, blocks=None, block_size=None, parents=None, lse=False,
+                sinks=None, sliding=0, latent=0):
+        """queries [tokens][heads][dim] of a StepBatch, RoundBatch or PromptBatch over the pool's KV (written for this
+        step already); each token sees its sequence's positions up to its own.  lse: also return each token's
+        log-sum-exp ([tokens][heads] FP32).  Returns out [tokens][heads][value dim] in the queries' dtype (and lse)."""
+        import torch
+        if blocks is not None or parents is not None or sinks is not None or sliding or latent:
+            raise NotImplementedError("crit_b200's attention reads causal windows over the whole context: no block lists, "
+                                      "draft trees, sinks, sliding windows or latent attention yet")
+        if not queries.is_cuda:
+            raise RuntimeError("crit_b200's attention runs on CUDA devices only (there is no CPU path)")
+        scale = scale if scale is not None else queries.shape[-1] ** -0.5
+        q = queries if queries.dtype == pool.compute and queries.stride(-1) == 1 else queries.to(pool.compute).contiguous()
+        tokens, heads = q.shape[0], q.shape[1]
+        out = q.new_empty(tokens, heads, pool.value_dim)
+        found = q.new_empty(tokens, heads, dtype=torch.float32) if lse else None
+        if getattr(batch, "prompt", False):
+            self._prompt(layer, q, pool, batch, scale, out, found)
+        elif getattr(batch, "round", False):
+            rows, cols = batch.rows, batch.width + 1
+            meta = Windows(pool.round_tables, batch.slots_t[:rows].to(torch.int32), batch.starts_t[:rows], None,
+                           batch.frontier_t, cols)
+            self._windows(layer, q, pool, meta, scale, out, found)
+        elif getattr(pool, "step_rows", 0):
+            n = len(pool.windows)
+            if n:
+                bounds = [batch.row(r)[2] for r in pool.windows]
+                meta = Windows(pool.d_tables, pool.d_rows[:n], pool.d_starts[:n], pool.d_counts[:n], pool.d_firsts[:n],
+                               pool.window, offsets=pool.d_offsets[:n], bounds=bounds, total=q.shape[0])
+                self._windows(layer, q, pool, meta, scale, out, found)
+            chosen = set(pool.windows)
+            self._prompts(layer, q, pool, batch, [r for r in range(batch.rows) if r not in chosen], scale, out, found)
+        else:
+            short = [r for r in range(batch.rows) if batch.row(r)[2] <= pool.window]
+            if short:
+                self._windows(layer, q, pool, self._step_windows(pool, batch, short, q.device), scale, out, found)
+            self._prompts(layer, q, pool, batch, [r for r in range(batch.rows) if batch.row(r)[2] > pool.window],
+                          scale, out, found)
+        out = out if out.dtype == queries.dtype else out.to(queries.dtype)
+        return (out, found) if lse else out
+
+    def merge(self, outs, lses):
+        """Partials of the same queries over disjoint keys -> (out, lse), the parts weighted by exp(lse - max) in part
+        order; a token no part saw gets zeros and -inf.  Reference: partitioned-attention/plugin.py:52-64."""
+        return self.kernels.merge_shards(outs, lses)
+
+    # -- window rows -----------------------------------------------------------------------------------------------------
+    def _step_windows(self, pool, batch, chosen, device):
+        key = (id(pool), pool.steps, tuple(chosen))
+        cached = self._steps.get("windows")
+        if cached is not None and cached[0] == key:
+            return cached[1]
+        found = windows_of(pool, [batch.row(r) for r in chosen], device)
+        self._steps["windows"] = (key, found)
+        return found
+
+    def _windows(self, layer, q, pool, meta, scale, out, found):
+        pages = pool.layer_pages(layer)
+        scaled = len(pages) == 4
+        multipliers = pool.scale_values[pool.layers[layer]] if pool.dtype == "fp8" else (1.0, 1.0)
+        kernels = self.kernels
+        positions = meta.tables.shape[1] * pool.page
+        chunk = self.chunk or kernels.chunk_for(pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, pool.page, pool.dtype)
+        if self.partitions:
+            chunk = max(chunk, -(-positions // self.partitions))
+        chunk = -(-chunk // 16) * 16
+        parts = kernels.parts_for(positions, chunk)
+        count = int(meta.starts.shape[0])
+        launches, workspace = [(slice(0, count), meta.total)], None
+        if self.partial_bytes and parts > 1:
+            per = kernels.workspace_floats(1, q.shape[1], parts, pool.value_dim)
+            capacity = self.partial_bytes // 4 // per
+            launches = _launches(meta, capacity)
+            most = max((cut.stop - cut.start) * meta.columns if tokens is None else tokens for cut, tokens in launches)
+            import torch
+            workspace = self.scratch.take(min(self.partial_bytes, 4 * per * most)).view(torch.float32)
+        for cut, tokens in launches:
+            part = (lambda t: t[cut]) if not cut.start else (lambda t: t[cut].clone())
+            offsets = part(meta.offsets) if meta.offsets is not None and tokens is not None else None
+            kernels.attend(q, pages[0], pages[1], pool.dtype, meta.tables, part(meta.rows), part(meta.starts),
+                           part(meta.firsts), meta.columns, pool.page,
+                           counts=part(meta.counts) if meta.counts is not None else None, offsets=offsets,
+                           tokens=tokens if offsets is not None else None,
+                           key_scales=pages[2] if scaled else None, value_scales=pages[3] if scaled else None,
+                           multipliers=multipliers, scale=scale, chunk=chunk, out=out, lse=found, workspace=workspace)
+
+    # -- prompt rows -----------------------------------------------------------------------------------------------------
+    def _prompts(self, layer, q, pool, batch, rows, scale, out, found):
+        if not rows:
+            return
+        if self.prompt_reader == "prefill" and self._prefill_serves(pool, q):
+            pages = pool.layer_pages(layer)
+            scaled = len(pages) == 4
+            multipliers = pool.scale_values[pool.layers[layer]] if pool.dtype == "fp8" else (1.0, 1.0)
+            for r in rows:
+                sequence, first, count, position = batch.row(r)
+                span = slice(first, first + count)
+                self.kernels.prefill(q[span], pages[0], pages[1], pool.dtype, pool.device_tables.get(sequence), position,
+                                     pool.page, key_scales=pages[2] if scaled else None,
+                                     value_scales=pages[3] if scaled else None, multipliers=multipliers, scale=scale,
+                                     out=out[span], lse=found[span] if found is not None else None)
+            return
+        pieces = []
+        for r in rows:
+            sequence, first, count, position = batch.row(r)
+            for at in range(0, count, PIECE_COLUMNS):
+                pieces.append((sequence, first + at, min(PIECE_COLUMNS, count - at), position + at))
+        self._windows(layer, q, pool, windows_of(pool, pieces, q.device), scale, out, found)
+
+    def _prefill_serves(self, pool, q):
+        serves = getattr(self.kernels, "prefill_serves", None)
+        return bool(serves and serves(pool.head_dim, pool.value_dim, q.dtype, pool.dtype, pool.page))
+
+    def _prompt(self, layer, q, pool, batch, scale, out, found):
+        """A PromptBatch: the bucket's tokens over the pool's prompt table, causal from batch.frontier_t, read on the
+        device: window rows of up to 64 columns (reference: device_attention.py:577-641)."""
+        import torch
+        key = (batch.bucket, str(q.device))
+        made = self._prompt_rows.get(key)
+        if made is None:
+            columns = min(PIECE_COLUMNS, batch.bucket)
+            count = -(-batch.bucket // columns)
+            starts = torch.arange(count, dtype=torch.int32, device=q.device) * columns
+            counts = torch.tensor([min(columns, batch.bucket - r * columns) for r in range(count)], dtype=torch.int32,
+                                  device=q.device)
+            made = self._prompt_rows[key] = (torch.zeros(count, dtype=torch.int32, device=q.device), starts, counts,
+                                             starts.long(), columns)
+        rows, starts, counts, offsets, columns = made
+        meta = Windows(pool.prompt_table, rows, starts, counts, batch.frontier_t + offsets, columns)
+        self._windows(layer, q, pool, meta, scale, out, found)
+
+
+def _launches(meta, capacity):
+    """[(rows, partial rows)]: consecutive rows whose partials fit `capacity` partial rows."""
+    count = int(meta.starts.shape[0])
+    if meta.offsets is None or meta.bounds is None:
+        step = capacity // meta.columns
+        if step < 1:
+            raise _too_small(meta.columns)
+        return [(slice(a, min(count, a + step)), None) for a in range(0, count, step)]
+    found, first, used = [], 0, 0
+    for r, bound in enumerate(meta.bounds):
+        if min(used + bound, meta.total) > capacity:
+            if r == first:
+                raise _too_small(bound)
+            found.append((slice(first, r), min(used, meta.total)))
+            first, used = r, 0
+        used += bound
+    found.append((slice(first, count), min(used, meta.total)))
+    return found
+
+
+def _too_small(tokens):
+    return ValueError(f"a row of {tokens} tokens needs more partials than the split-KV reader's workspace holds: raise "
+                      "the attention plugin's workspace_mib")
+
+
+def windows_of(pool, rows, device):
+    """Windows of host rows (sequence, first token, count, first position): their metadata in one copy to the device,
+    their partials packed by their tokens.  crit_b200's pool: the launch reads its block table in place; another pool:
+    padded tables built from pool.table() as the reference builds them (device_attention.py:1082-1105)."""
+    import torch
+    counts = [count for _, _, count, _ in rows]
+    offsets = [sum(counts[:i]) for i in range(len(rows))]
+    own = hasattr(pool, "block_tables")
+    if own:
+        pool._flush()
+        tables, ids = pool.block_tables, [pool.row_of[sequence] for sequence, _, _, _ in rows]
+    else:
+        lists = [pool.table(sequence)[:math.ceil((position + count) / pool.page)] for sequence, _, count, position in rows]
+        width = -(-max(len(t) for t in lists) // TABLE_WIDTH) * TABLE_WIDTH
+        grid = torch.full((len(rows), width), pool.dump, dtype=torch.int32)
+        for i, t in enumerate(lists):
+            grid[i, :len(t)] = torch.tensor(t, dtype=torch.int32)
+        tables, ids = grid.to(device), list(range(len(rows)))
+    meta = torch.tensor([[first, count, position, offset, row] for (_, first, count, position), offset, row
+                         in zip(rows, offsets, ids)], dtype=torch.int64)
+    meta = (meta.pin_memory() if torch.device(device).type == "cuda" else meta).to(device, non_blocking=True)
+    return Windows(tables, meta[:, 4].to(torch.int32), meta[:, 0].to(torch.int32), meta[:, 1].to(torch.int32),
+                   meta[:, 2].contiguous(), max(counts), offsets=meta[:, 3].to(torch.int32), bounds=counts,
+                   total=sum(counts))
+
+
+class PartitionedAttention:
+    """The attention slot's plugin object: the host form (partials of interleaved ownership, merged) and the device
+    form above.  Reference: inference/partitioned-attention/plugin.py:15-64."""
+
+    def __init__(self, kv, options, device_form):
+        self.kv, self.device_form = kv, device_form
+        self.ranks = [partition.SequencePartition(options["world"], rank, options["page_size"])
+                      for rank in range(options["world"])]
+
+    def attend(self, sequence, queries, positions, scale=None, pending=False):
+        rows = self.kv.rows(sequence, pending)
+        if not rows:
+            raise ValueError("no rows to attend")
+        width = len(rows[0][2])
+        out = []
+        for query, position in zip(queries, positions):
+            partials = [partition.attention_partial(query, [row for row in rows if rank.owner(row[0]) == rank.rank],
+                                                    value_width=width, query_position=position, scale=scale)
+                        for rank in self.ranks]
+            out.append(list(partition.merge_partials(partials).output))
+        return out
+
+    def forward(self, layer, queries, pool, batch, scale=None, blocks=None, block_size=None, parents=None, lse=False):
+        return self.device_form.forward(layer, queries, pool, batch, scale, blocks, block_size, parents, lse)
+
+    def merge(self, outs, lses):
+        return self.device_form.merge(outs, lses)
+
+    def facts(self):
+        return self.device_form.facts()
+
+    def exactness(self):
+        return self.device_form.exactness()
+
+    def close(self):
+        self.device_form.close()

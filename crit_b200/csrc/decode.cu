@@ -456,7 +456,7 @@ __global__ void __launch_bounds__(DECODE_THREADS) decode_kernel(const crit_b200_
             *reinterpret_cast<uint2*>(dst) = packed;
             if (p.lse && c4 == 0) p.lse[(int64_t)token * p.q_heads + head] = l > 0.f ? top * LN2 + logf(l) : -INFINITY;
         } else {
-            const int prow = (p.offsets ? p.offsets[r] : r * p.columns) + col;
+            const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
             const int64_t at = ((int64_t)prow * p.q_heads + head) * p.max_splits + split;
             *reinterpret_cast<float4*>(p.workspace + at * DV + c4 * 4) = o;
             if (c4 == 0) {
@@ -482,7 +482,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     if (nsplit <= 1) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int DV = p.value_dim, per = DV >> 5;
-    const int prow = (p.offsets ? p.offsets[r] : r * p.columns) + col;
+    const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
     const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
     const int64_t base = ((int64_t)prow * p.q_heads + head) * p.max_splits;
     const float* pm = p.workspace + states * DV;
@@ -529,6 +529,66 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     }
     if (p.lse && threadIdx.x == 0)
         p.lse[(int64_t)token * p.q_heads + head] = total > 0.f ? top * LN2 + logf(total) : -INFINITY;
+}
+
+
+// The same fold for rows of few splits: one warp per (window token, query head), the splits in order.
+template <int DV>
+__global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_params p) {
+    constexpr int PER = DV / 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t item = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int64_t items = (int64_t)p.n_rows * p.columns * p.q_heads;
+    if (item >= items) return;
+    const int head = (int)(item % p.q_heads);
+    const int rc = (int)(item / p.q_heads);
+    const int r = rc / p.columns, col = rc - r * p.columns;
+    int count = p.counts ? p.counts[r] : p.columns;
+    count = count > p.columns ? p.columns : count;
+    if (col >= count) return;
+    const int64_t L = p.firsts[r] + count;
+    const int nsplit = (int)((L + p.chunk - 1) / p.chunk);
+    if (nsplit <= 1) return;
+    const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
+    const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
+    const int64_t base = ((int64_t)prow * p.q_heads + head) * p.max_splits;
+    const float* pm = p.workspace + states * DV;
+    const float* pl = p.workspace + states * (DV + 1);
+    // every split's maximum first (one load a lane), then one pass over the outputs with fixed weights
+    float top = -INFINITY;
+    for (int s = lane; s < nsplit; s += 32) top = fmaxf(top, pm[base + s]);
+    top = warp_max(top);
+    const float sub = top == -INFINITY ? 0.f : top;
+    float total = 0.f, acc[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+#pragma unroll 4
+    for (int s = 0; s < nsplit; ++s) {
+        const float w = ex2(pm[base + s] - sub);
+        total += pl[base + s] * w;
+        const float* o = p.workspace + (base + s) * DV + lane * PER;
+        if constexpr (PER == 4) {
+            const float4 v = *reinterpret_cast<const float4*>(o);
+            acc[0] += v.x * w, acc[1] += v.y * w, acc[2] += v.z * w, acc[3] += v.w * w;
+        } else if constexpr (PER == 8) {
+            const float4 v = *reinterpret_cast<const float4*>(o), u = *reinterpret_cast<const float4*>(o + 4);
+            acc[0] += v.x * w, acc[1] += v.y * w, acc[2] += v.z * w, acc[3] += v.w * w;
+            acc[4] += u.x * w, acc[5] += u.y * w, acc[6] += u.z * w, acc[7] += u.w * w;
+        } else {
+            const float2 v = *reinterpret_cast<const float2*>(o);
+            acc[0] += v.x * w, acc[1] += v.y * w;
+        }
+    }
+    const float inv = total > 0.f ? 1.f / total : 0.f;
+    const int token = p.starts[r] + col;
+    const int64_t at = (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head + lane * PER;
+#pragma unroll
+    for (int i = 0; i < PER; i += 2) {
+        const uint32_t packed = p.q_dtype == CRIT_B200_DTYPE_BF16 ? pack2<true>(acc[i] * inv, acc[i + 1] * inv)
+                                                                   : pack2<false>(acc[i] * inv, acc[i + 1] * inv);
+        *reinterpret_cast<uint32_t*>((char*)p.out + (at + i) * 2) = packed;
+    }
+    if (p.lse && lane == 0) p.lse[(int64_t)token * p.q_heads + head] = total > 0.f ? top * LN2 + logf(total) : -INFINITY;
 }
 
 // -- host side --------------------------------------------------------------------------------------------------------
@@ -625,8 +685,17 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
 static int launch_merge(const crit_b200_attend_params& p, cudaStream_t s) {
     if (p.max_splits <= 1) return 0;
     if (p.value_dim > 256 || p.value_dim % 32) return CRIT_B200_EUNSUPPORTED;
-    dim3 grid((unsigned)p.q_heads, (unsigned)(p.n_rows * p.columns));
-    merge_kernel<<<grid, MERGE_WARPS * 32, 0, s>>>(p);
+    if (p.max_splits <= 32) {
+        const int64_t items = (int64_t)p.n_rows * p.columns * p.q_heads;
+        const unsigned blocks = (unsigned)((items + 3) / 4);
+        if (p.value_dim == 128) merge_warp_kernel<128><<<blocks, 128, 0, s>>>(p);
+        else if (p.value_dim == 256) merge_warp_kernel<256><<<blocks, 128, 0, s>>>(p);
+        else if (p.value_dim == 64) merge_warp_kernel<64><<<blocks, 128, 0, s>>>(p);
+        else return CRIT_B200_EUNSUPPORTED;
+    } else {
+        dim3 grid((unsigned)p.q_heads, (unsigned)(p.n_rows * p.columns));
+        merge_kernel<<<grid, MERGE_WARPS * 32, 0, s>>>(p);
+    }
     CRIT_CHECK_LAUNCH();
     return 0;
 }

@@ -117,7 +117,7 @@ typedef struct crit_b200_attend_params {
     const int32_t* starts;       /* [R] */
     const int32_t* counts;       /* [R] or NULL */
     const int64_t* firsts;       /* [R] */
-    const int32_t* offsets;      /* [R] first partial row of each row, or NULL (r * columns) */
+    const int32_t* offsets;      /* [R] first partial row of each row, counted from offsets[0]; or NULL (r * columns) */
     float* workspace;            /* crit_b200_attend_plan's floats, or NULL when max_splits is 1 */
     int64_t workspace_floats;
     int64_t q_stride_token, q_stride_head, out_stride_token, out_stride_head, table_stride;

@@ -1,0 +1,246 @@
+"""The plugin boundary on the GPU: crit_b200's pool and attention driven as crit's model plugin drives the
+reference's (reserve -> write -> forward -> keep), checked against the CPU oracle; the cases follow the reference's own
+plugin tests (inference/attention-state/tests/test_pages.py, inference/partitioned-attention/tests/test_device.py)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def parts(page=16, **kw):
+    from crit_b200.attention import DeviceAttention, PartitionedAttention
+    from crit_b200.kv_state import KVStateCache
+    import crit_b200
+    kv = KVStateCache(page=page, kernels=crit_b200, **kw)
+    return kv, PartitionedAttention(kv, {"world": 2, "page_size": 256}, DeviceAttention(device="cuda"))
+
+
+def rows_of(n, hkv, d, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(n, hkv, d, generator=g).bfloat16().cuda()
+
+
+def step(pool, rows, layer=0, seed=0):
+    from crit_b200.batch import StepBatch
+    batch = StepBatch.build(rows, "cuda")
+    slots = pool.reserve(batch)
+    keys = rows_of(batch.tokens, pool.kv_heads, pool.head_dim, seed)
+    values = rows_of(batch.tokens, pool.kv_heads, pool.value_dim, seed + 1)
+    pool.write(layer, slots, keys, values)
+    return batch, keys, values
+
+
+def stored(pool, layer=0):
+    i = pool.layers[layer]
+    found = []
+    for pages, scales, mult in ((pool.k[i], pool.k_scales, pool.scale_values[i][0]),
+                                (pool.v[i], pool.v_scales, pool.scale_values[i][1])):
+        dim = pages.shape[-1]
+        if pool.dtype in ("bf16", "fp16"):
+            found.append(pages.float().cpu().numpy().reshape(-1, pool.kv_heads, dim))
+            continue
+        codes = pages.view(torch.uint8).cpu().numpy().reshape(-1, pool.kv_heads, dim)
+        sc = scales[i].cpu().numpy() if scales is not None else None
+        if sc is not None and pool.dtype != "fp8:page":
+            sc = sc.reshape(-1, pool.kv_heads)
+        found.append(oracle.dequantize(codes, pool.dtype, sc, mult, page=pool.page))
+    return found
+
+
+def oracle_rows(pool, batch, q, layer=0):
+    k, v = stored(pool, layer)
+    width = max(len(pool.table(s)) for s in batch.sequences)
+    tables = np.full((batch.rows, width), pool.dump, np.int32)
+    for r, s in enumerate(batch.sequences):
+        tables[r, :len(pool.table(s))] = pool.table(s)
+    counts = [batch.row(r)[2] for r in range(batch.rows)]
+    return oracle.attend(q.float().cpu().numpy(), k, v, tables, list(range(batch.rows)), batch.starts[:-1],
+                         [batch.row(r)[3] for r in range(batch.rows)], max(counts), pool.page, counts=counts)
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8", "fp8:row", "int8", "fp8:page"])
+def test_a_step_of_many_sequences_writes_each_where_it_reads_back(dtype):
+    kv, _ = parts()
+    pool = kv.pool([0, 3], 2, 64, 256, "cuda", dtype)
+    if dtype == "fp8":
+        pool.set_scales(3, 0.05, 0.07)
+    for s in "abc":
+        pool.open(s)
+    batch, keys, values = step(pool, [("a", 0, 20), ("b", 0, 1), ("c", 0, 5)], layer=3)
+    k, v = stored(pool, 3)
+    for r in range(batch.rows):
+        s, first, count, _ = batch.row(r)
+        got_k, got_v = pool.gather(3, s, count)
+        at = oracle.slots(np.array(pool.table(s), np.int32), np.arange(count), 16)
+        assert torch.equal(got_k.cpu(), torch.from_numpy(k[at]).bfloat16())
+        assert torch.equal(got_v.cpu(), torch.from_numpy(v[at]).bfloat16())
+        if dtype == "bf16":
+            assert torch.equal(got_k, keys[first:first + count])
+    assert float(pool.gather(0, "a", 20)[0].float().abs().sum()) == 0.0      # another layer is apart
+    assert pool.free_pages() == 16 - 2 - 1 - 1
+    if dtype == "fp8:row":
+        codes, scale = oracle.quantize_rows(keys.float().cpu().numpy(), "fp8:row")
+        at = oracle.slots(np.array(pool.table("a"), np.int32), np.arange(20), 16)
+        assert np.array_equal(pool.k[1].view(torch.uint8).cpu().numpy().reshape(-1, 2, 64)[at], codes[:20])
+        assert np.array_equal(pool.k_scales[1].cpu().numpy().reshape(-1, 2)[at], scale[:20])
+
+
+def test_keep_rolls_a_verify_window_back_and_a_fork_copies_on_write():
+    kv, _ = parts()
+    pool = kv.pool([0], 2, 64, 256, "cuda", "fp8:row")
+    pool.open("a")
+    _, keys, _ = step(pool, [("a", 0, 20)])
+    pool.keep("a", 20)
+    before = pool.gather(0, "a", 20)[0].clone()
+    pool.fork("a", "b")
+    assert pool.table("a") == pool.table("b")
+    step(pool, [("b", 20, 3)], seed=9)           # into the page they share: b copies it first, scales too
+    assert pool.table("a")[0] == pool.table("b")[0] and pool.table("a")[1] != pool.table("b")[1]
+    assert torch.equal(pool.gather(0, "b", 20)[0], before) and torch.equal(pool.gather(0, "a", 20)[0], before)
+    step(pool, [("a", 20, 4)], seed=5)           # a verify window of 4
+    pool.keep("a", 21)
+    assert (pool.length("a"), len(pool.table("a"))) == (21, 2)
+    pool.keep("a", 16)
+    assert len(pool.table("a")) == 1
+    pool.close("a")
+    pool.close("b")
+    assert pool.free_pages() == 16
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8:page"])
+def test_a_decode_step_and_a_verify_window_match_the_oracle(dtype):
+    from crit_b200.batch import StepBatch
+    from helpers import assert_attention_close
+    kv, attention = parts()
+    pool = kv.pool([0], 4, 128, 16 * 400, "cuda", dtype)
+    lens = {"a": 700, "b": 64, "c": 1, "d": 2100}
+    for s, n in lens.items():
+        pool.open(s)
+        step(pool, [(s, 0, n)], seed=len(s) + n)
+        pool.keep(s, n)
+    batch, _, _ = step(pool, [("a", 700, 1), ("b", 64, 6), ("c", 1, 1), ("d", 2100, 4)], seed=77)
+    q = torch.randn(batch.tokens, 24, 128, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+    out, lse = attention.forward(0, q, pool, batch, lse=True)
+    want, want_lse = oracle_rows(pool, batch, q)
+    assert_attention_close(out, lse, want, want_lse, list(range(batch.tokens)))
+    again = attention.forward(0, q, pool, batch)           # without lse: the same bits
+    assert torch.equal(again, out)
+    # every row alone decodes to the same bits as in the batch
+    for r in range(batch.rows):
+        s, first, count, position = batch.row(r)
+        alone = StepBatch.build([(s, position, count)], "cuda")
+        pool.reserve(alone)
+        assert torch.equal(attention.forward(0, q[first:first + count], pool, alone), out[first:first + count])
+
+
+def test_a_prompt_row_past_the_window_is_causal_over_its_own_chunk():
+    from helpers import assert_attention_close
+    kv, attention = parts()
+    pool = kv.pool([0], 2, 128, 16 * 64, "cuda", "bf16")
+    pool.open("a")
+    step(pool, [("a", 0, 150)], seed=1)
+    pool.keep("a", 150)
+    batch, _, _ = step(pool, [("a", 150, 100)], seed=2)     # 100 tokens > window 16: a prompt row
+    q = torch.randn(100, 8, 128, generator=torch.Generator().manual_seed(6)).bfloat16().cuda()
+    out, lse = attention.forward(0, q, pool, batch, lse=True)
+    k, v = stored(pool)
+    want, want_lse = oracle.attend(q.float().cpu().numpy(), k, v, np.array([pool.table("a")], np.int32), [0], [0],
+                                   [150], 100, 16)
+    assert_attention_close(out, lse, want, want_lse, list(range(100)))
+
+
+def test_merged_shards_equal_attention_over_the_whole_sequence():
+    """inference/partitioned-attention/tests/test_device.py:44-68, on this pool and attention."""
+    from crit_b200.batch import StepBatch
+    kv, attention = parts()
+    g = torch.Generator().manual_seed(1)
+    keys, values = torch.randn(300, 2, 64, generator=g).bfloat16().cuda(), torch.randn(300, 2, 64, generator=g).bfloat16().cuda()
+    q = torch.randn(1, 4, 64, generator=g).bfloat16().cuda()
+
+    def pool_of(rows):
+        pool = kv.pool([0], 2, 64, 2048, "cuda", "bf16")
+        for s, (k, v) in rows.items():
+            pool.open(s)
+            batch = StepBatch.build([(s, 0, k.shape[0])], "cuda")
+            pool.write(0, pool.reserve(batch), k, v)
+            pool.keep(s, k.shape[0])
+        return pool
+    whole = pool_of({"s": (keys, values)})
+    shards = pool_of({"a": (keys[:120], values[:120]), "b": (keys[120:], values[120:])})
+
+    def attend(pool, s, position):
+        batch = StepBatch.build([(s, position, 1)], "cuda")
+        pool.reserve(batch)
+        return attention.forward(0, q, pool, batch, lse=True)
+    out, lse = attend(whole, "s", 299)
+    found = [attend(shards, s, n - 1) for s, n in (("a", 120), ("b", 180))]
+    merged, merged_lse = attention.merge([o for o, _ in found], [x for _, x in found])
+    torch.testing.assert_close(merged.float(), out.float(), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(merged_lse, lse, atol=2e-3, rtol=1e-4)
+    k = whole.gather(0, "s", 300)[0].double()
+    for h in range(4):
+        s = k[:, h // 2] @ q[0, h].double() / math.sqrt(64)
+        assert abs(float(lse[0, h]) - float(torch.logsumexp(s, 0))) < 2e-3
+    outs = [torch.ones(2, 1, 3).cuda(), torch.zeros(2, 1, 3).cuda()]
+    lses = [torch.tensor([[0.5], [float("-inf")]]).cuda(), torch.full((2, 1), float("-inf")).cuda()]
+    out, lse = attention.merge(outs, lses)
+    assert out[0].tolist() == [[1.0, 1.0, 1.0]]
+    assert (out[1].tolist(), lse[1].tolist()) == ([[0.0, 0.0, 0.0]], [float("-inf")])
+    assert abs(float(lse[0, 0]) - 0.5) < 1e-6
+
+
+def test_a_decode_step_replays_in_a_cuda_graph_over_the_step_buffers():
+    """The pool's step buffers keep a step's slots and window rows at fixed addresses: a graph captured over one step
+    replays after the next reserve() (other lengths, other rows) and gives that step's attention."""
+    from crit_b200.batch import StepBatch
+    from helpers import assert_attention_close
+    kv, attention = parts(step_rows=4, step_tokens=16)
+    pool = kv.pool([0], 2, 128, 16 * 64, "cuda", "bf16")
+    lens = {"a": 40, "b": 300, "c": 5}
+    for s, n in lens.items():
+        pool.open(s)
+        step(pool, [(s, 0, n)], seed=n)
+        pool.keep(s, n)
+    q = torch.zeros(3, 8, 128, dtype=torch.bfloat16, device="cuda")
+    keys = torch.zeros(3, 2, 128, dtype=torch.bfloat16, device="cuda")
+    values = torch.zeros_like(keys)
+    g = torch.Generator().manual_seed(8)
+
+    def fill():
+        q.copy_(torch.randn(3, 8, 128, generator=g).bfloat16())
+        keys.copy_(torch.randn(3, 2, 128, generator=g).bfloat16())
+        values.copy_(torch.randn(3, 2, 128, generator=g).bfloat16())
+    batch = StepBatch.build([(s, lens[s], 1) for s in "abc"], "cuda")
+    slots = pool.reserve(batch)
+    fill()
+    pool.write(0, slots, keys, values)
+    attention.forward(0, q, pool, batch, lse=True)              # warm: workspaces are made outside the capture
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            pool.write(0, slots, keys, values)
+            out, lse = attention.forward(0, q, pool, batch, lse=True)
+    for turn in range(3):
+        for s in "abc":
+            pool.keep(s, lens[s] + 1)
+            lens[s] += 1
+        batch = StepBatch.build([(s, lens[s], 1) for s in "abc"], "cuda")
+        assert pool.reserve(batch).data_ptr() == slots.data_ptr()
+        fill()
+        graph.replay()
+        torch.cuda.synchronize()
+        want, want_lse = oracle_rows(pool, batch, q)
+        assert_attention_close(out, lse, want, want_lse, [0, 1, 2])
+
+
+def test_facts_count_the_bytes_a_token_takes():
+    kv, attention = parts()
+    kv.pool([0, 1], 8, 128, 1024, "cuda", "fp8:page")
+    assert kv.facts()["kv_bytes_per_token"] == 2 * (8 * 128 * 2 + 8 * 2 * 4 / 16)
+    assert attention.exactness()["decode"] == "row-exact"
