@@ -199,7 +199,7 @@ def test_a_decode_step_replays_in_a_cuda_graph_over_the_step_buffers():
     replays after the next reserve() (other lengths, other rows) and gives that step's attention."""
     from crit_b200.batch import StepBatch
     from helpers import assert_attention_close
-    kv, attention = parts(step_rows=4, step_tokens=16)
+    kv, attention = parts(step_rows=4, step_tokens=512)
     pool = kv.pool([0], 2, 128, 16 * 64, "cuda", "bf16")
     lens = {"a": 40, "b": 300, "c": 5}
     for s, n in lens.items():
