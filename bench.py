@@ -192,7 +192,7 @@ def step(state, launch="both", append=True):
         pk.write(state["d_k"], state["d_v"], state["slots"], state["k"], state["v"], w["kind"], state["ks"], state["vs"])
     pk.attend(state["d_q"], state["k"], state["v"], w["kind"], state["tables"], state["rows"], state["starts"],
               state["firsts"], w["columns"], w["page"], key_scales=state["ks"], value_scales=state["vs"],
-              out=state["out"], lse=state["lse"], launch=launch)
+              out=state["out"], lse=state["lse"], launch=launch, staging=state.get("staging"))
 
 
 def timed(fn, steps, warmup, stream):
@@ -250,6 +250,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--staging", default=None, choices=["tma", "cp.async"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -266,6 +267,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     state = build_state(w, device, rank, world)
+    state["staging"] = args.staging
     torch.cuda.synchronize()
     tokens_step = state["tokens"]
     config = {"workload": w["name"], "kv": w["kind"], "steps_are": "slot map + KV append + split-K decode + merge",

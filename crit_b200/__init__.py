@@ -26,7 +26,7 @@ import torch
 from . import _lib
 
 __all__ = ["KINDS", "MAX_COLUMNS", "attend", "chunk_for", "gather", "merge_shards", "owner", "partitions", "parts_for",
-           "piece_size", "prefill", "release", "slots_at", "tile_for", "workspace_floats", "write"]
+           "piece_size", "prefill", "release", "slots_at", "status", "tile_for", "workspace_floats", "write"]
 
 KINDS = {"bf16": 0, "fp16": 0, "fp8": 1, "fp8:row": 2, "int8": 3, "fp8:page": 4}
 MAX_COLUMNS = 64            # columns of one row a launch reads
@@ -109,6 +109,27 @@ def _workspace(device, floats, given):
             _retired.append((at[1], found))
         found = _workspaces[at] = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
     return found
+
+
+_status = {}
+
+
+def _status_word(device):
+    """One int32 a device: a kernel sets it (and never clears it) when one of its bounded waits gave up."""
+    found = _status.get(str(device))
+    if found is None:
+        if torch.cuda.is_current_stream_capturing():
+            return None
+        found = _status[str(device)] = torch.zeros(1, dtype=torch.int32, device=device)
+    return found
+
+
+def status(device=None):
+    """0, or what a kernel recorded on `device` since load: 1 = a TMA copy's mbarrier wait ran out (that launch wrote
+    nothing for the block concerned).  Reads the device word (one wait)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    found = _status.get(str(device))
+    return 0 if found is None else int(found.item())
 
 
 # -- geometry rules -----------------------------------------------------------------------------------------------------
@@ -256,7 +277,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
            offsets=None, tokens=None, key_scales=None, value_scales=None, multipliers=(1.0, 1.0), scale=None,
            partitions=None, parents=None, blocks=None, block_size=None, out=None, lse=None, workspace=None, piece=None,
            fused=False, fresh=None, vsplit=None, tile=None, num_warps=None, num_stages=None, maxnreg=None,
-           flash=False, chunk=None, ramp=None, sinks=None, sliding=0, derive=None, launch="both"):
+           flash=False, chunk=None, ramp=None, sinks=None, sliding=0, derive=None, launch="both", staging=None):
     """Decode and verify windows over paged KV (reference: paged_kv_attention/__init__.py:396-445, same arguments).
 
     q [tokens][heads][dim] bf16 or fp16 (fp16 for "fp16" pages); key_pages / value_pages one layer's pages
@@ -268,7 +289,8 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     chunk: positions per split (default chunk_for()); partitions: the most splits a partial row may take (the
     workspace's, see partitions()).  piece, fused, vsplit, tile, num_warps, num_stages, maxnreg, flash and ramp are
     accepted and change nothing (one launch shape per geometry).  parents, blocks, fresh, sinks, sliding and derive
-    are not served.  launch: "both", or "decode" / "merge" alone (a measurement's)."""
+    are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: None (TMA tiled loads
+    where the geometry allows them: heads of 128 or 256 values, else cp.async) or "cp.async" (never TMA; the same bits)."""
     _refuse(parents=parents, blocks=blocks, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
@@ -319,6 +341,11 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     p.q_heads, p.kv_heads, p.head_dim, p.value_dim, p.page = hq, hkv, d, dv, page
     p.kind, p.page_dtype, p.q_dtype = k_kind, _page_dtype(kind, key_pages), _DTYPES[q.dtype]
     p.chunk, p.max_splits = chunk, splits
+    p.slots = key_pages.numel() // (hkv * d)
+    if staging not in (None, "tma", "cp.async"):
+        raise ValueError("staging is None, tma or cp.async")
+    p.flags = 1 if staging == "cp.async" else 0
+    p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])
     lib = _lib.load()

@@ -37,13 +37,13 @@ class AttendParams(Structure):
     _fields_ = [("q", c_void_p), ("out", c_void_p), ("lse", c_void_p), ("key_pages", c_void_p),
                 ("value_pages", c_void_p), ("key_scales", c_void_p), ("value_scales", c_void_p),
                 ("tables", c_void_p), ("rows", c_void_p), ("starts", c_void_p), ("counts", c_void_p),
-                ("firsts", c_void_p), ("offsets", c_void_p), ("workspace", c_void_p),
-                ("workspace_floats", c_int64), ("q_stride_token", c_int64), ("q_stride_head", c_int64),
+                ("firsts", c_void_p), ("offsets", c_void_p), ("workspace", c_void_p), ("status", c_void_p),
+                ("workspace_floats", c_int64), ("slots", c_int64), ("q_stride_token", c_int64), ("q_stride_head", c_int64),
                 ("out_stride_token", c_int64), ("out_stride_head", c_int64), ("table_stride", c_int64),
                 ("n_rows", c_int32), ("columns", c_int32), ("partial_rows", c_int32),
                 ("q_heads", c_int32), ("kv_heads", c_int32), ("head_dim", c_int32), ("value_dim", c_int32),
                 ("page", c_int32), ("kind", c_int32), ("page_dtype", c_int32), ("q_dtype", c_int32),
-                ("chunk", c_int32), ("max_splits", c_int32),
+                ("chunk", c_int32), ("max_splits", c_int32), ("flags", c_int32),
                 ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float)]
 
 

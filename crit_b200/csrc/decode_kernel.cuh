@@ -1,0 +1,583 @@
+// Split-K decode / speculative-verify attention over paged KV: the device kernel.
+//
+// One block serves (window row, kv head, split of `chunk` positions, tile of 16*MT query rows); a query row is one
+// (column, query head of the kv head's group) pair, so a GQA group's heads and a verify window's columns share every
+// key and value byte the block reads.  The block's four warps each stream their own 16-position tiles of the split
+// (tile i of the split belongs to warp i mod 4) through a private ring of stages in shared memory: a warp never waits
+// for another inside the loop.
+//
+// Staging (template TMA):
+//   true   one elected lane issues TMA tiled loads (cp.async.bulk.tensor, boxes of [16 positions][1 kv head][128 bytes]
+//          with the 128-byte swizzle, from a 3-D tensor map over [slots][kv_heads][dim]) and bulk copies of the tile's
+//          scales; their bytes are counted on the stage's mbarrier, which the warp's lanes then wait on (bounded);
+//   false  every lane issues 16-byte cp.async copies (zero-filled past the row's last position) in commit groups.
+// Scores and outputs are m16n8k16 tensor-core products with FP32 accumulators; the online softmax lives in registers
+// (quad shuffles for the row maxima).  8-bit pages (E4M3, INT8) are converted to FP16 in registers on the way from
+// shared memory to the tensor cores: the head dimension is consumed in a permuted order (each thread reads 16
+// contiguous bytes of a key row) and the value columns are produced in a permuted order (each thread owns contiguous
+// output columns), which needs no transposing load.  The warps' states are folded through shared memory at the end;
+// a row that fits one split is written out directly, else the split's state goes to the workspace for the merge.
+//
+// HBM traffic per block: its split's keys and values once (the algorithmic bytes), the queries, one partial state.
+// Reference: paged_kv_attention/_kernels.py:263-478 (_partition, _window_kernel), cuda_window.cu:284-1065 (cw_tile).
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace crit_b200 {
+
+constexpr int DECODE_WARPS = 4;
+constexpr int DECODE_THREADS = DECODE_WARPS * 32;
+
+// Page element classes (PK): 0 bf16, 1 fp16, 2 E4M3 bytes, 3 INT8 bytes.
+template <int D, int DV, int PK, int MT, bool TMA>
+struct DecodeCfg {
+    static constexpr int ES = PK < 2 ? 2 : 1;
+    static constexpr bool BF16 = PK == 0;
+    static constexpr int KROW = D * ES, VROW = DV * ES;
+    static constexpr int KTILE = 16 * KROW, VTILE = 16 * VROW;
+    static constexpr int TILES = KTILE + VTILE;
+    static constexpr int STAGES = TILES <= 4096 ? 4 : 3;
+    static constexpr int QROW = D * 2 + (ES == 1 ? 16 : 0);
+    static constexpr int QBYTES = 16 * MT * QROW;
+    static constexpr int FOLD = DECODE_WARPS * 16 * MT * (DV + 2) * 4;
+    static constexpr bool QREG = MT == 1 && D <= 128;
+    // dynamic shared memory: [1 KB of alignment slack][tiles | scales (or the fold)][queries][mbarriers]
+    __host__ __device__ static constexpr int ring_bytes(int scb) { return DECODE_WARPS * STAGES * (TILES + scb); }
+    __host__ __device__ static constexpr int region(int scb) { return ((ring_bytes(scb) > FOLD ? ring_bytes(scb) : FOLD) + 127) / 128 * 128; }
+    __host__ __device__ static constexpr int smem_bytes(int scb) { return 1024 + region(scb) + QBYTES + DECODE_WARPS * STAGES * 8; }
+};
+
+__device__ __forceinline__ int swz16(int c, int row) { return (c & ~7) | ((c ^ row) & 7); }
+
+template <int D>
+__device__ __forceinline__ int kswz8(int row, int c) {
+    if constexpr (D == 128) return c ^ (row & 1);
+    else if constexpr (D == 256) return c ^ (((row & 1) << 1) | ((c >> 3) & 1));
+    else return c;
+}
+template <int DV>
+__device__ __forceinline__ int vswz8(int row, int c) {
+    if constexpr (DV == 128) return c ^ (((row >> 1) & 3) << 1);
+    else if constexpr (DV == 256) return c ^ ((row >> 1) & 1) ^ (((row >> 2) & 1) << 2);
+    else return c ^ ((row >> 1) & 3);
+}
+
+// Byte offset of 16-byte chunk c of row `row` inside a 16-row tile.
+//   TMA:      the tile is boxes of [16 rows][128 bytes] (2 KB each), chunk index xor'ed with row & 7 (128-byte swizzle);
+//   cp.async: rows of ROWB bytes with a swizzle chosen for the reads each element size makes.
+template <bool TMA, int ROWB, int ES, int DIM, bool IS_V>
+__device__ __forceinline__ int tile_off(int row, int c) {
+    if constexpr (TMA) {
+        return ((c >> 3) << 11) + (row << 7) + (((c & 7) ^ (row & 7)) << 4);
+    } else if constexpr (ES == 2) {
+        return row * ROWB + (swz16(c, row) << 4);
+    } else if constexpr (IS_V) {
+        return row * ROWB + (vswz8<DIM>(row, c) << 4);
+    } else {
+        return row * ROWB + (kswz8<DIM>(row, c) << 4);
+    }
+}
+
+template <int D, int DV, int PK, int MT, bool TMA>
+__global__ void __launch_bounds__(DECODE_THREADS)
+decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode, const int scb,
+              const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+    using C = DecodeCfg<D, DV, PK, MT, TMA>;
+    constexpr bool BF16 = C::BF16;
+    constexpr int ES = C::ES;
+    constexpr int ROWS = 16 * MT;
+    constexpr int KC = C::KROW / 16, VC = C::VROW / 16;      // 16-byte chunks of a key row, of a value row
+    extern __shared__ unsigned char smem_raw[];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int split = blockIdx.x;
+    const int h = blockIdx.y / ctiles, ct = blockIdx.y - h * ctiles;
+    const int r = blockIdx.z;
+    const int G = p.q_heads / p.kv_heads;
+
+    int count = p.counts ? p.counts[r] : p.columns;
+    count = count > p.columns ? p.columns : count;
+    if (count <= 0) return;
+    if (ct * ROWS >= count * G) return;
+    const int64_t first = p.firsts[r];
+    const int64_t L = first + count;
+    const int64_t begin = (int64_t)split * p.chunk;
+    if (begin >= L) return;
+    const int64_t end = begin + p.chunk < L ? begin + p.chunk : L;
+    const int nsplit = (int)((L + p.chunk - 1) / p.chunk);
+    const int32_t* table = p.tables + (int64_t)p.rows[r] * p.table_stride;
+    const int start = p.starts[r];
+
+    // shared memory, its base rounded up to 1 KB (the 128-byte swizzle's period is 8 rows of 128 bytes)
+    unsigned char* smem = smem_raw + ((1024 - (smem_addr(smem_raw) & 1023)) & 1023);
+    const int region = C::region(scb);
+    unsigned char* tiles = smem + warp * (C::STAGES * C::TILES);
+    unsigned char* scales_ring = smem + DECODE_WARPS * C::STAGES * C::TILES + warp * (C::STAGES * scb);
+    unsigned char* qs = smem + region;
+    const uint32_t bars = smem_addr(qs + C::QBYTES) + warp * (C::STAGES * 8);
+
+    if constexpr (TMA) {
+        if (lane == 0) {
+#pragma unroll
+            for (int s = 0; s < C::STAGES; ++s) mbar_init(bars + s * 8, 1);
+            mbar_init_fence();
+        }
+    }
+
+    // -- the query tile into shared memory ---------------------------------------------------------------------------
+    {
+        constexpr int CPR = D / 8;
+        for (int idx = tid; idx < ROWS * CPR; idx += DECODE_THREADS) {
+            const int rr = idx / CPR, c = idx - rr * CPR;
+            const int flat = ct * ROWS + rr;
+            const int col = flat / G, gq = flat - col * G;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (col < count) {
+                const char* src = (const char*)p.q +
+                                  ((int64_t)(start + col) * p.q_stride_token + (int64_t)(h * G + gq) * p.q_stride_head + c * 8) * 2;
+                v = *reinterpret_cast<const uint4*>(src);
+            }
+            if constexpr (ES == 2) {
+                *reinterpret_cast<uint4*>(qs + rr * C::QROW + swz16(c, rr) * 16) = v;
+            } else {
+                if (p.q_dtype == CRIT_B200_DTYPE_BF16) {
+                    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&w[i]);
+                        float2 f = __bfloat1622float2(b);
+                        f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
+                        f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
+                        __half2 hh = __floats2half2_rn(f.x, f.y);
+                        w[i] = *reinterpret_cast<uint32_t*>(&hh);
+                    }
+                    v = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+                *reinterpret_cast<uint4*>(qs + rr * C::QROW + c * 16) = v;
+            }
+        }
+    }
+    __syncthreads();
+
+    // The last position each of this thread's query rows sees (-1: a padding row).
+    int64_t lastpos[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int flat = ct * ROWS + mt * 16 + g + 8 * hf;
+            const int col = flat / G;
+            lastpos[mt][hf] = col < count ? first + col : -1;
+        }
+
+    uint32_t qa[C::QREG ? D / 16 : 1][4];
+    if constexpr (C::QREG) {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            if constexpr (ES == 2) {
+                const int j = lane >> 3, row = (lane & 7) + 8 * (j & 1), chunk = 2 * ks + (j >> 1);
+                ldmatrix_x4(qa[ks], smem_addr(qs + row * C::QROW + swz16(chunk, row) * 16));
+            } else {
+                const uint2 lo = *reinterpret_cast<const uint2*>(qs + g * C::QROW + (t * (D / 4) + 4 * ks) * 2);
+                const uint2 hi = *reinterpret_cast<const uint2*>(qs + (g + 8) * C::QROW + (t * (D / 4) + 4 * ks) * 2);
+                qa[ks][0] = lo.x, qa[ks][1] = hi.x, qa[ks][2] = lo.y, qa[ks][3] = hi.y;
+            }
+        }
+    }
+
+    float acc[MT][DV / 8][4];
+    float m_run[MT][2], l_run[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[mt][n][i] = 0.f;
+        m_run[mt][0] = m_run[mt][1] = -INFINITY;
+        l_run[mt][0] = l_run[mt][1] = 0.f;
+    }
+
+    const float kmul = (PK == 2 && smode == 0) ? p.key_multiplier : 1.f;
+    const float sl2 = p.scale * LOG2E * kmul;
+
+    // -- this warp's tiles ---------------------------------------------------------------------------------------------
+    const int tile0 = (int)(begin >> 4);
+    const int ntiles = (int)((end - begin + 15) >> 4);
+    const int mine = ntiles > warp ? (ntiles - warp + DECODE_WARPS - 1) / DECODE_WARPS : 0;
+    const char* kbase = (const char*)p.key_pages + (int64_t)h * C::KROW;
+    const char* vbase = (const char*)p.value_pages + (int64_t)h * C::VROW;
+    const int64_t krow_stride = (int64_t)p.kv_heads * C::KROW, vrow_stride = (int64_t)p.kv_heads * C::VROW;
+    const uint32_t scale_bytes = smode == 2 ? (uint32_t)p.kv_heads * 4u : (smode == 1 ? (uint32_t)p.kv_heads * 64u : 0u);
+
+    auto issue = [&](int i) {
+        if (i < mine) {
+            const int64_t pos0 = (int64_t)(tile0 + warp + i * DECODE_WARPS) << 4;
+            const int pidx = (int)(pos0 / p.page);
+            const int off = (int)(pos0 - (int64_t)pidx * p.page);
+            const int pg = table[pidx];
+            const int64_t slot0 = (int64_t)pg * p.page + off;
+            const int stage = i % C::STAGES;
+            const uint32_t ks = smem_addr(tiles + stage * C::TILES), vs = ks + C::KTILE;
+            const uint32_t sc = smem_addr(scales_ring + stage * scb);
+            if constexpr (TMA) {
+                if (lane == 0) {
+                    const uint32_t bar = bars + stage * 8;
+                    fence_proxy_async();
+                    mbar_expect_tx(bar, (uint32_t)C::TILES + (PK >= 2 ? 2u * scale_bytes : 0u));
+#pragma unroll
+                    for (int b = 0; b < C::KROW / 128; ++b) tma_load_3d(ks + b * 2048, &kmap, b * (128 / ES), h, (int)slot0, bar);
+#pragma unroll
+                    for (int b = 0; b < C::VROW / 128; ++b) tma_load_3d(vs + b * 2048, &vmap, b * (128 / ES), h, (int)slot0, bar);
+                    if (PK >= 2 && smode) {
+                        const int64_t at = smode == 2 ? (int64_t)pg * p.kv_heads : slot0 * p.kv_heads;
+                        bulk_load(sc, p.key_scales + at, scale_bytes, bar);
+                        bulk_load(sc + (scb >> 1), p.value_scales + at, scale_bytes, bar);
+                    }
+                }
+            } else {
+                const int live = (int)(L - pos0 < 16 ? L - pos0 : 16);
+#pragma unroll
+                for (int u = 0; u < 16 * KC / 32; ++u) {
+                    const int id = lane + 32 * u, row = id / KC, c = id - row * KC;
+                    const bool ok = row < live;
+                    cp_async16(ks + tile_off<false, C::KROW, ES, D, false>(row, c),
+                               kbase + (slot0 + (ok ? row : 0)) * krow_stride + c * 16, ok);
+                }
+#pragma unroll
+                for (int u = 0; u < 16 * VC / 32; ++u) {
+                    const int id = lane + 32 * u, row = id / VC, c = id - row * VC;
+                    const bool ok = row < live;
+                    cp_async16(vs + tile_off<false, C::VROW, ES, DV, true>(row, c),
+                               vbase + (slot0 + (ok ? row : 0)) * vrow_stride + c * 16, ok);
+                }
+                if (PK >= 2 && smode) {
+                    const int row = lane & 15;
+                    const bool ok = row < live;
+                    const float* src = lane < 16 ? p.key_scales : p.value_scales;
+                    const int64_t at = smode == 2 ? (int64_t)pg * p.kv_heads + h : (slot0 + (ok ? row : 0)) * p.kv_heads + h;
+                    cp_async4(sc + lane * 4, src + at, ok);
+                }
+            }
+        }
+        if constexpr (!TMA) cp_async_commit();
+    };
+
+#pragma unroll
+    for (int i = 0; i < C::STAGES - 1; ++i) issue(i);
+
+    bool dead = false;
+    for (int i = 0; i < mine; ++i) {
+        issue(i + C::STAGES - 1);
+        const int stage = i % C::STAGES;
+        if constexpr (TMA) {
+            if (!__all_sync(0xffffffffu, mbar_wait(bars + stage * 8, (uint32_t)(i / C::STAGES) & 1u))) {
+                dead = true;                // the copy never landed: record it and leave, nothing is written
+                break;
+            }
+        } else {
+            cp_async_wait<C::STAGES - 1>();
+            __syncwarp();
+        }
+        const int64_t pos0 = (int64_t)(tile0 + warp + i * DECODE_WARPS) << 4;
+        unsigned char* kst = tiles + stage * C::TILES;
+        unsigned char* vst = kst + C::KTILE;
+        const float* scales = reinterpret_cast<const float*>(scales_ring + stage * scb);
+        const bool masked = pos0 + 16 > first;
+        if constexpr (TMA) {
+            // A tiled load brings all 16 rows: the value rows past the row's last position become zeros, as the
+            // zero-filling cp.async leaves them (a probability of 0 times a stale NaN would poison the output).
+            const int live = (int)(L - pos0 < 16 ? L - pos0 : 16);
+            if (live < 16) {
+                for (int id = lane; id < 16 * VC; id += 32) {
+                    const int row = id / VC, c = id - row * VC;
+                    if (row >= live)
+                        *reinterpret_cast<uint4*>(vst + tile_off<true, C::VROW, ES, DV, true>(row, c)) = make_uint4(0, 0, 0, 0);
+                }
+                __syncwarp();
+            }
+        }
+
+        // scores: S[16*MT x 16] = Q K^T
+        float s[MT][2][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[mt][n][e] = 0.f;
+
+        uint32_t kw[2][ES == 1 ? D / 16 : 1];
+        if constexpr (ES == 1) {
+#pragma unroll
+            for (int n = 0; n < 2; ++n) {
+                const int row = g + 8 * n;
+#pragma unroll
+                for (int qd = 0; qd < D / 64; ++qd) {
+                    const int c = t * (D / 64) + qd;
+                    const uint4 v = *reinterpret_cast<const uint4*>(kst + tile_off<TMA, C::KROW, ES, D, false>(row, c));
+                    kw[n][qd * 4 + 0] = v.x, kw[n][qd * 4 + 1] = v.y, kw[n][qd * 4 + 2] = v.z, kw[n][qd * 4 + 3] = v.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t kb[4];
+            if constexpr (ES == 2) {
+                const int j = lane >> 3, tok = (lane & 7) + 8 * (j >> 1), chunk = 2 * ks + (j & 1);
+                ldmatrix_x4(kb, smem_addr(kst + tile_off<TMA, C::KROW, ES, D, false>(tok, chunk)));
+            } else {
+                kb[0] = code2_to_f16x2<PK == 3>(kw[0][ks]);
+                kb[1] = code2_to_f16x2<PK == 3>(kw[0][ks] >> 16);
+                kb[2] = code2_to_f16x2<PK == 3>(kw[1][ks]);
+                kb[3] = code2_to_f16x2<PK == 3>(kw[1][ks] >> 16);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+                uint32_t a[4];
+                if constexpr (C::QREG) {
+                    a[0] = qa[ks][0], a[1] = qa[ks][1], a[2] = qa[ks][2], a[3] = qa[ks][3];
+                } else if constexpr (ES == 2) {
+                    const int j = lane >> 3, row = mt * 16 + (lane & 7) + 8 * (j & 1), chunk = 2 * ks + (j >> 1);
+                    ldmatrix_x4(a, smem_addr(qs + row * C::QROW + swz16(chunk, row) * 16));
+                } else {
+                    const int row = mt * 16 + g;
+                    const uint2 lo = *reinterpret_cast<const uint2*>(qs + row * C::QROW + (t * (D / 4) + 4 * ks) * 2);
+                    const uint2 hi = *reinterpret_cast<const uint2*>(qs + (row + 8) * C::QROW + (t * (D / 4) + 4 * ks) * 2);
+                    a[0] = lo.x, a[1] = hi.x, a[2] = lo.y, a[3] = hi.y;
+                }
+                mma16816<BF16>(s[mt][0], a, kb[0], kb[1]);
+                mma16816<BF16>(s[mt][1], a, kb[2], kb[3]);
+            }
+        }
+
+        // the tile's scales: ksc/vsc[2 * n + e] belong to position n * 8 + 2 * t + e of the tile
+        float ksc[4] = {1.f, 1.f, 1.f, 1.f}, vsc[4] = {1.f, 1.f, 1.f, 1.f};
+        if (PK >= 2 && smode) {
+            if constexpr (TMA) {
+                const float* vscales = scales + (scb >> 3);
+                if (smode == 2) {
+                    const float a = scales[h], b = vscales[h];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) ksc[e] = a, vsc[e] = b;
+                } else {
+#pragma unroll
+                    for (int n = 0; n < 2; ++n)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int tok = n * 8 + 2 * t + e;
+                            ksc[2 * n + e] = scales[tok * p.kv_heads + h];
+                            vsc[2 * n + e] = vscales[tok * p.kv_heads + h];
+                        }
+                }
+            } else {
+#pragma unroll
+                for (int n = 0; n < 2; ++n) {
+                    const float2 a = *reinterpret_cast<const float2*>(scales + n * 8 + 2 * t);
+                    const float2 b = *reinterpret_cast<const float2*>(scales + 16 + n * 8 + 2 * t);
+                    ksc[2 * n] = a.x, ksc[2 * n + 1] = a.y, vsc[2 * n] = b.x, vsc[2 * n + 1] = b.y;
+                }
+            }
+        }
+
+        // scale, mask, online softmax (base 2)
+        uint32_t pa[MT][4];
+        bool rescale = false;
+        float alpha[MT][2];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float x = s[mt][n][e] * (sl2 * ksc[2 * n + (e & 1)]);
+                    if (masked) {
+                        const int64_t pos = pos0 + n * 8 + 2 * t + (e & 1);
+                        if (pos > lastpos[mt][e >> 1]) x = -INFINITY;
+                    }
+                    s[mt][n][e] = x;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], x);
+                }
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
+                mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
+                const float top = fmaxf(m_run[mt][hf], mx[hf]);
+                const float sub = top == -INFINITY ? 0.f : top;
+                alpha[mt][hf] = ex2(m_run[mt][hf] - sub);
+                rescale |= top != m_run[mt][hf];
+                m_run[mt][hf] = top;
+                mx[hf] = sub;
+            }
+            float sum[2] = {0.f, 0.f};
+            float pr[2][4];
+#pragma unroll
+            for (int n = 0; n < 2; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = ex2(s[mt][n][e] - mx[e >> 1]);
+                    sum[e >> 1] += pv;
+                    float scaled = pv * vsc[2 * n + (e & 1)];
+                    if (masked && s[mt][n][e] == -INFINITY) scaled = 0.f;     // a stale scale past the row's end
+                    pr[n][e] = scaled;
+                }
+            l_run[mt][0] = l_run[mt][0] * alpha[mt][0] + sum[0];
+            l_run[mt][1] = l_run[mt][1] * alpha[mt][1] + sum[1];
+            pa[mt][0] = pack2<BF16>(pr[0][0], pr[0][1]);
+            pa[mt][1] = pack2<BF16>(pr[0][2], pr[0][3]);
+            pa[mt][2] = pack2<BF16>(pr[1][0], pr[1][1]);
+            pa[mt][3] = pack2<BF16>(pr[1][2], pr[1][3]);
+        }
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int n = 0; n < DV / 8; ++n) {
+                    acc[mt][n][0] *= alpha[mt][0], acc[mt][n][1] *= alpha[mt][0];
+                    acc[mt][n][2] *= alpha[mt][1], acc[mt][n][3] *= alpha[mt][1];
+                }
+        }
+
+        // outputs: O[16*MT x DV] += P V
+        if constexpr (ES == 2) {
+#pragma unroll
+            for (int np = 0; np < DV / 16; ++np) {
+                uint32_t vb[4];
+                const int j = lane >> 3, tok = (lane & 7) + 8 * (j & 1), chunk = 2 * np + (j >> 1);
+                ldmatrix_x4_trans(vb, smem_addr(vst + tile_off<TMA, C::VROW, ES, DV, true>(tok, chunk)));
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma16816<BF16>(acc[mt][2 * np], pa[mt], vb[0], vb[1]);
+                    mma16816<BF16>(acc[mt][2 * np + 1], pa[mt], vb[2], vb[3]);
+                }
+            }
+        } else {
+            constexpr int VW = DV / 32;            // 32-bit words of a value row this thread owns
+            uint32_t vw[4][VW];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const int row = 2 * t + (q4 & 1) + 8 * (q4 >> 1);
+                if constexpr (DV == 64) {
+                    const uint2 v = *reinterpret_cast<const uint2*>(vst + tile_off<false, C::VROW, ES, DV, true>(row, g >> 1) + (g & 1) * 8);
+                    vw[q4][0] = v.x, vw[q4][1] = v.y;
+                } else {
+#pragma unroll
+                    for (int qd = 0; qd < DV / 128; ++qd) {
+                        const int c = g * (DV / 128) + qd;
+                        const uint4 v = *reinterpret_cast<const uint4*>(vst + tile_off<TMA, C::VROW, ES, DV, true>(row, c));
+                        vw[q4][qd * 4 + 0] = v.x, vw[q4][qd * 4 + 1] = v.y, vw[q4][qd * 4 + 2] = v.z, vw[q4][qd * 4 + 3] = v.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int np = 0; np < DV / 16; ++np) {
+                const int w = np >> 1;
+                const uint32_t sel = (np & 1) ? 0x7362u : 0x5140u;
+                const uint32_t x01 = __byte_perm(vw[0][w], vw[1][w], sel);
+                const uint32_t x23 = __byte_perm(vw[2][w], vw[3][w], sel);
+                const uint32_t b00 = code2_to_f16x2<PK == 3>(x01), b01 = code2_to_f16x2<PK == 3>(x23);
+                const uint32_t b10 = code2_to_f16x2<PK == 3>(x01 >> 16), b11 = code2_to_f16x2<PK == 3>(x23 >> 16);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    mma16816<BF16>(acc[mt][2 * np], pa[mt], b00, b01);
+                    mma16816<BF16>(acc[mt][2 * np + 1], pa[mt], b10, b11);
+                }
+            }
+        }
+        __syncwarp();
+    }
+    if constexpr (TMA) {
+        if (__any_sync(0xffffffffu, dead)) {
+            // Give every copy this warp still has in flight a last bounded chance to land before the block leaves.
+            for (int s = 0; s < C::STAGES; ++s) mbar_wait(bars + s * 8, 0, 1 << 12);
+            if (lane == 0 && p.status) atomicExch(p.status, 1);
+            dead = true;
+        }
+    } else {
+        cp_async_wait<0>();
+    }
+
+    // -- fold the four warps' states ---------------------------------------------------------------------------------
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            l_run[mt][hf] += __shfl_xor_sync(0xffffffffu, l_run[mt][hf], 1);
+            l_run[mt][hf] += __shfl_xor_sync(0xffffffffu, l_run[mt][hf], 2);
+        }
+    const int any_dead = __syncthreads_or(dead ? 1 : 0);
+    if (any_dead) return;
+    float* fold = reinterpret_cast<float*>(smem);
+    float* fm = fold;                                   // [warps][ROWS]
+    float* fl = fold + DECODE_WARPS * ROWS;             // [warps][ROWS]
+    float* fo = fold + 2 * DECODE_WARPS * ROWS;         // [warps][ROWS][DV]
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+            const int rr = mt * 16 + g + 8 * hf;
+            if (t == 0) {
+                fm[warp * ROWS + rr] = m_run[mt][hf];
+                fl[warp * ROWS + rr] = l_run[mt][hf];
+            }
+            float* dst = fo + (warp * ROWS + rr) * DV;
+#pragma unroll
+            for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int col = ES == 2 ? n * 8 + 2 * t + e : (2 * t + e) * (DV / 8) + n;
+                    dst[col] = acc[mt][n][2 * hf + e];
+                }
+        }
+    __syncthreads();
+
+    const float vmul = (PK == 2 && smode == 0) ? p.value_multiplier : 1.f;
+    const bool whole = nsplit == 1;
+    const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
+    for (int idx = tid; idx < ROWS * (DV / 4); idx += DECODE_THREADS) {
+        const int rr = idx / (DV / 4), c4 = idx - rr * (DV / 4);
+        const int flat = ct * ROWS + rr;
+        const int col = flat / G, gq = flat - col * G;
+        if (col >= count) continue;
+        float top = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < DECODE_WARPS; ++w) top = fmaxf(top, fm[w * ROWS + rr]);
+        const float sub = top == -INFINITY ? 0.f : top;
+        float l = 0.f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < DECODE_WARPS; ++w) {
+            const float f = ex2(fm[w * ROWS + rr] - sub);
+            l += fl[w * ROWS + rr] * f;
+            const float4 v = *reinterpret_cast<const float4*>(fo + (w * ROWS + rr) * DV + c4 * 4);
+            o.x += v.x * f, o.y += v.y * f, o.z += v.z * f, o.w += v.w * f;
+        }
+        o.x *= vmul, o.y *= vmul, o.z *= vmul, o.w *= vmul;
+        const int token = start + col, head = h * G + gq;
+        if (whole) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            char* dst = (char*)p.out + ((int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head + c4 * 4) * 2;
+            uint2 packed;
+            if (p.q_dtype == CRIT_B200_DTYPE_BF16) {
+                packed.x = pack2<true>(o.x * inv, o.y * inv), packed.y = pack2<true>(o.z * inv, o.w * inv);
+            } else {
+                packed.x = pack2<false>(o.x * inv, o.y * inv), packed.y = pack2<false>(o.z * inv, o.w * inv);
+            }
+            *reinterpret_cast<uint2*>(dst) = packed;
+            if (p.lse && c4 == 0) p.lse[(int64_t)token * p.q_heads + head] = l > 0.f ? top * LN2 + logf(l) : -INFINITY;
+        } else {
+            const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
+            const int64_t at = ((int64_t)prow * p.q_heads + head) * p.max_splits + split;
+            *reinterpret_cast<float4*>(p.workspace + at * DV + c4 * 4) = o;
+            if (c4 == 0) {
+                p.workspace[states * DV + at] = top;
+                p.workspace[states * (DV + 1) + at] = l;
+            }
+        }
+    }
+}
+
+}  // namespace crit_b200

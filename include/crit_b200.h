@@ -96,6 +96,8 @@ typedef struct crit_b200_slots_params {
 
 int crit_b200_slots(const crit_b200_slots_params* params, void* stream);
 
+#define CRIT_B200_ATTEND_NO_TMA 1   /* stage pages with cp.async even where the TMA path serves the geometry */
+
 /* -- split-K decode / speculative-verify attention ------------------------------------------------------------------
  * Replaces paged_kv_attention.attend (paged_kv_attention/__init__.py:396-576; kernels _kernels.py:263-478 and :558-604,
  * cuda_window.cu:284-1286) behind DeviceAttention._windows (inference/attention-state/code/device_attention.py:659-704).
@@ -119,13 +121,17 @@ typedef struct crit_b200_attend_params {
     const int64_t* firsts;       /* [R] */
     const int32_t* offsets;      /* [R] first partial row of each row, counted from offsets[0]; or NULL (r * columns) */
     float* workspace;            /* crit_b200_attend_plan's floats, or NULL when max_splits is 1 */
+    int32_t* status;             /* or NULL: a device word a kernel sets (never clears) when a bounded wait gave up */
     int64_t workspace_floats;
+    int64_t slots;               /* slots each page tensor stores ((pages + 1) * page): the bound of the TMA tensor maps;
+                                    0: unknown, pages are staged with cp.async */
     int64_t q_stride_token, q_stride_head, out_stride_token, out_stride_head, table_stride;
     int32_t n_rows, columns, partial_rows;
     int32_t q_heads, kv_heads, head_dim, value_dim, page;
     int32_t kind, page_dtype, q_dtype;
     int32_t chunk;               /* positions per split: a multiple of 16 */
     int32_t max_splits;          /* splits a partial row has room for: ceil(positions a row may reach / chunk) */
+    int32_t flags;               /* CRIT_B200_ATTEND_* */
     float scale, key_multiplier, value_multiplier;
 } crit_b200_attend_params;
 

@@ -180,6 +180,23 @@ def test_a_column_decodes_the_same_alone_and_in_a_window(pk, kind):
         assert torch.equal(wide, together[start:start + 8])
 
 
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "fp8", "fp8:row", "int8", "fp8:page"])
+@pytest.mark.parametrize("hq,hkv,d", [(32, 4, 128), (24, 4, 256), (40, 8, 128)])
+def test_tma_and_cp_async_staging_give_the_same_bits(pk, kind, hq, hkv, d):
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, hkv, d, d, 16, [130, 64, 1, 517, 1000], outliers=kind == "fp8:page")
+    rows, starts, firsts, counts = [0, 1, 2, 3, 4], [0, 5, 10, 15, 20], [125, 59, 0, 400, 990], [5, 5, 1, 3, 6]
+    q = queries(26, hq, d, 3, torch.float16 if kind == "fp16" else torch.bfloat16)
+    lse_a, lse_b = torch.empty(26, hq, device="cuda"), torch.empty(26, hq, device="cuda")
+    tma = cache.attend(q, rows, starts, firsts, 6, counts=counts, lse=lse_a, chunk=128)
+    plain = cache.attend(q, rows, starts, firsts, 6, counts=counts, lse=lse_b, chunk=128, staging="cp.async")
+    tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
+    assert torch.equal(tma[tokens], plain[tokens]) and torch.equal(lse_a[tokens], lse_b[tokens])
+    want, want_lse = cache.oracle(q, rows, starts, firsts, 6, counts=counts)
+    assert_attention_close(tma, lse_a, want, want_lse, tokens, rel=2.0 ** -7 if kind == "fp8:page" else 0.0)
+    assert pk.status() == 0
+
+
 def test_a_count_past_the_columns_reads_as_the_columns(pk):
     from helpers import Cache, queries
     cache = Cache("bf16", 2, 128, 128, 16, [300, 300], spare=8)
