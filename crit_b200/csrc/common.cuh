@@ -57,6 +57,13 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
                  : "r"(addr));
 }
 
+// The transpose of an 8x8 matrix of 16-bit values held one row per four lanes (two values a lane).
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+
 // D += A (16x16, row) * B (16x8, col), FP32 accumulate; BF16 selects the operand type.
 template <bool BF16>
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
@@ -95,6 +102,18 @@ __device__ __forceinline__ uint32_t s8x2_to_f16x2(uint32_t x) {
     __half2 h = *reinterpret_cast<__half2*>(&w);
     h = __hsub2(h, __floats2half2_rn(1152.f, 1152.f));
     return *reinterpret_cast<uint32_t*>(&h);
+}
+// Four code bytes of one word -> two FP16 pairs (bytes 0,1 and bytes 2,3), the halves split without a shift.
+template <bool INT8>
+__device__ __forceinline__ void code4_to_f16x2x2(uint32_t x, uint32_t& lo, uint32_t& hi) {
+    if constexpr (INT8) {
+        lo = s8x2_to_f16x2(x);
+        hi = s8x2_to_f16x2(x >> 16);
+    } else {
+        asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}"
+            : "=r"(lo), "=r"(hi)
+            : "r"(x));
+    }
 }
 template <bool INT8>
 __device__ __forceinline__ uint32_t code2_to_f16x2(uint32_t x) {

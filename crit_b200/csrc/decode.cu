@@ -143,20 +143,20 @@ struct Variant {
     int es;
 };
 
-template <int D, int DV, int PK, int MT, bool TMA>
+template <int D, int DV, int PK, int NT, bool TMA>
 static Variant variant() {
-    return Variant{decode_kernel<D, DV, PK, MT, TMA>, DecodeCfg<D, DV, PK, MT, TMA>::smem_bytes, TMA, PK < 2 ? 2 : 1};
+    return Variant{decode_kernel<D, DV, PK, NT, TMA>, DecodeCfg<D, DV, PK, NT, TMA>::smem_bytes, TMA, PK < 2 ? 2 : 1};
 }
 
-template <int PK, int MT, bool TMA>
+template <int PK, int NT, bool TMA>
 static int pick_width(int d, int dv, Variant* out) {
     if (d == 64 && dv == 64) {
-        if constexpr (!TMA) *out = variant<64, 64, PK, MT, false>();
+        if constexpr (!TMA) *out = variant<64, 64, PK, NT, false>();
         else return CRIT_B200_EUNSUPPORTED;
     } else if (d == 128 && dv == 128) {
-        *out = variant<128, 128, PK, MT, TMA>();
+        *out = variant<128, 128, PK, NT, TMA>();
     } else if (d == 256 && dv == 256) {
-        if constexpr (MT == 1) *out = variant<256, 256, PK, 1, TMA>();
+        if constexpr (NT <= 2) *out = variant<256, 256, PK, NT, TMA>();
         else return CRIT_B200_EUNSUPPORTED;
     } else {
         return CRIT_B200_EUNSUPPORTED;
@@ -171,16 +171,25 @@ static int page_class(int kind, int page_dtype) {
     return -1;
 }
 
-// Query rows a block's tile holds: 16, or 32 where a row's columns times the group's heads pass 16 and the value
-// accumulators of two row tiles still fit the registers.
-static int row_tiles(int rows, int dv) { return rows > 16 && dv <= 128 ? 2 : 1; }
+// 8-row tiles of query rows a block holds: as many as a row's columns times the group's heads need, up to 4 (32 rows),
+// 2 where the value accumulators of more would not fit the registers (256-wide values).
+static int row_tiles(int rows, int dv) {
+    const int most = dv <= 128 ? 4 : 2;
+    const int need = rows <= 8 ? 1 : (rows <= 16 ? 2 : 4);
+    return need < most ? need : most;
+}
 
-static int pick(int kind, int page_dtype, int d, int dv, int mt, bool tma, Variant* out) {
+template <int PK, bool TMA>
+static int pick_rows(int d, int dv, int nt, Variant* out) {
+    if (nt == 1) return pick_width<PK, 1, TMA>(d, dv, out);
+    if (nt == 2) return pick_width<PK, 2, TMA>(d, dv, out);
+    return pick_width<PK, 4, TMA>(d, dv, out);
+}
+
+static int pick(int kind, int page_dtype, int d, int dv, int nt, bool tma, Variant* out) {
     const int pk = page_class(kind, page_dtype);
     if (pk < 0) return CRIT_B200_EUNSUPPORTED;
-#define CRIT_PICK(PK)                                                                                  \
-    return tma ? (mt == 2 ? pick_width<PK, 2, true>(d, dv, out) : pick_width<PK, 1, true>(d, dv, out)) \
-               : (mt == 2 ? pick_width<PK, 2, false>(d, dv, out) : pick_width<PK, 1, false>(d, dv, out))
+#define CRIT_PICK(PK) return tma ? pick_rows<PK, true>(d, dv, nt, out) : pick_rows<PK, false>(d, dv, nt, out)
     switch (pk) {
         case 0: CRIT_PICK(0);
         case 1: CRIT_PICK(1);
@@ -277,7 +286,7 @@ static int check(const crit_b200_attend_params& p) {
 static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     const int G = p.q_heads / p.kv_heads;
     const int rows = p.columns * G;
-    const int mt = row_tiles(rows, p.value_dim);
+    const int nt = row_tiles(rows, p.value_dim);
     const int pk = page_class(p.kind, p.page_dtype);
     CUtensorMap kmap, vmap;
     memset(&kmap, 0, sizeof kmap);
@@ -285,14 +294,14 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     bool tma = tma_serves(p) && pk >= 0 && page_map(&kmap, p.key_pages, pk, p.head_dim, p.kv_heads, p.slots) &&
                page_map(&vmap, p.value_pages, pk, p.value_dim, p.kv_heads, p.slots);
     Variant v;
-    int e = pick(p.kind, p.page_dtype, p.head_dim, p.value_dim, mt, tma, &v);
+    int e = pick(p.kind, p.page_dtype, p.head_dim, p.value_dim, nt, tma, &v);
     if (e) return e;
     const int scb = scale_stage_bytes(p, tma);
     const int smem = v.smem(scb);
     // Set at every launch: the attribute belongs to the function on the current device, and a process may drive several.
     cudaError_t ce = cudaFuncSetAttribute((const void*)v.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (ce != cudaSuccess) return (int)ce;
-    const int ctiles = (rows + 16 * mt - 1) / (16 * mt);
+    const int ctiles = (rows + 8 * nt - 1) / (8 * nt);
     dim3 grid((unsigned)p.max_splits, (unsigned)(p.kv_heads * ctiles), (unsigned)p.n_rows);
     v.fn<<<grid, DECODE_THREADS, smem, s>>>(p, ctiles, scale_mode(p.kind), scb, kmap, vmap);
     CRIT_CHECK_LAUNCH();
@@ -327,9 +336,9 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_attend_plan(int3
     if (!out5 || q_heads < 1 || kv_heads < 1 || q_heads % kv_heads || columns < 1) return CRIT_B200_EINVAL;
     if (page < 16 || page % 16) return CRIT_B200_EUNSUPPORTED;
     const int rows = columns * (q_heads / kv_heads);
-    const int mt = row_tiles(rows, value_dim);
+    const int nt = row_tiles(rows, value_dim);
     Variant v;
-    int e = pick(kind, page_dtype, head_dim, value_dim, mt, false, &v);
+    int e = pick(kind, page_dtype, head_dim, value_dim, nt, false, &v);
     if (e) return e;
     const int smem = v.smem(128);
     int device = 0, sms = 0, per_sm = 0;
@@ -341,7 +350,7 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_attend_plan(int3
     cudaGetLastError();
     out5[0] = 1024;
     out5[1] = smem;
-    out5[2] = 16 * mt;
+    out5[2] = 8 * nt;
     out5[3] = per_sm;
     out5[4] = sms;
     return 0;

@@ -11,12 +11,19 @@
 //          with the 128-byte swizzle, from a 3-D tensor map over [slots][kv_heads][dim]) and bulk copies of the tile's
 //          scales; their bytes are counted on the stage's mbarrier, which the warp's lanes then wait on (bounded);
 //   false  every lane issues 16-byte cp.async copies (zero-filled past the row's last position) in commit groups.
-// Scores and outputs are m16n8k16 tensor-core products with FP32 accumulators; the online softmax lives in registers
-// (quad shuffles for the row maxima).  8-bit pages (E4M3, INT8) are converted to FP16 in registers on the way from
-// shared memory to the tensor cores: the head dimension is consumed in a permuted order (each thread reads 16
-// contiguous bytes of a key row) and the value columns are produced in a permuted order (each thread owns contiguous
-// output columns), which needs no transposing load.  The warps' states are folded through shared memory at the end;
-// a row that fits one split is written out directly, else the split's state goes to the workspace for the merge.
+// Scores and outputs are m16n8k16 tensor-core products with FP32 accumulators, with the POSITIONS on the instruction's
+// 16-row axis and the query rows on its 8-column axis: S^T[16 positions x 8 query rows] = K Q^T and
+// O^T[16 value columns x 8 query rows] += V^T P^T.  A decode step of a GQA group of up to 8 heads therefore fills the
+// tile exactly (no padding rows), a verify window takes NT = 2 or 4 such column tiles, and the keys and values, which
+// are the bytes streamed from HBM, are the A operands converted once per tile.  The probabilities cross from the
+// accumulator layout to the B-operand layout with movmatrix (an 8x8 transpose inside the warp).  The online softmax
+// lives in registers (shuffles over the lanes that share a query row).  8-bit pages (E4M3, INT8) are converted to
+// FP16 in registers on the way from shared memory to the tensor cores: the head dimension is consumed in a permuted
+// order (each thread reads 16 contiguous bytes of a key row) and the value columns are produced in a permuted order
+// (each thread owns contiguous output columns), which needs no transposing load.  Where a tile is small (8-bit pages
+// of heads up to 128 wide) an iteration takes two tiles (32 positions): two independent accumulator chains, and one
+// softmax update for both.  The warps' states are folded through shared memory at the end; a row that fits one split
+// is written out directly, else the split's state goes to the workspace for the merge.
 //
 // HBM traffic per block: its split's keys and values once (the algorithmic bytes), the queries, one partial state.
 // Reference: paged_kv_attention/_kernels.py:263-478 (_partition, _window_kernel), cuda_window.cu:284-1065 (cw_tile).
@@ -30,20 +37,24 @@ namespace crit_b200 {
 
 constexpr int DECODE_WARPS = 4;
 constexpr int DECODE_THREADS = DECODE_WARPS * 32;
+constexpr float LAZY = 8.f;
 
 // Page element classes (PK): 0 bf16, 1 fp16, 2 E4M3 bytes, 3 INT8 bytes.
-template <int D, int DV, int PK, int MT, bool TMA>
+// NT: 8-row tiles of query rows a block holds (1, 2 or 4).
+template <int D, int DV, int PK, int NT, bool TMA>
 struct DecodeCfg {
     static constexpr int ES = PK < 2 ? 2 : 1;
     static constexpr bool BF16 = PK == 0;
     static constexpr int KROW = D * ES, VROW = DV * ES;
     static constexpr int KTILE = 16 * KROW, VTILE = 16 * VROW;
     static constexpr int TILES = KTILE + VTILE;
-    static constexpr int STAGES = TILES <= 4096 ? 4 : 3;
-    static constexpr int QROW = D * 2 + (ES == 1 ? 16 : 0);
-    static constexpr int QBYTES = 16 * MT * QROW;
-    static constexpr int FOLD = DECODE_WARPS * 16 * MT * (DV + 2) * 4;
-    static constexpr bool QREG = MT == 1 && D <= 128;
+    static constexpr int TPI = TILES <= 4096 ? 2 : 1;          // tiles an iteration consumes
+    static constexpr int STAGES = TPI == 2 ? 4 : 3;
+    static constexpr int ROWS = 8 * NT;
+    static constexpr int QROW = D * 2 + 16;                    // padded: rows 8 apart fall in different banks
+    static constexpr int QBYTES = ROWS * QROW;
+    static constexpr int FOLD = DECODE_WARPS * ROWS * (DV + 2) * 4;
+    static constexpr bool QREG = NT * D <= 256;                // the query fragments stay in registers
     // dynamic shared memory: [1 KB of alignment slack][tiles | scales (or the fold)][queries][mbarriers]
     __host__ __device__ static constexpr int ring_bytes(int scb) { return DECODE_WARPS * STAGES * (TILES + scb); }
     __host__ __device__ static constexpr int region(int scb) { return ((ring_bytes(scb) > FOLD ? ring_bytes(scb) : FOLD) + 127) / 128 * 128; }
@@ -81,14 +92,15 @@ __device__ __forceinline__ int tile_off(int row, int c) {
     }
 }
 
-template <int D, int DV, int PK, int MT, bool TMA>
+template <int D, int DV, int PK, int NT, bool TMA>
 __global__ void __launch_bounds__(DECODE_THREADS)
 decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode, const int scb,
               const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
-    using C = DecodeCfg<D, DV, PK, MT, TMA>;
+    using C = DecodeCfg<D, DV, PK, NT, TMA>;
     constexpr bool BF16 = C::BF16;
     constexpr int ES = C::ES;
-    constexpr int ROWS = 16 * MT;
+    constexpr int ROWS = C::ROWS;
+    constexpr int TPI = C::TPI;
     constexpr int KC = C::KROW / 16, VC = C::VROW / 16;      // 16-byte chunks of a key row, of a value row
     extern __shared__ unsigned char smem_raw[];
 
@@ -127,7 +139,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
         }
     }
 
-    // -- the query tile into shared memory ---------------------------------------------------------------------------
+    // -- the query tile into shared memory: ROWS rows of D 16-bit values (FP16 where the pages are 8-bit) -------------
     {
         constexpr int CPR = D / 8;
         for (int idx = tid; idx < ROWS * CPR; idx += DECODE_THREADS) {
@@ -140,64 +152,65 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
                                   ((int64_t)(start + col) * p.q_stride_token + (int64_t)(h * G + gq) * p.q_stride_head + c * 8) * 2;
                 v = *reinterpret_cast<const uint4*>(src);
             }
-            if constexpr (ES == 2) {
-                *reinterpret_cast<uint4*>(qs + rr * C::QROW + swz16(c, rr) * 16) = v;
-            } else {
-                if (p.q_dtype == CRIT_B200_DTYPE_BF16) {
-                    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            if (ES == 1 && p.q_dtype == CRIT_B200_DTYPE_BF16) {
+                uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&w[i]);
-                        float2 f = __bfloat1622float2(b);
-                        f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
-                        f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
-                        __half2 hh = __floats2half2_rn(f.x, f.y);
-                        w[i] = *reinterpret_cast<uint32_t*>(&hh);
-                    }
-                    v = make_uint4(w[0], w[1], w[2], w[3]);
+                for (int i = 0; i < 4; ++i) {
+                    __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&w[i]);
+                    float2 f = __bfloat1622float2(b);
+                    f.x = fminf(fmaxf(f.x, -65504.f), 65504.f);
+                    f.y = fminf(fmaxf(f.y, -65504.f), 65504.f);
+                    __half2 hh = __floats2half2_rn(f.x, f.y);
+                    w[i] = *reinterpret_cast<uint32_t*>(&hh);
                 }
-                *reinterpret_cast<uint4*>(qs + rr * C::QROW + c * 16) = v;
+                v = make_uint4(w[0], w[1], w[2], w[3]);
             }
+            *reinterpret_cast<uint4*>(qs + rr * C::QROW + c * 16) = v;
         }
     }
     __syncthreads();
 
-    // The last position each of this thread's query rows sees (-1: a padding row).
-    int64_t lastpos[MT][2];
+    // The last position each of this thread's query rows sees (-1: a padding row).  A thread's query rows are
+    // nt * 8 + 2 * t + {0, 1}.
+    int lastpos[NT][2];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-            const int flat = ct * ROWS + mt * 16 + g + 8 * hf;
+        for (int e = 0; e < 2; ++e) {
+            const int flat = ct * ROWS + nt * 8 + 2 * t + e;
             const int col = flat / G;
-            lastpos[mt][hf] = col < count ? first + col : -1;
+            lastpos[nt][e] = col < count ? (int)(first + col) : -1;
         }
 
-    uint32_t qa[C::QREG ? D / 16 : 1][4];
+    // The B operand of the scores: Q^T, k16 x n8 per step; b0 holds k = 2t, 2t+1 and b1 k = 2t+8, 2t+9 of query row g.
+    auto q_frag = [&](int nt, int ks, uint32_t& b0, uint32_t& b1) {
+        const unsigned char* row = qs + (nt * 8 + g) * C::QROW;
+        if constexpr (ES == 1) {
+            const uint2 v = *reinterpret_cast<const uint2*>(row + (t * (D / 4) + 4 * ks) * 2);
+            b0 = v.x, b1 = v.y;
+        } else {
+            b0 = *reinterpret_cast<const uint32_t*>(row + (16 * ks + 2 * t) * 2);
+            b1 = *reinterpret_cast<const uint32_t*>(row + (16 * ks + 8 + 2 * t) * 2);
+        }
+    };
+    uint32_t qb[C::QREG ? NT : 1][C::QREG ? D / 16 : 1][2];
     if constexpr (C::QREG) {
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            if constexpr (ES == 2) {
-                const int j = lane >> 3, row = (lane & 7) + 8 * (j & 1), chunk = 2 * ks + (j >> 1);
-                ldmatrix_x4(qa[ks], smem_addr(qs + row * C::QROW + swz16(chunk, row) * 16));
-            } else {
-                const uint2 lo = *reinterpret_cast<const uint2*>(qs + g * C::QROW + (t * (D / 4) + 4 * ks) * 2);
-                const uint2 hi = *reinterpret_cast<const uint2*>(qs + (g + 8) * C::QROW + (t * (D / 4) + 4 * ks) * 2);
-                qa[ks][0] = lo.x, qa[ks][1] = hi.x, qa[ks][2] = lo.y, qa[ks][3] = hi.y;
-            }
-        }
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) q_frag(nt, ks, qb[nt][ks][0], qb[nt][ks][1]);
     }
 
-    float acc[MT][DV / 8][4];
-    float m_run[MT][2], l_run[MT][2];
+    float acc[DV / 16][NT][4];
+    float m_run[NT][2], l_run[NT][2];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt) {
+    for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
-        for (int n = 0; n < DV / 8; ++n)
+        for (int mt = 0; mt < DV / 16; ++mt)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) acc[mt][n][i] = 0.f;
-        m_run[mt][0] = m_run[mt][1] = -INFINITY;
-        l_run[mt][0] = l_run[mt][1] = 0.f;
+            for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.f;
+        m_run[nt][0] = m_run[nt][1] = -INFINITY;
+        l_run[nt][0] = l_run[nt][1] = 0.f;
     }
 
     const float kmul = (PK == 2 && smode == 0) ? p.key_multiplier : 1.f;
@@ -211,12 +224,14 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     const char* vbase = (const char*)p.value_pages + (int64_t)h * C::VROW;
     const int64_t krow_stride = (int64_t)p.kv_heads * C::KROW, vrow_stride = (int64_t)p.kv_heads * C::VROW;
     const uint32_t scale_bytes = smode == 2 ? (uint32_t)p.kv_heads * 4u : (smode == 1 ? (uint32_t)p.kv_heads * 64u : 0u);
+    const uint32_t tiles_per_page = (uint32_t)p.page >> 4;
+    const int Lr = (int)L;
 
     auto issue = [&](int i) {
         if (i < mine) {
-            const int64_t pos0 = (int64_t)(tile0 + warp + i * DECODE_WARPS) << 4;
-            const int pidx = (int)(pos0 / p.page);
-            const int off = (int)(pos0 - (int64_t)pidx * p.page);
+            const uint32_t tile = (uint32_t)(tile0 + warp + i * DECODE_WARPS);
+            const uint32_t pidx = tile / tiles_per_page;
+            const int off = (int)(tile - pidx * tiles_per_page) << 4;
             const int pg = table[pidx];
             const int64_t slot0 = (int64_t)pg * p.page + off;
             const int stage = i % C::STAGES;
@@ -238,7 +253,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
                     }
                 }
             } else {
-                const int live = (int)(L - pos0 < 16 ? L - pos0 : 16);
+                const int live = Lr - (int)(tile << 4);          // rows past it are zero-filled
 #pragma unroll
                 for (int u = 0; u < 16 * KC / 32; ++u) {
                     const int id = lane + 32 * u, row = id / KC, c = id - row * KC;
@@ -266,224 +281,212 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     };
 
 #pragma unroll
-    for (int i = 0; i < C::STAGES - 1; ++i) issue(i);
+    for (int i = 0; i < C::STAGES - TPI; ++i) issue(i);
 
     bool dead = false;
-    for (int i = 0; i < mine; ++i) {
-        issue(i + C::STAGES - 1);
-        const int stage = i % C::STAGES;
+    const int first32 = first > 0x7fffffffLL ? 0x7fffffff : (int)first;
+    for (int i = 0; i < mine; i += TPI) {
+#pragma unroll
+        for (int u = 0; u < TPI; ++u) issue(i + C::STAGES - TPI + u);
+        const int have = mine - i < TPI ? mine - i : TPI;          // tiles of this iteration (warp-uniform)
         if constexpr (TMA) {
-            if (!__all_sync(0xffffffffu, mbar_wait(bars + stage * 8, (uint32_t)(i / C::STAGES) & 1u))) {
-                dead = true;                // the copy never landed: record it and leave, nothing is written
+            bool ok = true;
+#pragma unroll
+            for (int u = 0; u < TPI; ++u)
+                if (u < have) ok &= mbar_wait(bars + ((i + u) % C::STAGES) * 8, (uint32_t)((i + u) / C::STAGES) & 1u);
+            if (!__all_sync(0xffffffffu, ok)) {
+                dead = true;                // a copy never landed: record it and leave, nothing is written
                 break;
             }
         } else {
-            cp_async_wait<C::STAGES - 1>();
+            cp_async_wait<C::STAGES - TPI>();
             __syncwarp();
         }
-        const int64_t pos0 = (int64_t)(tile0 + warp + i * DECODE_WARPS) << 4;
-        unsigned char* kst = tiles + stage * C::TILES;
-        unsigned char* vst = kst + C::KTILE;
-        const float* scales = reinterpret_cast<const float*>(scales_ring + stage * scb);
-        const bool masked = pos0 + 16 > first;
-        if constexpr (TMA) {
-            // A tiled load brings all 16 rows: the value rows past the row's last position become zeros, as the
-            // zero-filling cp.async leaves them (a probability of 0 times a stale NaN would poison the output).
-            const int live = (int)(L - pos0 < 16 ? L - pos0 : 16);
-            if (live < 16) {
-                for (int id = lane; id < 16 * VC; id += 32) {
-                    const int row = id / VC, c = id - row * VC;
-                    if (row >= live)
-                        *reinterpret_cast<uint4*>(vst + tile_off<true, C::VROW, ES, DV, true>(row, c)) = make_uint4(0, 0, 0, 0);
-                }
-                __syncwarp();
-            }
-        }
 
-        // scores: S[16*MT x 16] = Q K^T
-        float s[MT][2][4];
+        float s[TPI][NT][4];
+        float ksc[TPI][2], vsc[TPI][2];
+        int pos0[TPI];
+        bool masked = false;
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+        for (int u = 0; u < TPI; ++u) {
+            pos0[u] = (tile0 + warp + (i + u) * DECODE_WARPS) << 4;
+            ksc[u][0] = ksc[u][1] = vsc[u][0] = vsc[u][1] = 1.f;
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) s[mt][n][e] = 0.f;
-
-        uint32_t kw[2][ES == 1 ? D / 16 : 1];
-        if constexpr (ES == 1) {
-#pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                const int row = g + 8 * n;
-#pragma unroll
-                for (int qd = 0; qd < D / 64; ++qd) {
-                    const int c = t * (D / 64) + qd;
-                    const uint4 v = *reinterpret_cast<const uint4*>(kst + tile_off<TMA, C::KROW, ES, D, false>(row, c));
-                    kw[n][qd * 4 + 0] = v.x, kw[n][qd * 4 + 1] = v.y, kw[n][qd * 4 + 2] = v.z, kw[n][qd * 4 + 3] = v.w;
-                }
-            }
-        }
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
-            uint32_t kb[4];
-            if constexpr (ES == 2) {
-                const int j = lane >> 3, tok = (lane & 7) + 8 * (j >> 1), chunk = 2 * ks + (j & 1);
-                ldmatrix_x4(kb, smem_addr(kst + tile_off<TMA, C::KROW, ES, D, false>(tok, chunk)));
-            } else {
-                kb[0] = code2_to_f16x2<PK == 3>(kw[0][ks]);
-                kb[1] = code2_to_f16x2<PK == 3>(kw[0][ks] >> 16);
-                kb[2] = code2_to_f16x2<PK == 3>(kw[1][ks]);
-                kb[3] = code2_to_f16x2<PK == 3>(kw[1][ks] >> 16);
-            }
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                uint32_t a[4];
-                if constexpr (C::QREG) {
-                    a[0] = qa[ks][0], a[1] = qa[ks][1], a[2] = qa[ks][2], a[3] = qa[ks][3];
-                } else if constexpr (ES == 2) {
-                    const int j = lane >> 3, row = mt * 16 + (lane & 7) + 8 * (j & 1), chunk = 2 * ks + (j >> 1);
-                    ldmatrix_x4(a, smem_addr(qs + row * C::QROW + swz16(chunk, row) * 16));
-                } else {
-                    const int row = mt * 16 + g;
-                    const uint2 lo = *reinterpret_cast<const uint2*>(qs + row * C::QROW + (t * (D / 4) + 4 * ks) * 2);
-                    const uint2 hi = *reinterpret_cast<const uint2*>(qs + (row + 8) * C::QROW + (t * (D / 4) + 4 * ks) * 2);
-                    a[0] = lo.x, a[1] = hi.x, a[2] = lo.y, a[3] = hi.y;
-                }
-                mma16816<BF16>(s[mt][0], a, kb[0], kb[1]);
-                mma16816<BF16>(s[mt][1], a, kb[2], kb[3]);
-            }
-        }
-
-        // the tile's scales: ksc/vsc[2 * n + e] belong to position n * 8 + 2 * t + e of the tile
-        float ksc[4] = {1.f, 1.f, 1.f, 1.f}, vsc[4] = {1.f, 1.f, 1.f, 1.f};
-        if (PK >= 2 && smode) {
+                for (int e = 0; e < 4; ++e) s[u][nt][e] = u < have ? 0.f : -INFINITY;
+            if (u >= have) continue;
+            masked |= pos0[u] + 16 > first32;
+            const int stage = (i + u) % C::STAGES;
+            unsigned char* kst = tiles + stage * C::TILES;
+            const float* scales = reinterpret_cast<const float*>(scales_ring + stage * scb);
             if constexpr (TMA) {
-                const float* vscales = scales + (scb >> 3);
-                if (smode == 2) {
-                    const float a = scales[h], b = vscales[h];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) ksc[e] = a, vsc[e] = b;
-                } else {
-#pragma unroll
-                    for (int n = 0; n < 2; ++n)
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int tok = n * 8 + 2 * t + e;
-                            ksc[2 * n + e] = scales[tok * p.kv_heads + h];
-                            vsc[2 * n + e] = vscales[tok * p.kv_heads + h];
-                        }
+                // A tiled load brings all 16 rows: the value rows past the row's last position become zeros, as the
+                // zero-filling cp.async leaves them (a probability of 0 times a stale NaN would poison the output).
+                const int live = Lr - pos0[u];
+                if (live < 16) {
+                    unsigned char* vst = kst + C::KTILE;
+                    for (int id = lane; id < 16 * VC; id += 32) {
+                        const int row = id / VC, c = id - row * VC;
+                        if (row >= live)
+                            *reinterpret_cast<uint4*>(vst + tile_off<true, C::VROW, ES, DV, true>(row, c)) = make_uint4(0, 0, 0, 0);
+                    }
+                    __syncwarp();
                 }
-            } else {
+            }
+            // the tile's scales: ksc/vsc[u][hf] belong to position g + 8 * hf of the tile
+            if (PK >= 2 && smode) {
+                if constexpr (TMA) {
+                    const float* vscales = scales + (scb >> 3);
+                    if (smode == 2) {
+                        ksc[u][0] = ksc[u][1] = scales[h];
+                        vsc[u][0] = vsc[u][1] = vscales[h];
+                    } else {
+                        ksc[u][0] = scales[g * p.kv_heads + h], ksc[u][1] = scales[(g + 8) * p.kv_heads + h];
+                        vsc[u][0] = vscales[g * p.kv_heads + h], vsc[u][1] = vscales[(g + 8) * p.kv_heads + h];
+                    }
+                } else {
+                    ksc[u][0] = scales[g], ksc[u][1] = scales[g + 8];
+                    vsc[u][0] = scales[16 + g], vsc[u][1] = scales[24 + g];
+                }
+            }
+
+            // scores: S^T[16 positions x 8*NT query rows] = K Q^T
+            uint32_t kw[2][ES == 1 ? D / 16 : 1];
+            if constexpr (ES == 1) {
 #pragma unroll
                 for (int n = 0; n < 2; ++n) {
-                    const float2 a = *reinterpret_cast<const float2*>(scales + n * 8 + 2 * t);
-                    const float2 b = *reinterpret_cast<const float2*>(scales + 16 + n * 8 + 2 * t);
-                    ksc[2 * n] = a.x, ksc[2 * n + 1] = a.y, vsc[2 * n] = b.x, vsc[2 * n + 1] = b.y;
+                    const int row = g + 8 * n;
+#pragma unroll
+                    for (int qd = 0; qd < D / 64; ++qd) {
+                        const int c = t * (D / 64) + qd;
+                        const uint4 v = *reinterpret_cast<const uint4*>(kst + tile_off<TMA, C::KROW, ES, D, false>(row, c));
+                        kw[n][qd * 4 + 0] = v.x, kw[n][qd * 4 + 1] = v.y, kw[n][qd * 4 + 2] = v.z, kw[n][qd * 4 + 3] = v.w;
+                    }
+                }
+            }
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t a[4];
+                if constexpr (ES == 2) {
+                    const int j = lane >> 3, row = (lane & 7) + 8 * (j & 1), chunk = 2 * ks + (j >> 1);
+                    ldmatrix_x4(a, smem_addr(kst + tile_off<TMA, C::KROW, ES, D, false>(row, chunk)));
+                } else {
+                    code4_to_f16x2x2<PK == 3>(kw[0][ks], a[0], a[2]);
+                    code4_to_f16x2x2<PK == 3>(kw[1][ks], a[1], a[3]);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    uint32_t b0, b1;
+                    if constexpr (C::QREG) b0 = qb[nt][ks][0], b1 = qb[nt][ks][1];
+                    else q_frag(nt, ks, b0, b1);
+                    mma16816<BF16>(s[u][nt], a, b0, b1);
                 }
             }
         }
 
-        // scale, mask, online softmax (base 2)
-        uint32_t pa[MT][4];
+        // scale, mask, online softmax (base 2) over the iteration's positions
+        uint32_t pb[TPI][NT][2];
         bool rescale = false;
-        float alpha[MT][2];
+        float alpha[NT][2];
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
+        for (int nt = 0; nt < NT; ++nt) {
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int u = 0; u < TPI; ++u)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    float x = s[mt][n][e] * (sl2 * ksc[2 * n + (e & 1)]);
-                    if (masked) {
-                        const int64_t pos = pos0 + n * 8 + 2 * t + (e & 1);
-                        if (pos > lastpos[mt][e >> 1]) x = -INFINITY;
-                    }
-                    s[mt][n][e] = x;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], x);
+                    float x = s[u][nt][e] * (sl2 * ksc[u][e >> 1]);
+                    if (masked && pos0[u] + g + 8 * (e >> 1) > lastpos[nt][e & 1]) x = -INFINITY;
+                    s[u][nt][e] = x;
+                    mx[e & 1] = fmaxf(mx[e & 1], x);
                 }
 #pragma unroll
-            for (int hf = 0; hf < 2; ++hf) {
-                mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 1));
-                mx[hf] = fmaxf(mx[hf], __shfl_xor_sync(0xffffffffu, mx[hf], 2));
-                const float top = fmaxf(m_run[mt][hf], mx[hf]);
+            for (int j = 0; j < 2; ++j) {
+                mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 4));
+                mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 8));
+                mx[j] = fmaxf(mx[j], __shfl_xor_sync(0xffffffffu, mx[j], 16));
+                // The running maximum moves only when the iteration's passes it by more than LAZY (2^8 in the
+                // probabilities, well inside FP16 and FP32): most iterations then rescale nothing.
+                const bool moved = mx[j] > m_run[nt][j] + LAZY || m_run[nt][j] == -INFINITY;
+                const float top = moved ? mx[j] : m_run[nt][j];
                 const float sub = top == -INFINITY ? 0.f : top;
-                alpha[mt][hf] = ex2(m_run[mt][hf] - sub);
-                rescale |= top != m_run[mt][hf];
-                m_run[mt][hf] = top;
-                mx[hf] = sub;
+                alpha[nt][j] = moved ? ex2(m_run[nt][j] - sub) : 1.f;
+                rescale |= moved && top != m_run[nt][j];
+                m_run[nt][j] = top;
+                mx[j] = sub;
             }
             float sum[2] = {0.f, 0.f};
-            float pr[2][4];
 #pragma unroll
-            for (int n = 0; n < 2; ++n)
+            for (int u = 0; u < TPI; ++u) {
+                float pr[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = ex2(s[mt][n][e] - mx[e >> 1]);
-                    sum[e >> 1] += pv;
-                    float scaled = pv * vsc[2 * n + (e & 1)];
-                    if (masked && s[mt][n][e] == -INFINITY) scaled = 0.f;     // a stale scale past the row's end
-                    pr[n][e] = scaled;
+                    const float pv = ex2(s[u][nt][e] - mx[e & 1]);
+                    sum[e & 1] += pv;
+                    float scaled = pv * vsc[u][e >> 1];
+                    if (masked && s[u][nt][e] == -INFINITY) scaled = 0.f;     // a stale scale past the row's end
+                    pr[e] = scaled;
                 }
-            l_run[mt][0] = l_run[mt][0] * alpha[mt][0] + sum[0];
-            l_run[mt][1] = l_run[mt][1] * alpha[mt][1] + sum[1];
-            pa[mt][0] = pack2<BF16>(pr[0][0], pr[0][1]);
-            pa[mt][1] = pack2<BF16>(pr[0][2], pr[0][3]);
-            pa[mt][2] = pack2<BF16>(pr[1][0], pr[1][1]);
-            pa[mt][3] = pack2<BF16>(pr[1][2], pr[1][3]);
+                // accumulator layout [position g (+8)][query rows 2t, 2t+1] -> B operand [positions 2t, 2t+1 (+8)][row g]
+                pb[u][nt][0] = movmatrix_trans(pack2<BF16>(pr[0], pr[1]));
+                pb[u][nt][1] = movmatrix_trans(pack2<BF16>(pr[2], pr[3]));
+            }
+            l_run[nt][0] = l_run[nt][0] * alpha[nt][0] + sum[0];
+            l_run[nt][1] = l_run[nt][1] * alpha[nt][1] + sum[1];
         }
         if (__any_sync(0xffffffffu, rescale)) {
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+            for (int mt = 0; mt < DV / 16; ++mt)
 #pragma unroll
-                for (int n = 0; n < DV / 8; ++n) {
-                    acc[mt][n][0] *= alpha[mt][0], acc[mt][n][1] *= alpha[mt][0];
-                    acc[mt][n][2] *= alpha[mt][1], acc[mt][n][3] *= alpha[mt][1];
+                for (int nt = 0; nt < NT; ++nt) {
+                    acc[mt][nt][0] *= alpha[nt][0], acc[mt][nt][1] *= alpha[nt][1];
+                    acc[mt][nt][2] *= alpha[nt][0], acc[mt][nt][3] *= alpha[nt][1];
                 }
         }
 
-        // outputs: O[16*MT x DV] += P V
-        if constexpr (ES == 2) {
+        // outputs: O^T[DV value columns x 8*NT query rows] += V^T P^T
 #pragma unroll
-            for (int np = 0; np < DV / 16; ++np) {
-                uint32_t vb[4];
-                const int j = lane >> 3, tok = (lane & 7) + 8 * (j & 1), chunk = 2 * np + (j >> 1);
-                ldmatrix_x4_trans(vb, smem_addr(vst + tile_off<TMA, C::VROW, ES, DV, true>(tok, chunk)));
+        for (int u = 0; u < TPI; ++u) {
+            if (u >= have) continue;
+            unsigned char* vst = tiles + ((i + u) % C::STAGES) * C::TILES + C::KTILE;
+            if constexpr (ES == 2) {
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    mma16816<BF16>(acc[mt][2 * np], pa[mt], vb[0], vb[1]);
-                    mma16816<BF16>(acc[mt][2 * np + 1], pa[mt], vb[2], vb[3]);
+                for (int mt = 0; mt < DV / 16; ++mt) {
+                    uint32_t a[4];
+                    const int j = lane >> 3, tok = (lane & 7) + 8 * (j >> 1), chunk = 2 * mt + (j & 1);
+                    ldmatrix_x4_trans(a, smem_addr(vst + tile_off<TMA, C::VROW, ES, DV, true>(tok, chunk)));
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) mma16816<BF16>(acc[mt][nt], a, pb[u][nt][0], pb[u][nt][1]);
                 }
-            }
-        } else {
-            constexpr int VW = DV / 32;            // 32-bit words of a value row this thread owns
-            uint32_t vw[4][VW];
+            } else {
+                constexpr int VW = DV / 32;            // 32-bit words of a value row this thread owns
+                uint32_t vw[4][VW];
 #pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-                const int row = 2 * t + (q4 & 1) + 8 * (q4 >> 1);
-                if constexpr (DV == 64) {
-                    const uint2 v = *reinterpret_cast<const uint2*>(vst + tile_off<false, C::VROW, ES, DV, true>(row, g >> 1) + (g & 1) * 8);
-                    vw[q4][0] = v.x, vw[q4][1] = v.y;
-                } else {
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int row = 2 * t + (q4 & 1) + 8 * (q4 >> 1);
+                    if constexpr (DV == 64) {
+                        const uint2 v = *reinterpret_cast<const uint2*>(vst + tile_off<false, C::VROW, ES, DV, true>(row, g >> 1) + (g & 1) * 8);
+                        vw[q4][0] = v.x, vw[q4][1] = v.y;
+                    } else {
 #pragma unroll
-                    for (int qd = 0; qd < DV / 128; ++qd) {
-                        const int c = g * (DV / 128) + qd;
-                        const uint4 v = *reinterpret_cast<const uint4*>(vst + tile_off<TMA, C::VROW, ES, DV, true>(row, c));
-                        vw[q4][qd * 4 + 0] = v.x, vw[q4][qd * 4 + 1] = v.y, vw[q4][qd * 4 + 2] = v.z, vw[q4][qd * 4 + 3] = v.w;
+                        for (int qd = 0; qd < DV / 128; ++qd) {
+                            const int c = g * (DV / 128) + qd;
+                            const uint4 v = *reinterpret_cast<const uint4*>(vst + tile_off<TMA, C::VROW, ES, DV, true>(row, c));
+                            vw[q4][qd * 4 + 0] = v.x, vw[q4][qd * 4 + 1] = v.y, vw[q4][qd * 4 + 2] = v.z, vw[q4][qd * 4 + 3] = v.w;
+                        }
                     }
                 }
-            }
 #pragma unroll
-            for (int np = 0; np < DV / 16; ++np) {
-                const int w = np >> 1;
-                const uint32_t sel = (np & 1) ? 0x7362u : 0x5140u;
-                const uint32_t x01 = __byte_perm(vw[0][w], vw[1][w], sel);
-                const uint32_t x23 = __byte_perm(vw[2][w], vw[3][w], sel);
-                const uint32_t b00 = code2_to_f16x2<PK == 3>(x01), b01 = code2_to_f16x2<PK == 3>(x23);
-                const uint32_t b10 = code2_to_f16x2<PK == 3>(x01 >> 16), b11 = code2_to_f16x2<PK == 3>(x23 >> 16);
+                for (int mt = 0; mt < DV / 16; ++mt) {
+                    // bytes 2*mt and 2*mt+1 of this thread's value bytes are rows g and g+8 of the m-tile
+                    const int w = mt >> 1;
+                    const uint32_t sel = (mt & 1) ? 0x7362u : 0x5140u;
+                    uint32_t a[4];
+                    code4_to_f16x2x2<PK == 3>(__byte_perm(vw[0][w], vw[1][w], sel), a[0], a[1]);
+                    code4_to_f16x2x2<PK == 3>(__byte_perm(vw[2][w], vw[3][w], sel), a[2], a[3]);
 #pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    mma16816<BF16>(acc[mt][2 * np], pa[mt], b00, b01);
-                    mma16816<BF16>(acc[mt][2 * np + 1], pa[mt], b10, b11);
+                    for (int nt = 0; nt < NT; ++nt) mma16816<BF16>(acc[mt][nt], a, pb[u][nt][0], pb[u][nt][1]);
                 }
             }
         }
@@ -502,11 +505,12 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
 
     // -- fold the four warps' states ---------------------------------------------------------------------------------
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-            l_run[mt][hf] += __shfl_xor_sync(0xffffffffu, l_run[mt][hf], 1);
-            l_run[mt][hf] += __shfl_xor_sync(0xffffffffu, l_run[mt][hf], 2);
+        for (int j = 0; j < 2; ++j) {
+            l_run[nt][j] += __shfl_xor_sync(0xffffffffu, l_run[nt][j], 4);
+            l_run[nt][j] += __shfl_xor_sync(0xffffffffu, l_run[nt][j], 8);
+            l_run[nt][j] += __shfl_xor_sync(0xffffffffu, l_run[nt][j], 16);
         }
     const int any_dead = __syncthreads_or(dead ? 1 : 0);
     if (any_dead) return;
@@ -515,21 +519,21 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     float* fl = fold + DECODE_WARPS * ROWS;             // [warps][ROWS]
     float* fo = fold + 2 * DECODE_WARPS * ROWS;         // [warps][ROWS][DV]
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-            const int rr = mt * 16 + g + 8 * hf;
-            if (t == 0) {
-                fm[warp * ROWS + rr] = m_run[mt][hf];
-                fl[warp * ROWS + rr] = l_run[mt][hf];
+        for (int j = 0; j < 2; ++j) {
+            const int rr = nt * 8 + 2 * t + j;
+            if (g == 0) {
+                fm[warp * ROWS + rr] = m_run[nt][j];
+                fl[warp * ROWS + rr] = l_run[nt][j];
             }
             float* dst = fo + (warp * ROWS + rr) * DV;
 #pragma unroll
-            for (int n = 0; n < DV / 8; ++n)
+            for (int mt = 0; mt < DV / 16; ++mt)
 #pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int col = ES == 2 ? n * 8 + 2 * t + e : (2 * t + e) * (DV / 8) + n;
-                    dst[col] = acc[mt][n][2 * hf + e];
+                for (int hf = 0; hf < 2; ++hf) {
+                    const int col = ES == 2 ? mt * 16 + g + 8 * hf : g * (DV / 8) + 2 * mt + hf;
+                    dst[col] = acc[mt][nt][2 * hf + j];
                 }
         }
     __syncthreads();
