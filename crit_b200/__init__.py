@@ -289,8 +289,9 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     chunk: positions per split (default chunk_for()); partitions: the most splits a partial row may take (the
     workspace's, see partitions()).  piece, fused, vsplit, tile, num_warps, num_stages, maxnreg, flash and ramp are
     accepted and change nothing (one launch shape per geometry).  parents, blocks, fresh, sinks, sliding and derive
-    are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: None (TMA tiled loads
-    where the geometry allows them: heads of 128 or 256 values, else cp.async) or "cp.async" (never TMA; the same bits)."""
+    are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
+    None (TMA tiled loads for 16-bit pages of 128- or 256-wide heads, cp.async otherwise: what measured faster), "tma"
+    (TMA wherever the geometry allows it) or "cp.async" (never TMA); the same bits either way."""
     _refuse(parents=parents, blocks=blocks, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
@@ -344,7 +345,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     p.slots = key_pages.numel() // (hkv * d)
     if staging not in (None, "tma", "cp.async"):
         raise ValueError("staging is None, tma or cp.async")
-    p.flags = 1 if staging == "cp.async" else 0
+    p.flags = {None: 0, "cp.async": 1, "tma": 2}[staging]
     p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])

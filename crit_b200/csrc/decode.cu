@@ -207,6 +207,7 @@ static int scale_mode(int kind) {
 // copies can take (a multiple of 16 bytes, 16-byte aligned, up to 1 KB a tile).
 static bool tma_serves(const crit_b200_attend_params& p) {
     if (p.flags & CRIT_B200_ATTEND_NO_TMA) return false;
+    if (!(p.flags & CRIT_B200_ATTEND_TMA) && p.kind != CRIT_B200_KIND_16BIT) return false;
     if (p.slots < 16 || p.slots > 0x7fffffffLL) return false;
     if (!(p.head_dim == p.value_dim && (p.head_dim == 128 || p.head_dim == 256))) return false;
     const int sm = scale_mode(p.kind);

@@ -97,6 +97,8 @@ typedef struct crit_b200_slots_params {
 int crit_b200_slots(const crit_b200_slots_params* params, void* stream);
 
 #define CRIT_B200_ATTEND_NO_TMA 1   /* stage pages with cp.async even where the TMA path serves the geometry */
+#define CRIT_B200_ATTEND_TMA    2   /* stage pages with TMA wherever it serves the geometry (default: 16-bit pages only,
+                                       where it measured faster; 8-bit pages measured faster with cp.async) */
 
 /* -- split-K decode / speculative-verify attention ------------------------------------------------------------------
  * Replaces paged_kv_attention.attend (paged_kv_attention/__init__.py:396-576; kernels _kernels.py:263-478 and :558-604,
