@@ -117,6 +117,7 @@ def build_state(w, device, rank, world):
     import crit_b200 as pk
     g = torch.Generator(device=device).manual_seed(w["seed"] * 1000 + rank)
     cpu = torch.Generator().manual_seed(w["seed"] * 1000 + rank)
+    same = torch.Generator().manual_seed(w["seed"] * 1000)       # the queries of a KV-range-sharded context: one set
     cols, page, hkv, d, hq = w["columns"], w["page"], w["hkv"], w["d"], w["hq"]
     if w["ctx"] is None:
         everyone = lognormal_lengths(w["batch"] * max(world, 8), w["seed"])
@@ -167,7 +168,7 @@ def build_state(w, device, rank, world):
                  firsts=firsts.to(device),
                  token_rows=torch.tensor(live, dtype=torch.int64).repeat_interleave(cols).to(device),
                  positions=(firsts[:, None] + torch.arange(cols)[None, :]).reshape(-1).to(device),
-                 h_q=torch.randn(max(tokens, 1), hq, d, generator=cpu).bfloat16().pin_memory(),
+                 h_q=torch.randn(max(tokens, 1), hq, d, generator=same if w["batch"] == 1 else cpu).bfloat16().pin_memory(),
                  h_k=torch.randn(max(tokens, 1), hkv, d, generator=cpu).bfloat16().pin_memory(),
                  h_v=torch.randn(max(tokens, 1), hkv, d, generator=cpu).bfloat16().pin_memory())
     for name in ("q", "k", "v"):
@@ -178,6 +179,13 @@ def build_state(w, device, rank, world):
     state["h_out"] = torch.empty(max(tokens, 1), hq, d, dtype=torch.bfloat16).pin_memory()
     state["h_lse"] = torch.empty(max(tokens, 1), hq, dtype=torch.float32).pin_memory()
     state["kv_bytes"] = sum(lens) * kv_bytes_per_token(w)
+    state["merger"] = None
+    if w["batch"] == 1 and world > 1:
+        # one context over the ranks by KV range: every rank keeps the step's token rows, an empty rank sends -inf
+        from crit_b200.dist import ShardMerge
+        state["merger"] = ShardMerge(cols, hq, d, device, out_dtype=torch.bfloat16)
+        state["out"].zero_()
+        state["lse"].fill_(float("-inf"))
     return state
 
 
@@ -186,6 +194,8 @@ def step(state, launch="both", append=True):
     import crit_b200 as pk
     w = state["w"]
     if not state["live"]:
+        if state["merger"] is not None and launch == "both":
+            state["merged"] = state["merger"].merge(state["out"], state["lse"])
         return
     if append:
         pk.slots_at(state["tables"], state["token_rows"], state["positions"], w["page"], state["pool"], out=state["slots"])
@@ -193,6 +203,8 @@ def step(state, launch="both", append=True):
     pk.attend(state["d_q"], state["k"], state["v"], w["kind"], state["tables"], state["rows"], state["starts"],
               state["firsts"], w["columns"], w["page"], key_scales=state["ks"], value_scales=state["vs"],
               out=state["out"], lse=state["lse"], launch=launch, staging=state.get("staging"))
+    if state["merger"] is not None and launch == "both":
+        state["merged"] = state["merger"].merge(state["out"], state["lse"])
 
 
 def timed(fn, steps, warmup, stream):
@@ -294,9 +306,14 @@ def main():
         stream.synchronize()
         graph = None
         if not args.no_graph:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                step(state)
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    step(state)
+            except Exception as error:          # a collective that does not capture: time eager steps instead
+                print(f"[bench] step not captured ({type(error).__name__}: {error}); timing eager steps", file=sys.stderr)
+                graph = None
+                torch.cuda.synchronize()
         run = (lambda: step(state)) if graph is None else graph.replay
 
         def barrier():
@@ -352,7 +369,7 @@ def main():
                     "ms_per_step": e2e_step_s * 1e3,
                     "h2d_bytes_per_step": sum(state["h_" + n].numel() * 2 for n in ("q", "k", "v")),
                     "d2h_bytes_per_step": state["h_out"].numel() * 2 + state["h_lse"].numel() * 4},
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": (4 + (2 if state["merger"] is not None else 0)) * args.steps,
             "roofline": {"bound": "hbm", "kernel": "decode_kernel (split-K decode over paged KV)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_source, "us_per_launch": decode_step_s * 1e6,

@@ -1,0 +1,102 @@
+"""The hot path across the GPUs of one node: one process per GPU, torch.distributed (NCCL over NVLink) for the only
+exchange the path has.
+
+The reference has no distributed runtime; it states the technique on the host (interleaved ownership, partials merged
+by their log-normalisers: inference/partitioned-attention/code/implementation.py:21-162, README "all-gather
+normalizers, reduce-scatter weighted outputs") and tests it with two pools on one device
+(inference/partitioned-attention/tests/test_device.py:44-68).  Here:
+
+  - batches shard BY SEQUENCE (each rank owns whole sequences and their pages): no collective at all, outputs are
+    disjoint rows.  assign_sequences() balances ranks by context length (longest first onto the lightest rank).
+  - one long context shards BY KV RANGE: rank g owns a contiguous run of `partition`-position partitions, its pages are
+    resident on its own GPU, every rank has the same queries.  Each rank runs the split-K decode over its own range
+    and folds its splits locally into one (out, lse) per (token, head); merge_across_ranks() all-gathers those
+    (tokens x heads x (dim + 1) floats a rank: 24.7 KB at 24 heads x 256) and folds them in rank order with the
+    merge-of-shards kernel, identically on every rank.  A rank with no positions contributes zeros and -inf.
+
+Failure detection without faulting a GPU: every rank's message carries (rank, epoch, rows) in its last three floats;
+with check=True the gathered headers are read on the host and a stale, missing or foreign message raises before the
+merged result is used (the reference's stated rule: a failed collective must block publication,
+inference/partitioned-attention/README.md:100-102).  A rank that never joins ends the collective through the process
+group's timeout.
+"""
+import math
+
+HEADER = 3      # floats after a rank's payload: rank, epoch, rows
+
+
+def assign_sequences(lengths, world, balance=True):
+    """Sequence indices per rank.  balance: longest sequence first onto the rank with the least positions so far (LPT);
+    else contiguous blocks of ceil(n / world)."""
+    n = len(lengths)
+    if not balance:
+        per = -(-n // world)
+        return [list(range(r * per, min(n, (r + 1) * per))) for r in range(world)]
+    found, load = [[] for _ in range(world)], [0] * world
+    for s in sorted(range(n), key=lambda i: (-lengths[i], i)):
+        r = min(range(world), key=lambda i: (load[i], len(found[i]), i))
+        found[r].append(s)
+        load[r] += lengths[s]
+    return [sorted(rows) for rows in found]
+
+
+def kv_ranges(context, world, partition=4096):
+    """[(first, end)] positions each rank owns of one context: contiguous runs of whole partitions, ceil(parts / world)
+    a rank; ranks past the context get an empty range."""
+    parts = -(-context // partition)
+    per = -(-parts // world)
+    return [(min(min(r * per, parts) * partition, context), min(min((r + 1) * per, parts) * partition, context))
+            for r in range(world)]
+
+
+class ShardMerge:
+    """Buffers (made once, so a captured step replays over them) and the exchange for rows of `tokens` x `heads`
+    partials of width `dim`."""
+
+    def __init__(self, tokens, heads, dim, device, group=None, merge=None, out_dtype=None):
+        import torch
+        import torch.distributed as dist
+        self.torch, self.dist, self.group = torch, dist, group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.tokens, self.heads, self.dim = tokens, heads, dim
+        self.rows = tokens * heads
+        self.size = self.rows * (dim + 1) + HEADER
+        self.mine = torch.zeros(self.size, dtype=torch.float32, device=device)
+        self.all = torch.zeros(self.world, self.size, dtype=torch.float32, device=device)
+        self.merge_fn, self.out_dtype, self.epoch = merge, out_dtype, 0
+        self.mine[-3], self.mine[-1] = float(self.rank), float(self.rows)
+
+    def merge(self, out, lse, check=False, epoch=None):
+        """This rank's (out [tokens][heads][dim], lse [tokens][heads]; lse -inf and out 0 where it saw no key) ->
+        the merged (out, lse) over every rank, in rank order.  epoch: the step's number, the same on every rank (default:
+        a counter of the calls); check: read the gathered headers on the host (one wait) and raise on a message that is
+        missing, stale or another shape's."""
+        torch = self.torch
+        self.epoch = self.epoch + 1 if epoch is None else int(epoch)
+        rows, dim = self.rows, self.dim
+        self.mine[:rows * dim].copy_(out.reshape(-1))
+        self.mine[rows * dim:rows * (dim + 1)].copy_(lse.reshape(-1))
+        self.mine[-2] = float(self.epoch % (1 << 20))
+        if self.world > 1:
+            self.dist.all_gather_into_tensor(self.all.view(-1), self.mine, group=self.group)
+        else:
+            self.all[0].copy_(self.mine)
+        if check:
+            self.verify()
+        outs = self.all[:, :rows * dim].view(self.world, self.tokens, self.heads, dim)
+        lses = self.all[:, rows * dim:rows * (dim + 1)].view(self.world, self.tokens, self.heads)
+        if self.merge_fn is not None:
+            return self.merge_fn(outs, lses)
+        import crit_b200
+        return crit_b200.merge_shards(outs, lses, dtype=self.out_dtype)
+
+    def verify(self):
+        """Raise unless every rank's message of this epoch and shape arrived (host read of world x 3 floats)."""
+        headers = self.all[:, -HEADER:].cpu().tolist()
+        want = float(self.epoch % (1 << 20))
+        for r, (rank, epoch, rows) in enumerate(headers):
+            if rank != float(r) or epoch != want or rows != float(self.rows) or not all(map(math.isfinite, (rank, epoch, rows))):
+                raise RuntimeError(f"rank {self.rank}: the partial of rank {r} is missing or stale (header rank {rank}, "
+                                   f"epoch {epoch}, rows {rows}; expected rank {r}, epoch {want}, rows {self.rows}): "
+                                   "the merged attention is not published")
