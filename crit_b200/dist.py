@@ -64,20 +64,22 @@ class ShardMerge:
         self.size = self.rows * (dim + 1) + HEADER
         self.mine = torch.zeros(self.size, dtype=torch.float32, device=device)
         self.all = torch.zeros(self.world, self.size, dtype=torch.float32, device=device)
-        self.merge_fn, self.out_dtype, self.epoch = merge, out_dtype, 0
+        self.merge_fn, self.out_dtype = merge, out_dtype
         self.mine[-3], self.mine[-1] = float(self.rank), float(self.rows)
 
     def merge(self, out, lse, check=False, epoch=None):
         """This rank's (out [tokens][heads][dim], lse [tokens][heads]; lse -inf and out 0 where it saw no key) ->
-        the merged (out, lse) over every rank, in rank order.  epoch: the step's number, the same on every rank (default:
-        a counter of the calls); check: read the gathered headers on the host (one wait) and raise on a message that is
-        missing, stale or another shape's."""
-        torch = self.torch
-        self.epoch = self.epoch + 1 if epoch is None else int(epoch)
+        the merged (out, lse) over every rank, in rank order.  Device work only (it can be captured in a CUDA graph):
+        the message's epoch is a counter kept on the device, one more every call.  epoch: set the counter instead (outside
+        a capture); check: read the gathered headers on the host (one wait) and raise on a message that is missing,
+        stale (another epoch than this rank's) or another shape's."""
         rows, dim = self.rows, self.dim
         self.mine[:rows * dim].copy_(out.reshape(-1))
         self.mine[rows * dim:rows * (dim + 1)].copy_(lse.reshape(-1))
-        self.mine[-2] = float(self.epoch % (1 << 20))
+        if epoch is None:
+            self.mine[-2:-1].add_(1.0)
+        else:
+            self.mine[-2:-1].fill_(float(epoch))
         if self.world > 1:
             self.dist.all_gather_into_tensor(self.all.view(-1), self.mine, group=self.group)
         else:
@@ -94,7 +96,7 @@ class ShardMerge:
     def verify(self):
         """Raise unless every rank's message of this epoch and shape arrived (host read of world x 3 floats)."""
         headers = self.all[:, -HEADER:].cpu().tolist()
-        want = float(self.epoch % (1 << 20))
+        want = headers[self.rank][1]
         for r, (rank, epoch, rows) in enumerate(headers):
             if rank != float(r) or epoch != want or rows != float(self.rows) or not all(map(math.isfinite, (rank, epoch, rows))):
                 raise RuntimeError(f"rank {self.rank}: the partial of rank {r} is missing or stale (header rank {rank}, "
