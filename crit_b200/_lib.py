@@ -74,6 +74,7 @@ SYMBOLS = {
     "crit_b200_decode": (c_int, [POINTER(AttendParams), c_void_p]),
     "crit_b200_merge": (c_int, [POINTER(AttendParams), c_void_p]),
     "crit_b200_attend": (c_int, [POINTER(AttendParams), c_void_p]),
+    "crit_b200_attend_static": (c_int, [POINTER(AttendParams), c_void_p]),
     "crit_b200_merge_shards": (c_int, [POINTER(MergeShardsParams), c_void_p]),
     "crit_b200_prefill": (c_int, [POINTER(PrefillParams), c_void_p]),
     "crit_b200_abi_version": (c_int, []),

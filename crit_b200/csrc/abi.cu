@@ -22,6 +22,7 @@ extern "C" __attribute__((visibility("default"))) const char* crit_b200_error(in
         case CRIT_B200_EUNSUPPORTED: return "crit_b200: no kernel was built for this geometry (head widths 64, 128 or 256 with keys and values of one width, pages of a multiple of 16 positions, page kinds bf16, fp16, fp8, fp8:row, int8, fp8:page)";
         case CRIT_B200_EWORKSPACE: return "crit_b200: the workspace is smaller than partial_rows * q_heads * max_splits * (value_dim + 2) floats";
         case CRIT_B200_EALIGN: return "crit_b200: q and pages are read in 16-byte vectors and outputs written in 8-byte ones: a pointer or stride is not aligned for that";
+        case CRIT_B200_ESTATIC: return "crit_b200: crit_b200_attend_static holds 4,194,304 floats (16 MiB) of partials; this launch needs more (partial_rows * q_heads * max_splits * (value_dim + 2)): raise chunk or attend fewer rows a call";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "crit_b200: unknown error";
     }
 }

@@ -327,9 +327,48 @@ static int launch_merge(const crit_b200_attend_params& p, cudaStream_t s) {
     return 0;
 }
 
+// -- partials without an allocator ------------------------------------------------------------------------------------
+// The scratch of crit_b200_attend_static: part of the library's image on every GPU that loads it.  In host code this
+// name only stands for the array (it is not a device address): the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static __device__ __align__(256) float static_scratch[CRIT_B200_STATIC_SCRATCH_FLOATS];
+
+static int static_scratch_address(float** out) {
+    constexpr int MOST = 64;
+    static float* found[MOST];
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= MOST) return CRIT_B200_EUNSUPPORTED;
+    if (!found[device]) {
+        void* address = nullptr;
+        e = cudaGetSymbolAddress(&address, static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        found[device] = static_cast<float*>(address);
+    }
+    *out = found[device];
+    return 0;
+}
+
 }  // namespace crit_b200
 
 using namespace crit_b200;
+
+extern "C" __attribute__((visibility("default"))) int crit_b200_attend_static(const crit_b200_attend_params* params, void* stream) {
+    if (!params) return CRIT_B200_EINVAL;
+    crit_b200_attend_params p = *params;
+    const int64_t need = p.max_splits > 1 ? (int64_t)p.partial_rows * p.q_heads * p.max_splits * (p.value_dim + 2) : 0;
+    if (need > CRIT_B200_STATIC_SCRATCH_FLOATS) return CRIT_B200_ESTATIC;
+    float* scratch = nullptr;
+    int e = static_scratch_address(&scratch);
+    if (e) return e;
+    p.workspace = scratch;
+    p.workspace_floats = CRIT_B200_STATIC_SCRATCH_FLOATS;
+    e = check(p);
+    if (e) return e;
+    e = launch_decode(p, (cudaStream_t)stream);
+    return e ? e : launch_merge(p, (cudaStream_t)stream);
+}
 
 extern "C" __attribute__((visibility("default"))) int crit_b200_attend_plan(int32_t q_heads, int32_t kv_heads, int32_t head_dim,
                                                                             int32_t value_dim, int32_t page, int32_t kind,

@@ -38,6 +38,7 @@ extern "C" {
 #define CRIT_B200_EUNSUPPORTED (-2) /* a geometry no kernel was built for (head widths, page size, page kind) */
 #define CRIT_B200_EWORKSPACE  (-3)  /* the workspace is smaller than crit_b200_attend_plan said */
 #define CRIT_B200_EALIGN      (-4)  /* a pointer or stride is not aligned as the kernels read it */
+#define CRIT_B200_ESTATIC     (-5)  /* the launch needs more partials than crit_b200_attend_static's built-in scratch holds */
 
 /* -- KV append ---------------------------------------------------------------------------------------------------
  * Replaces paged_kv_attention.write (paged_kv_attention/__init__.py:289-324, kernel _kernels.py:112-150) and the torch
@@ -147,6 +148,26 @@ int crit_b200_attend_plan(int32_t q_heads, int32_t kv_heads, int32_t head_dim, i
 int crit_b200_decode(const crit_b200_attend_params* params, void* stream);   /* the splits' partials */
 int crit_b200_merge(const crit_b200_attend_params* params, void* stream);    /* the fold in split order */
 int crit_b200_attend(const crit_b200_attend_params* params, void* stream);   /* both */
+
+/* crit_b200_attend for callers that may not allocate device memory.  It has no counterpart in the reference (whose
+ * launches always take their partials from a torch workspace or the engine's scratch).
+ *
+ * Some hosts of this library cannot call cudaMalloc on the path that runs attention: an engine that plans every device
+ * byte at load and refuses allocation afterwards, a plugin sandbox that is given buffers but no allocator, a request
+ * path that cannot afford the device-wide synchronisation an allocation implies.  For them the split-K partials live
+ * in an array compiled into the library: CRIT_B200_STATIC_SCRATCH_FLOATS FP32 values (16 MiB) in every GPU's memory
+ * from the moment the library is loaded there until the process exits.  params->workspace and workspace_floats are
+ * ignored; every other field means what it means for crit_b200_attend, and the results are the same bits.
+ *
+ * Limit: partial_rows * q_heads * max_splits * (value_dim + 2) must not pass CRIT_B200_STATIC_SCRATCH_FLOATS, else the
+ * call returns CRIT_B200_ESTATIC and launches nothing (raise `chunk` so rows take fewer splits, or attend fewer rows a
+ * call).  The call itself allocates and frees nothing, on the device or through any library.
+ * The first call on each device looks the array's device address up (with that device current) and keeps it; make that
+ * first call before any stream capture begins.  All calls on a device share the one array and it keeps the previous
+ * call's partials: nothing in it needs clearing, because a launch writes every partial it later reads, but two calls
+ * that run on the GPU at the same time (different streams, threads or engines) race on it: run them one after another. */
+#define CRIT_B200_STATIC_SCRATCH_FLOATS (4 * 1024 * 1024)
+int crit_b200_attend_static(const crit_b200_attend_params* params, void* stream);
 
 /* -- merge of shards --------------------------------------------------------------------------------------------
  * Replaces PartitionedAttention.merge (inference/partitioned-attention/plugin.py:52-64; host form merge_partials,
