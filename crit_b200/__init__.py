@@ -26,7 +26,7 @@ import torch
 from . import _lib
 
 __all__ = ["KINDS", "MAX_COLUMNS", "attend", "chunk_for", "gather", "merge_shards", "owner", "partitions", "parts_for",
-           "piece_size", "prefill", "release", "slots_at", "status", "tile_for", "workspace_floats", "write"]
+           "piece_size", "prefill", "prefill_serves", "release", "slots_at", "status", "tile_for", "workspace_floats", "write"]
 
 KINDS = {"bf16": 0, "fp16": 0, "fp8": 1, "fp8:row": 2, "int8": 3, "fp8:page": 4}
 MAX_COLUMNS = 64            # columns of one row a launch reads
@@ -381,6 +381,12 @@ def merge_shards(outs, lses, dtype=None):
     return out, lse
 
 
+def prefill_serves(head_dim, value_dim, q_dtype, kind, page):
+    """Whether prefill() reads a cache of this geometry (else prompt rows go through attend in pieces)."""
+    return head_dim == value_dim and head_dim in (64, 128) and page % TILE == 0 and kind in KINDS and \
+        q_dtype in (torch.bfloat16, torch.float16)
+
+
 # -- prompt chunks ------------------------------------------------------------------------------------------------------
 def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scales=None, value_scales=None,
             multipliers=(1.0, 1.0), scale=None, out=None, lse=None, int8_qk=False, fresh=None, flash=False,
@@ -396,6 +402,10 @@ def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scale
     if value_pages.shape[-1] != d:
         raise ValueError("prompt chunks read keys and values of one width")
     out = torch.empty_like(q) if out is None else out
+    if q.stride(-1) != 1 or out.stride(-1) != 1 or table.dtype != torch.int32 or not table.is_contiguous():
+        raise ValueError("q and out have contiguous last dimensions, table is contiguous int32")
+    if torch.is_tensor(position) and (position.dtype != torch.int64 or position.numel() != 1 or not position.is_cuda):
+        raise ValueError("a position read on the device is a one-element int64 tensor there")
     p = _lib.PrefillParams()
     p.q, p.out, p.lse = _ptr(q), _ptr(out), _ptr(lse)
     p.key_pages, p.value_pages = _ptr(key_pages), _ptr(value_pages)

@@ -262,6 +262,36 @@ def test_config_1_matches_the_references_outputs(pk, golden):
     assert_attention_close(out, lse, data["out"], data["lse"], list(range(len(lens))), lse_abs=2e-2)
 
 
+# -- prompt chunks ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["bf16", "fp16", "fp8", "fp8:row", "int8", "fp8:page"])
+@pytest.mark.parametrize("hq,hkv,d", [(8, 2, 128), (12, 2, 64), (32, 8, 128)])
+@pytest.mark.parametrize("position,tokens", [(0, 70), (333, 150), (1000, 1), (64, 64)])
+def test_prompt_chunks_match_the_oracle(pk, kind, hq, hkv, d, position, tokens):
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, hkv, d, d, 16, [position + tokens, 40], spare=20)
+    dtype = torch.float16 if kind == "fp16" else torch.bfloat16
+    q = queries(tokens, hq, d, 13, dtype)
+    lse = torch.empty(tokens, hq, device="cuda")
+    out = pk.prefill(q, cache.k, cache.v, kind, cache.tables[0].contiguous(), position, 16, key_scales=cache.ks,
+                     value_scales=cache.vs, multipliers=cache.multipliers, lse=lse)
+    want, want_lse = cache.oracle(q, [0], [0], [position], tokens)
+    assert_attention_close(out, lse, want, want_lse, list(range(tokens)))
+    # the position read on the device, no log-sum-exps: the same bits
+    again = pk.prefill(q, cache.k, cache.v, kind, cache.tables[0].contiguous(), torch.tensor([position], device="cuda"), 16,
+                       key_scales=cache.ks, value_scales=cache.vs, multipliers=cache.multipliers)
+    assert torch.equal(again, out)
+
+
+def test_a_prompt_token_reads_the_same_alone_and_in_its_chunk(pk):
+    from helpers import Cache, queries
+    cache = Cache("bf16", 2, 128, 128, 16, [700], spare=8)
+    q = queries(200, 8, 128, 3)
+    table = cache.tables[0].contiguous()
+    whole = pk.prefill(q, cache.k, cache.v, "bf16", table, 500, 16)
+    part = pk.prefill(q[64:130], cache.k, cache.v, "bf16", table, 564, 16)
+    torch.testing.assert_close(part.float(), whole[64:130].float(), atol=2e-2, rtol=2e-2)
+
+
 # -- merges ---------------------------------------------------------------------------------------------------------------
 def test_merge_of_shards_matches_the_references(pk, golden):
     data = golden("merge.npz")
