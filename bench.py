@@ -37,6 +37,9 @@ WORKLOADS = {
     "c5": dict(batch=32, ctx=None, hq=40, hkv=8, d=128, page=16, pool=None, kind="fp8:page", columns=6, seed=5,
                name="configs[4]: FP8 speculative verify, 32 sequences per GPU x 6 draft tokens, lognormal contexts "
                     "(median 8192, 512..65536), 40q/8kv x 128, page 16"),
+    # configs[3]: chunked prefill, 4 sequences, 32,768 positions in the pages + a chunk of 2,048, bf16 (tensor-bound)
+    "c4": dict(batch=4, ctx=32768 + 2048, hq=32, hkv=8, d=128, page=16, pool=None, kind="bf16", columns=2048, seed=4,
+               name="configs[3]: bf16 chunked prefill, 4 sequences x (32,768 prefix + 2,048 chunk), 32q/8kv x 128, page 16"),
 }
 
 
@@ -196,6 +199,17 @@ def step(state, launch="both", append=True):
     if not state["live"]:
         if state["merger"] is not None and launch == "both":
             state["merged"] = state["merger"].merge(state["out"], state["lse"])
+        return
+    if w["columns"] > 64:        # a prompt chunk per sequence: append, then one prefill launch a sequence
+        cols = w["columns"]
+        if append:
+            pk.slots_at(state["tables"], state["token_rows"], state["positions"], w["page"], state["pool"], out=state["slots"])
+            pk.write(state["d_k"], state["d_v"], state["slots"], state["k"], state["v"], w["kind"], state["ks"], state["vs"])
+        for i, s in enumerate(state["live"]):
+            span = slice(i * cols, (i + 1) * cols)
+            pk.prefill(state["d_q"][span], state["k"], state["v"], w["kind"], state["tables"][s], state["lens"][s] - cols,
+                       w["page"], key_scales=state["ks"], value_scales=state["vs"], out=state["out"][span],
+                       lse=state["lse"][span])
         return
     if append:
         pk.slots_at(state["tables"], state["token_rows"], state["positions"], w["page"], state["pool"], out=state["slots"])
@@ -376,6 +390,22 @@ def main():
                          "merge_us_per_launch": merge_s / max(20, args.steps // 4) * 1e6,
                          "algorithmic_bytes_per_launch": state["kv_bytes"], "traffic": None},
             "graph_replay": graph is not None}
+    if w["columns"] > 64:        # a dense contraction: the roofline is the tensor cores'
+        cols, hq, d = w["columns"], w["hq"], w["d"]
+        pairs = sum(cols * (n - cols) + cols * (cols + 1) // 2 for n in state["lens"])
+        flops = pairs * 4 * d * hq
+        tensor_peak = 1414.1
+        path = ROOT / "MEASURED_PEAKS.json"
+        if path.exists():
+            tensor_peak = float(json.loads(path.read_text())["bf16_tflops_sustained"])
+        tf = flops / decode_step_s / 1e12
+        line["tflops"] = flops / per_step / 1e12
+        line["gpu_launches"] = (2 + len(state["live"])) * args.steps
+        line["roofline"] = {"bound": "tensor", "kernel": "prefill_kernel (chunked prefill over paged KV)", "achieved": tf,
+                            "peak": tensor_peak, "unit": "TFLOP/s", "frac": tf / tensor_peak,
+                            "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if path.exists() else "fallback",
+                            "us_per_launch": decode_step_s * 1e6 / len(state["live"]), "algorithmic_flops_per_step": flops,
+                            "traffic": None}
     if world == 1:
         gbs, sample, spent, threads = cpu_reference(w, state, budget_s=args.cpu_seconds)
         line["cpu_baseline"] = {"value": gbs, "unit": unit, "cores": threads, "kind": "port", "sample": sample}

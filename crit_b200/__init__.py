@@ -126,7 +126,8 @@ def _status_word(device):
 
 def status(device=None):
     """0, or what a kernel recorded on `device` since load: 1 = a TMA copy's mbarrier wait ran out (that launch wrote
-    nothing for the block concerned).  Reads the device word (one wait)."""
+    nothing for the block concerned), 0x100/0x200/0x300 + tile = a wait of the tcgen05 prefill kernel (loads/scores/outputs) ran out.  Reads the device word (one
+    wait)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     found = _status.get(str(device))
     return 0 if found is None else int(found.item())
@@ -277,7 +278,8 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
            offsets=None, tokens=None, key_scales=None, value_scales=None, multipliers=(1.0, 1.0), scale=None,
            partitions=None, parents=None, blocks=None, block_size=None, out=None, lse=None, workspace=None, piece=None,
            fused=False, fresh=None, vsplit=None, tile=None, num_warps=None, num_stages=None, maxnreg=None,
-           flash=False, chunk=None, ramp=None, sinks=None, sliding=0, derive=None, launch="both", staging=None):
+           flash=False, chunk=None, ramp=None, sinks=None, sliding=0, derive=None, launch="both", staging=None,
+           persistent=False):
     """Decode and verify windows over paged KV (reference: paged_kv_attention/__init__.py:396-445, same arguments).
 
     q [tokens][heads][dim] bf16 or fp16 (fp16 for "fp16" pages); key_pages / value_pages one layer's pages
@@ -291,7 +293,9 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     accepted and change nothing (one launch shape per geometry).  parents, blocks, fresh, sinks, sliding and derive
     are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
     None (TMA tiled loads for 16-bit pages of 128- or 256-wide heads, cp.async otherwise: what measured faster), "tma"
-    (TMA wherever the geometry allows it) or "cp.async" (never TMA); the same bits either way."""
+    (TMA wherever the geometry allows it) or "cp.async" (never TMA); the same bits either way.  persistent: a fixed
+    number of blocks walk a work list built on the device from the rows' lengths, instead of one block per (split, kv
+    head, row) of a 3-D grid (the same bits; measured slower on the bench workloads, hence off)."""
     _refuse(parents=parents, blocks=blocks, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
@@ -345,7 +349,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     p.slots = key_pages.numel() // (hkv * d)
     if staging not in (None, "tma", "cp.async"):
         raise ValueError("staging is None, tma or cp.async")
-    p.flags = {None: 0, "cp.async": 1, "tma": 2}[staging]
+    p.flags = {None: 0, "cp.async": 1, "tma": 2}[staging] | (4 if persistent else 0)
     p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])
@@ -390,10 +394,12 @@ def prefill_serves(head_dim, value_dim, q_dtype, kind, page):
 # -- prompt chunks ------------------------------------------------------------------------------------------------------
 def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scales=None, value_scales=None,
             multipliers=(1.0, 1.0), scale=None, out=None, lse=None, int8_qk=False, fresh=None, flash=False,
-            sinks=None, sliding=0, splits=None, workspace=None, derive=None):
+            sinks=None, sliding=0, splits=None, workspace=None, derive=None, engine=None):
     """A prompt chunk of one sequence: q [T][heads][dim] at positions position.. (their keys and values written),
     table [pages] int32 -> out [T][heads][dim] in q's dtype (and lse [T][heads] FP32 when given), causal.  position: an
-    int, or a one-element int64 device tensor read on the device.  Reference: paged_kv_attention/__init__.py:1245-1332."""
+    int, or a one-element int64 device tensor read on the device.  engine: None or "mma.sync" (m16n8k16 tiles, every
+    page kind) or "tcgen05" (tcgen05.mma tiles with TMEM accumulators: 16-bit pages of 128-wide heads only).
+    Reference: paged_kv_attention/__init__.py:1245-1332."""
     _refuse(int8_qk=int8_qk, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
@@ -417,6 +423,9 @@ def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scale
         p.position = int(position)
     p.q_stride_token, p.q_stride_head = q.stride(0), q.stride(1)
     p.out_stride_token, p.out_stride_head = out.stride(0), out.stride(1)
+    p.slots = key_pages.numel() // (hkv * d)
+    p.flags = {None: 0, "mma.sync": 1, "tcgen05": 2}[engine]
+    p.status = _ptr(_status_word(q.device))
     p.tokens, p.q_heads, p.kv_heads, p.head_dim, p.value_dim, p.page = T, hq, hkv, d, d, int(page)
     p.kind, p.page_dtype, p.q_dtype = k_kind, _page_dtype(kind, key_pages), _DTYPES[q.dtype]
     p.scale = float(scale if scale is not None else d ** -0.5)

@@ -55,11 +55,11 @@ class MergeShardsParams(Structure):
 class PrefillParams(Structure):
     _fields_ = [("q", c_void_p), ("out", c_void_p), ("lse", c_void_p), ("key_pages", c_void_p),
                 ("value_pages", c_void_p), ("key_scales", c_void_p), ("value_scales", c_void_p),
-                ("table", c_void_p), ("position_ptr", c_void_p), ("position", c_int64),
+                ("table", c_void_p), ("position_ptr", c_void_p), ("status", c_void_p), ("position", c_int64), ("slots", c_int64),
                 ("q_stride_token", c_int64), ("q_stride_head", c_int64), ("out_stride_token", c_int64),
                 ("out_stride_head", c_int64), ("tokens", c_int32), ("q_heads", c_int32), ("kv_heads", c_int32),
                 ("head_dim", c_int32), ("value_dim", c_int32), ("page", c_int32), ("kind", c_int32),
-                ("page_dtype", c_int32), ("q_dtype", c_int32),
+                ("page_dtype", c_int32), ("q_dtype", c_int32), ("flags", c_int32),
                 ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float)]
 
 

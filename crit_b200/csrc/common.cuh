@@ -171,9 +171,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Waits for a phase of the barrier, at most `limit` polls: false when it gave up (the caller records it and leaves).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int limit = 1 << 18) {
-    for (int i = 0; i < limit; ++i)
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Waits for a phase of the barrier for at most `limit_ns` (a quarter of a second by default; a poll itself may block
+// for a while, so the bound is on time, not on polls): false when it gave up (the caller records it and leaves).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint64_t limit_ns = 250000000ull) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    while (global_ns() - t0 < limit_ns)
         if (mbar_try_wait(bar, parity)) return true;
     return false;
 }

@@ -3,6 +3,7 @@
 // Reference: paged_kv_attention/_kernels.py:558-604 (_merge_kernel), cuda_window.cu:1071-1286 (cw_merge, cw_merge2),
 // :1482-1535 (the C ABI this one mirrors).
 #include "decode_kernel.cuh"
+#include "tensor_map.cuh"
 
 namespace crit_b200 {
 
@@ -133,7 +134,8 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
 }
 
 // -- host side --------------------------------------------------------------------------------------------------------
-typedef void (*decode_fn)(const crit_b200_attend_params, const int, const int, const int, const CUtensorMap, const CUtensorMap);
+typedef void (*decode_fn)(const crit_b200_attend_params, const int, const int, const int, const int, const CUtensorMap,
+                          const CUtensorMap);
 typedef int (*smem_fn)(int);
 
 struct Variant {
@@ -228,39 +230,25 @@ static int scale_stage_bytes(const crit_b200_attend_params& p, bool tma) {
     return 0;
 }
 
-typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static encode_tiled_fn encoder() {
-    static encode_tiled_fn found = nullptr;
-    static bool asked = false;
-    if (!asked) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult how;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &how) == cudaSuccess &&
-            how == cudaDriverEntryPointSuccess)
-            found = (encode_tiled_fn)fn;
+// Blocks of a kernel the current device holds at once (SMs x blocks per SM), remembered per kernel, shared-memory size
+// and device.
+static int resident_blocks(const void* fn, int smem) {
+    struct Entry { const void* fn; int smem, device, blocks; };
+    static Entry seen[256];
+    static int n = 0;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    for (int i = 0; i < n; ++i)
+        if (seen[i].fn == fn && seen[i].smem == smem && seen[i].device == device) return seen[i].blocks;
+    int sms = 0, per_sm = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, fn, DECODE_THREADS, smem) != cudaSuccess) {
         cudaGetLastError();
-        asked = true;
+        return 0;
     }
-    return found;
-}
-
-// A 3-D map over one page tensor [slots][kv_heads][dim]; a box is 16 slots of one head, 128 bytes wide.
-static bool page_map(CUtensorMap* map, const void* pages, int pk, int dim, int kv_heads, int64_t slots) {
-    encode_tiled_fn encode = encoder();
-    if (!encode) return false;
-    const int es = pk < 2 ? 2 : 1;
-    const CUtensorMapDataType type = pk == 0 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                             : (pk == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8);
-    const cuuint64_t dims[3] = {(cuuint64_t)dim, (cuuint64_t)kv_heads, (cuuint64_t)slots};
-    const cuuint64_t strides[2] = {(cuuint64_t)dim * es, (cuuint64_t)dim * es * kv_heads};
-    const cuuint32_t box[3] = {(cuuint32_t)(128 / es), 1, 16};
-    const cuuint32_t steps[3] = {1, 1, 1};
-    return encode(map, type, 3, const_cast<void*>(pages), dims, strides, box, steps, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    const int blocks = sms * per_sm;
+    if (n < 256) seen[n++] = Entry{fn, smem, device, blocks};
+    return blocks;
 }
 
 static int check(const crit_b200_attend_params& p) {
@@ -303,8 +291,19 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     cudaError_t ce = cudaFuncSetAttribute((const void*)v.fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (ce != cudaSuccess) return (int)ce;
     const int ctiles = (rows + 8 * nt - 1) / (8 * nt);
+    const int64_t most = (int64_t)p.max_splits * p.kv_heads * ctiles * p.n_rows;      // units the launch can have
+    if (p.n_rows <= DECODE_MAX_LIST && (p.flags & CRIT_B200_ATTEND_PERSISTENT)) {
+        // persistent: a fixed number of blocks (what the SMs hold at once) walk the launch's work list
+        const int slots = resident_blocks((const void*)v.fn, smem);
+        if (slots > 0) {
+            const unsigned blocks = (unsigned)(most < slots ? most : slots);
+            v.fn<<<blocks, DECODE_THREADS, smem, s>>>(p, ctiles, scale_mode(p.kind), scb, 1, kmap, vmap);
+            CRIT_CHECK_LAUNCH();
+            return 0;
+        }
+    }
     dim3 grid((unsigned)p.max_splits, (unsigned)(p.kv_heads * ctiles), (unsigned)p.n_rows);
-    v.fn<<<grid, DECODE_THREADS, smem, s>>>(p, ctiles, scale_mode(p.kind), scb, kmap, vmap);
+    v.fn<<<grid, DECODE_THREADS, smem, s>>>(p, ctiles, scale_mode(p.kind), scb, 0, kmap, vmap);
     CRIT_CHECK_LAUNCH();
     return 0;
 }

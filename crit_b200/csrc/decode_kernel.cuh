@@ -38,6 +38,7 @@ namespace crit_b200 {
 constexpr int DECODE_WARPS = 4;
 constexpr int DECODE_THREADS = DECODE_WARPS * 32;
 constexpr float LAZY = 8.f;
+constexpr int DECODE_MAX_LIST = 256;       // rows a persistent launch lists its work for
 
 // Page element classes (PK): 0 bf16, 1 fp16, 2 E4M3 bytes, 3 INT8 bytes.
 // NT: 8-row tiles of query rows a block holds (1, 2 or 4).
@@ -94,7 +95,7 @@ __device__ __forceinline__ int tile_off(int row, int c) {
 
 template <int D, int DV, int PK, int NT, bool TMA>
 __global__ void __launch_bounds__(DECODE_THREADS)
-decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode, const int scb,
+decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode, const int scb, const int persistent,
               const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
     using C = DecodeCfg<D, DV, PK, NT, TMA>;
     constexpr bool BF16 = C::BF16;
@@ -105,23 +106,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     extern __shared__ unsigned char smem_raw[];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-    const int split = blockIdx.x;
-    const int h = blockIdx.y / ctiles, ct = blockIdx.y - h * ctiles;
-    const int r = blockIdx.z;
     const int G = p.q_heads / p.kv_heads;
-
-    int count = p.counts ? p.counts[r] : p.columns;
-    count = count > p.columns ? p.columns : count;
-    if (count <= 0) return;
-    if (ct * ROWS >= count * G) return;
-    const int64_t first = p.firsts[r];
-    const int64_t L = first + count;
-    const int64_t begin = (int64_t)split * p.chunk;
-    if (begin >= L) return;
-    const int64_t end = begin + p.chunk < L ? begin + p.chunk : L;
-    const int nsplit = (int)((L + p.chunk - 1) / p.chunk);
-    const int32_t* table = p.tables + (int64_t)p.rows[r] * p.table_stride;
-    const int start = p.starts[r];
 
     // shared memory, its base rounded up to 1 KB (the 128-byte swizzle's period is 8 rows of 128 bytes)
     unsigned char* smem = smem_raw + ((1024 - (smem_addr(smem_raw) & 1023)) & 1023);
@@ -138,6 +123,80 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
             mbar_init_fence();
         }
     }
+
+    // -- the work list -------------------------------------------------------------------------------------------------
+    // persistent: the grid is a fixed number of blocks (a few per SM); every block lists the launch's work units
+    // (row, kv head, query-row tile, split), counted from the rows' lengths read here on the device, and takes units
+    // block, block + grid, ...  So a launch over rows of very different lengths starts no block that has nothing to
+    // do, and the last wave is short.  Otherwise one unit per block, named by the block's place in a 3-D grid.
+    __shared__ int unit_first[DECODE_MAX_LIST + 1];
+    int units = 1;
+    if (persistent) {
+        if (warp == 0) {
+            int carry = 0;
+            for (int base = 0; base < p.n_rows; base += 32) {
+                const int rr = base + lane;
+                int mine_units = 0;
+                if (rr < p.n_rows) {
+                    int cnt = p.counts ? p.counts[rr] : p.columns;
+                    cnt = cnt > p.columns ? p.columns : cnt;
+                    if (cnt > 0) {
+                        const int64_t len = p.firsts[rr] + cnt;
+                        mine_units = (int)((len + p.chunk - 1) / p.chunk) * ((cnt * G + ROWS - 1) / ROWS) * p.kv_heads;
+                    }
+                }
+                int scan = mine_units;
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const int up = __shfl_up_sync(0xffffffffu, scan, o);
+                    if (lane >= o) scan += up;
+                }
+                if (rr < p.n_rows) unit_first[rr + 1] = carry + scan;
+                carry += __shfl_sync(0xffffffffu, scan, 31);
+            }
+            if (lane == 0) unit_first[0] = 0;
+        }
+        __syncthreads();
+        units = unit_first[p.n_rows];
+    }
+    int tbase = 0;              // tiles this warp has staged in earlier units (the stages' and mbarriers' running count)
+
+    for (int unit = persistent ? (int)blockIdx.x : 0; unit < units; unit += persistent ? (int)gridDim.x : 1) {
+    int split, h, ct, r;
+    if (persistent) {
+        int lo = 0, hi = p.n_rows;              // the row whose units hold this one
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (unit_first[mid] <= unit) lo = mid;
+            else hi = mid;
+        }
+        r = lo;
+    } else {
+        r = blockIdx.z;
+    }
+    int count = p.counts ? p.counts[r] : p.columns;
+    count = count > p.columns ? p.columns : count;
+    if (count <= 0) continue;
+    const int64_t first = p.firsts[r];
+    const int64_t L = first + count;
+    const int nsplit = (int)((L + p.chunk - 1) / p.chunk);
+    if (persistent) {
+        const int local = unit - unit_first[r];
+        const int row_tiles = (count * G + ROWS - 1) / ROWS;
+        split = local % nsplit;
+        ct = (local / nsplit) % row_tiles;
+        h = local / (nsplit * row_tiles);
+    } else {
+        split = blockIdx.x;
+        h = blockIdx.y / ctiles;
+        ct = blockIdx.y - h * ctiles;
+    }
+    if (ct * ROWS >= count * G) continue;
+    const int64_t begin = (int64_t)split * p.chunk;
+    if (begin >= L) continue;
+    const int64_t end = begin + p.chunk < L ? begin + p.chunk : L;
+    const int32_t* table = p.tables + (int64_t)p.rows[r] * p.table_stride;
+    const int start = p.starts[r];
 
     // -- the query tile into shared memory: ROWS rows of D 16-bit values (FP16 where the pages are 8-bit) -------------
     {
@@ -234,7 +293,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
             const int off = (int)(tile - pidx * tiles_per_page) << 4;
             const int pg = table[pidx];
             const int64_t slot0 = (int64_t)pg * p.page + off;
-            const int stage = i % C::STAGES;
+            const int stage = (tbase + i) % C::STAGES;
             const uint32_t ks = smem_addr(tiles + stage * C::TILES), vs = ks + C::KTILE;
             const uint32_t sc = smem_addr(scales_ring + stage * scb);
             if constexpr (TMA) {
@@ -293,7 +352,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
             bool ok = true;
 #pragma unroll
             for (int u = 0; u < TPI; ++u)
-                if (u < have) ok &= mbar_wait(bars + ((i + u) % C::STAGES) * 8, (uint32_t)((i + u) / C::STAGES) & 1u);
+                if (u < have) ok &= mbar_wait(bars + ((tbase + i + u) % C::STAGES) * 8, (uint32_t)((tbase + i + u) / C::STAGES) & 1u);
             if (!__all_sync(0xffffffffu, ok)) {
                 dead = true;                // a copy never landed: record it and leave, nothing is written
                 break;
@@ -317,7 +376,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
                 for (int e = 0; e < 4; ++e) s[u][nt][e] = u < have ? 0.f : -INFINITY;
             if (u >= have) continue;
             masked |= pos0[u] + 16 > first32;
-            const int stage = (i + u) % C::STAGES;
+            const int stage = (tbase + i + u) % C::STAGES;
             unsigned char* kst = tiles + stage * C::TILES;
             const float* scales = reinterpret_cast<const float*>(scales_ring + stage * scb);
             if constexpr (TMA) {
@@ -449,7 +508,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
 #pragma unroll
         for (int u = 0; u < TPI; ++u) {
             if (u >= have) continue;
-            unsigned char* vst = tiles + ((i + u) % C::STAGES) * C::TILES + C::KTILE;
+            unsigned char* vst = tiles + ((tbase + i + u) % C::STAGES) * C::TILES + C::KTILE;
             if constexpr (ES == 2) {
 #pragma unroll
                 for (int mt = 0; mt < DV / 16; ++mt) {
@@ -495,7 +554,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     if constexpr (TMA) {
         if (__any_sync(0xffffffffu, dead)) {
             // Give every copy this warp still has in flight a last bounded chance to land before the block leaves.
-            for (int s = 0; s < C::STAGES; ++s) mbar_wait(bars + s * 8, 0, 1 << 12);
+            for (int s = 0; s < C::STAGES; ++s) mbar_wait(bars + s * 8, 0, 1000000ull);
             if (lane == 0 && p.status) atomicExch(p.status, 1);
             dead = true;
         }
@@ -581,6 +640,9 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
                 p.workspace[states * (DV + 1) + at] = l;
             }
         }
+    }
+    tbase += mine;
+    __syncthreads();            // the fold and the queries are read to the end before the next unit stages over them
     }
 }
 

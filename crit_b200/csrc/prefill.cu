@@ -9,6 +9,8 @@
 // Reference: paged_kv_attention/_kernels.py:610-726 (_prefill_kernel), __init__.py:1245-1332 (prefill); the reference
 // runs one program per (64 queries, query head), re-reading a kv head's pages once per query head of its group.
 #include "decode_kernel.cuh"
+#include "prefill_tc.cuh"
+#include "tensor_map.cuh"
 
 namespace crit_b200 {
 
@@ -368,6 +370,25 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_prefill(const cr
     if (!aligned(p.q, 16) || p.q_stride_token % 8 || p.q_stride_head % 8 || !aligned(p.key_pages, 16) ||
         !aligned(p.value_pages, 16) || !aligned(p.out, 4) || p.out_stride_token % 2 || p.out_stride_head % 2)
         return CRIT_B200_EALIGN;
+    const int G = p.q_heads / p.kv_heads;
+    // tcgen05 tiles: 16-bit pages of 128-wide heads, with the pool's size known for the tensor maps
+    const bool tc_serves = p.kind == CRIT_B200_KIND_16BIT && p.head_dim == TC_D && p.slots >= 16 && p.slots <= 0x7fffffffLL;
+    if ((p.flags & CRIT_B200_PREFILL_TCGEN05) && !tc_serves) return CRIT_B200_EUNSUPPORTED;
+    if (tc_serves && (p.flags & CRIT_B200_PREFILL_TCGEN05)) {
+        const bool bf16 = p.page_dtype == CRIT_B200_DTYPE_BF16;
+        CUtensorMap kmap, vmap;
+        if (page_map(&kmap, p.key_pages, bf16 ? 0 : 1, p.head_dim, p.kv_heads, p.slots) &&
+            page_map(&vmap, p.value_pages, bf16 ? 0 : 1, p.value_dim, p.kv_heads, p.slots)) {
+            auto tc = bf16 ? prefill_tc_kernel<true> : prefill_tc_kernel<false>;
+            cudaError_t ce = cudaFuncSetAttribute((const void*)tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
+            if (ce != cudaSuccess) return (int)ce;
+            dim3 grid((unsigned)((p.tokens * G + TC_ROWS - 1) / TC_ROWS), (unsigned)p.kv_heads);
+            tc<<<grid, TC_ROWS, TC_SMEM, (cudaStream_t)stream>>>(p, kmap, vmap, p.status);
+            CRIT_CHECK_LAUNCH();
+            return 0;
+        }
+        if (p.flags & CRIT_B200_PREFILL_TCGEN05) return CRIT_B200_EUNSUPPORTED;
+    }
     prefill_fn fn = nullptr;
     int smem = 0, e;
     if (p.kind == CRIT_B200_KIND_16BIT) e = p.page_dtype == CRIT_B200_DTYPE_BF16 ? prefill_pick<0>(p.head_dim, &fn, &smem) : prefill_pick<1>(p.head_dim, &fn, &smem);
@@ -377,7 +398,6 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_prefill(const cr
     if (e) return e;
     cudaError_t ce = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (ce != cudaSuccess) return (int)ce;
-    const int G = p.q_heads / p.kv_heads;
     dim3 grid((unsigned)((p.tokens * G + PF_ROWS - 1) / PF_ROWS), (unsigned)p.kv_heads);
     fn<<<grid, PF_THREADS, smem, (cudaStream_t)stream>>>(p, smode);
     CRIT_CHECK_LAUNCH();

@@ -101,6 +101,10 @@ int crit_b200_slots(const crit_b200_slots_params* params, void* stream);
 #define CRIT_B200_ATTEND_TMA    2   /* stage pages with TMA wherever it serves the geometry (default: 16-bit pages only,
                                        where it measured faster; 8-bit pages measured faster with cp.async) */
 
+#define CRIT_B200_ATTEND_PERSISTENT 4 /* a fixed number of blocks (what the SMs hold at once) walk a work list built on the
+                                        device from the rows' lengths, instead of one block per (split, kv head, row)
+                                        slot of a 3-D grid; the same bits; at most 256 rows, else the 3-D grid */
+
 /* -- split-K decode / speculative-verify attention ------------------------------------------------------------------
  * Replaces paged_kv_attention.attend (paged_kv_attention/__init__.py:396-576; kernels _kernels.py:263-478 and :558-604,
  * cuda_window.cu:284-1286) behind DeviceAttention._windows (inference/attention-state/code/device_attention.py:659-704).
@@ -189,7 +193,11 @@ int crit_b200_merge_shards(const crit_b200_merge_shards_params* params, void* st
  * Replaces paged_kv_attention.prefill (paged_kv_attention/__init__.py:1245-1332; kernel _kernels.py:610-726) behind
  * DeviceAttention._prefill_rows (device_attention.py:901-916): one sequence's chunk of `tokens` queries at positions
  * position.. (position_ptr, a device int64, wins over position when not NULL) over its page table, causal; the
- * chunk's keys and values are in the pages already. */
+ * chunk's keys and values are in the pages already.  16-bit pages of 128-wide heads run on tcgen05 tensor-core tiles
+ * with TMEM accumulators (TMA-staged pages); every other geometry on m16n8k16 tiles. */
+#define CRIT_B200_PREFILL_MMA_SYNC 1   /* the m16n8k16 kernel (also what 0 selects) */
+#define CRIT_B200_PREFILL_TCGEN05  2   /* the tcgen05 kernel or CRIT_B200_EUNSUPPORTED */
+
 typedef struct crit_b200_prefill_params {
     const void* q;
     void* out;
@@ -200,10 +208,13 @@ typedef struct crit_b200_prefill_params {
     const float* value_scales;
     const int32_t* table;        /* [pages of the sequence] */
     const int64_t* position_ptr; /* or NULL */
+    int32_t* status;             /* or NULL: set (never cleared) when a bounded wait of the tcgen05 kernel gave up */
     int64_t position;
+    int64_t slots;               /* slots each page tensor stores ((pages + 1) * page), 0: unknown (no TMA, no tcgen05 path) */
     int64_t q_stride_token, q_stride_head, out_stride_token, out_stride_head;
     int32_t tokens, q_heads, kv_heads, head_dim, value_dim, page;
     int32_t kind, page_dtype, q_dtype;
+    int32_t flags;               /* CRIT_B200_PREFILL_* */
     float scale, key_multiplier, value_multiplier;
 } crit_b200_prefill_params;
 

@@ -192,6 +192,9 @@ def test_tma_and_cp_async_staging_give_the_same_bits(pk, kind, hq, hkv, d):
     plain = cache.attend(q, rows, starts, firsts, 6, counts=counts, lse=lse_b, chunk=128, staging="cp.async")
     tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
     assert torch.equal(tma[tokens], plain[tokens]) and torch.equal(lse_a[tokens], lse_b[tokens])
+    # ... and persistent blocks over a device-built work list instead of one block per grid slot
+    listed = cache.attend(q, rows, starts, firsts, 6, counts=counts, lse=lse_b, chunk=128, persistent=True)
+    assert torch.equal(listed[tokens], plain[tokens]) and torch.equal(lse_a[tokens], lse_b[tokens])
     want, want_lse = cache.oracle(q, rows, starts, firsts, 6, counts=counts)
     assert_attention_close(tma, lse_a, want, want_lse, tokens, rel=2.0 ** -7 if kind == "fp8:page" else 0.0)
     assert pk.status() == 0
