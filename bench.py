@@ -209,7 +209,7 @@ def step(state, launch="both", append=True):
             span = slice(i * cols, (i + 1) * cols)
             pk.prefill(state["d_q"][span], state["k"], state["v"], w["kind"], state["tables"][s], state["lens"][s] - cols,
                        w["page"], key_scales=state["ks"], value_scales=state["vs"], out=state["out"][span],
-                       lse=state["lse"][span])
+                       lse=state["lse"][span], engine=state.get("engine"))
         return
     if append:
         pk.slots_at(state["tables"], state["token_rows"], state["positions"], w["page"], state["pool"], out=state["slots"])
@@ -277,11 +277,16 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--staging", default=None, choices=["tma", "cp.async"])
+    ap.add_argument("--engine", default=None, choices=["mma.sync", "tcgen05"], help="the prefill kernel (c4)")
+    ap.add_argument("--batch", type=int, default=None,
+                    help="sequences per GPU instead of the workload's own (a small case for a profiler capture)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
-    w = WORKLOADS[args.workload]
+    w = dict(WORKLOADS[args.workload])
+    if args.batch:
+        w["batch"], w["name"] = args.batch, w["name"] + f" [--batch {args.batch}: a reduced case]"
     reference = args.impl == "reference"
     if reference and rank != 0:
         return
@@ -293,10 +298,12 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     state = build_state(w, device, rank, world)
-    state["staging"] = args.staging
+    state["staging"], state["engine"] = args.staging, args.engine
     torch.cuda.synchronize()
     tokens_step = state["tokens"]
-    config = {"workload": w["name"], "kv": w["kind"], "steps_are": "slot map + KV append + split-K decode + merge",
+    steps_are = ("slot map + KV append + one prefill launch per sequence" if w["columns"] > 64
+                 else "slot map + KV append + split-K decode + merge")
+    config = {"workload": w["name"], "kv": w["kind"], "steps_are": steps_are,
               "l2": "inputs larger than L2: every step reads the whole KV context "
                     f"({state['kv_bytes'] / 1e6:.1f} MB per GPU, L2 is 126 MB)",
               "sharding": "sequences per GPU, no collective" if w["batch"] > 1 else "KV range per GPU"}
@@ -401,7 +408,8 @@ def main():
         tf = flops / decode_step_s / 1e12
         line["tflops"] = flops / per_step / 1e12
         line["gpu_launches"] = (2 + len(state["live"])) * args.steps
-        line["roofline"] = {"bound": "tensor", "kernel": "prefill_kernel (chunked prefill over paged KV)", "achieved": tf,
+        line["roofline"] = {"bound": "tensor", "kernel": ("prefill_tc_kernel (tcgen05 chunked prefill over paged KV)" if args.engine == "tcgen05"
+                                       else "prefill_kernel (m16n8k16 chunked prefill over paged KV)"), "achieved": tf,
                             "peak": tensor_peak, "unit": "TFLOP/s", "frac": tf / tensor_peak,
                             "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if path.exists() else "fallback",
                             "us_per_launch": decode_step_s * 1e6 / len(state["live"]), "algorithmic_flops_per_step": flops,

@@ -372,7 +372,7 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_prefill(const cr
         return CRIT_B200_EALIGN;
     const int G = p.q_heads / p.kv_heads;
     // tcgen05 tiles: 16-bit pages of 128-wide heads, with the pool's size known for the tensor maps
-    const bool tc_serves = p.kind == CRIT_B200_KIND_16BIT && p.head_dim == TC_D && p.slots >= 16 && p.slots <= 0x7fffffffLL;
+    const bool tc_serves = p.kind == CRIT_B200_KIND_16BIT && p.head_dim == TC_D && p.value_dim == TC_D && p.slots >= 16 && p.slots <= 0x7fffffffLL;
     if ((p.flags & CRIT_B200_PREFILL_TCGEN05) && !tc_serves) return CRIT_B200_EUNSUPPORTED;
     if (tc_serves && (p.flags & CRIT_B200_PREFILL_TCGEN05)) {
         const bool bf16 = p.page_dtype == CRIT_B200_DTYPE_BF16;

@@ -285,6 +285,40 @@ def test_prompt_chunks_match_the_oracle(pk, kind, hq, hkv, d, position, tokens):
     assert torch.equal(again, out)
 
 
+@pytest.mark.parametrize("kind", ["bf16", "fp16"])
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (32, 8), (5, 1), (16, 16)])
+@pytest.mark.parametrize("position,tokens", [(0, 70), (333, 150), (1000, 1), (64, 64), (0, 32), (4090, 300)])
+def test_prompt_chunks_on_tcgen05_tiles_match_the_oracle(pk, kind, hq, hkv, position, tokens):
+    """The tcgen05 / TMEM engine: 128-row blocks (partly filled last blocks and warps, one tile and many)."""
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, hkv, 128, 128, 16, [position + tokens, 40], spare=20)
+    dtype = torch.float16 if kind == "fp16" else torch.bfloat16
+    q = queries(tokens, hq, 128, 13, dtype)
+    lse = torch.empty(tokens, hq, device="cuda")
+    table = cache.tables[0].contiguous()
+    out = pk.prefill(q, cache.k, cache.v, kind, table, position, 16, lse=lse, engine="tcgen05")
+    assert pk.status() == 0
+    want, want_lse = cache.oracle(q, [0], [0], [position], tokens)
+    assert_attention_close(out, lse, want, want_lse, list(range(tokens)))
+    again = pk.prefill(q, cache.k, cache.v, kind, table, torch.tensor([position], device="cuda"), 16, engine="tcgen05")
+    assert torch.equal(again, out)
+    # against the m16n8k16 engine: the same tiles of 64 positions and the same lazy maximum, so nearly the same bits
+    other = pk.prefill(q, cache.k, cache.v, kind, table, position, 16, engine="mma.sync")
+    torch.testing.assert_close(out.float(), other.float(), atol=1e-2, rtol=2e-2)
+
+
+def test_tcgen05_tiles_refuse_what_they_do_not_serve(pk):
+    from helpers import Cache, queries
+    cache = Cache("fp8:row", 2, 128, 128, 16, [100], spare=4)
+    q = queries(20, 8, 128, 1)
+    with pytest.raises(Exception):
+        pk.prefill(q, cache.k, cache.v, "fp8:row", cache.tables[0].contiguous(), 80, 16, key_scales=cache.ks,
+                   value_scales=cache.vs, engine="tcgen05")
+    cache = Cache("bf16", 2, 64, 64, 16, [100], spare=4)
+    with pytest.raises(Exception):
+        pk.prefill(queries(20, 8, 64, 1), cache.k, cache.v, "bf16", cache.tables[0].contiguous(), 80, 16, engine="tcgen05")
+
+
 def test_a_prompt_token_reads_the_same_alone_and_in_its_chunk(pk):
     from helpers import Cache, queries
     cache = Cache("bf16", 2, 128, 128, 16, [700], spare=8)
