@@ -216,7 +216,8 @@ def step(state, launch="both", append=True):
         pk.write(state["d_k"], state["d_v"], state["slots"], state["k"], state["v"], w["kind"], state["ks"], state["vs"])
     pk.attend(state["d_q"], state["k"], state["v"], w["kind"], state["tables"], state["rows"], state["starts"],
               state["firsts"], w["columns"], w["page"], key_scales=state["ks"], value_scales=state["vs"],
-              out=state["out"], lse=state["lse"], launch=launch, staging=state.get("staging"))
+              out=state["out"], lse=state["lse"], launch=launch, staging=state.get("staging"),
+              engine=state.get("engine"))
     if state["merger"] is not None and launch == "both":
         state["merged"] = state["merger"].merge(state["out"], state["lse"])
 
@@ -277,7 +278,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--staging", default=None, choices=["tma", "cp.async"])
-    ap.add_argument("--engine", default=None, choices=["mma.sync", "tcgen05"], help="the prefill kernel (c4)")
+    ap.add_argument("--engine", default=None, choices=["mma.sync", "tcgen05"], help="the attention kernel instead of the library's choice")
     ap.add_argument("--batch", type=int, default=None,
                     help="sequences per GPU instead of the workload's own (a small case for a profiler capture)")
     args = ap.parse_args()

@@ -279,7 +279,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
            partitions=None, parents=None, blocks=None, block_size=None, out=None, lse=None, workspace=None, piece=None,
            fused=False, fresh=None, vsplit=None, tile=None, num_warps=None, num_stages=None, maxnreg=None,
            flash=False, chunk=None, ramp=None, sinks=None, sliding=0, derive=None, launch="both", staging=None,
-           persistent=False):
+           persistent=False, engine=None):
     """Decode and verify windows over paged KV (reference: paged_kv_attention/__init__.py:396-445, same arguments).
 
     q [tokens][heads][dim] bf16 or fp16 (fp16 for "fp16" pages); key_pages / value_pages one layer's pages
@@ -295,7 +295,9 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     None (TMA tiled loads for 16-bit pages of 128- or 256-wide heads, cp.async otherwise: what measured faster), "tma"
     (TMA wherever the geometry allows it) or "cp.async" (never TMA); the same bits either way.  persistent: a fixed
     number of blocks walk a work list built on the device from the rows' lengths, instead of one block per (split, kv
-    head, row) of a 3-D grid (the same bits; measured slower on the bench workloads, hence off)."""
+    head, row) of a 3-D grid (the same bits; measured slower on the bench workloads, hence off).  engine: None (the
+    library's choice), "mma.sync" (the m16n8k16 kernel) or "tcgen05" (E4M3 page bytes straight into tcgen05.mma: E4M3
+    pages of 128-wide heads, columns x group heads <= 32, chunk a multiple of 128; refused elsewhere)."""
     _refuse(parents=parents, blocks=blocks, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
@@ -349,7 +351,8 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     p.slots = key_pages.numel() // (hkv * d)
     if staging not in (None, "tma", "cp.async"):
         raise ValueError("staging is None, tma or cp.async")
-    p.flags = {None: 0, "cp.async": 1, "tma": 2}[staging] | (4 if persistent else 0)
+    p.flags = ({None: 0, "cp.async": 1, "tma": 2}[staging] | (4 if persistent else 0) |
+               {None: 0, "tcgen05": 8, "mma.sync": 16}[engine])
     p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])

@@ -3,6 +3,7 @@
 // Reference: paged_kv_attention/_kernels.py:558-604 (_merge_kernel), cuda_window.cu:1071-1286 (cw_merge, cw_merge2),
 // :1482-1535 (the C ABI this one mirrors).
 #include "decode_kernel.cuh"
+#include "decode_tc.cuh"
 #include "tensor_map.cuh"
 
 namespace crit_b200 {
@@ -272,7 +273,40 @@ static int check(const crit_b200_attend_params& p) {
     return 0;
 }
 
+// Whether the tcgen05 kernel serves a launch: E4M3 pages of 128-wide heads, at most 32 query rows a unit (columns x
+// heads of a group), splits that are whole tiles of 128 positions, the pool's size known for the tensor maps.
+static bool tc_serves(const crit_b200_attend_params& p) {
+    if (page_class(p.kind, p.page_dtype) != 2) return false;
+    if (p.head_dim != DT_D || p.value_dim != DT_D) return false;
+    if (p.columns * (p.q_heads / p.kv_heads) > 32) return false;
+    if (p.chunk % DT_N || p.chunk > DT_MAX_CHUNK) return false;
+    if (p.slots < 16 || p.slots > 0x7fffffffLL) return false;
+    if (p.n_rows > DT_MAX_LIST) return false;
+    return true;
+}
+
+static int launch_decode_tc(const crit_b200_attend_params& p, cudaStream_t s) {
+    CUtensorMap kmap, vmap;
+    if (!page_map(&kmap, p.key_pages, 2, p.head_dim, p.kv_heads, p.slots) ||
+        !page_map(&vmap, p.value_pages, 2, p.value_dim, p.kv_heads, p.slots))
+        return CRIT_B200_EUNSUPPORTED;
+    const int rows = p.columns * (p.q_heads / p.kv_heads);
+    auto fn = rows <= 8 ? decode_tc_kernel<1> : (rows <= 16 ? decode_tc_kernel<2> : decode_tc_kernel<4>);
+    cudaError_t ce = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM);
+    if (ce != cudaSuccess) return (int)ce;
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
+        return CRIT_B200_EUNSUPPORTED;
+    const int64_t most = (int64_t)p.max_splits * p.kv_heads * p.n_rows;        // units the launch can have
+    const unsigned blocks = (unsigned)(most < sms ? most : sms);               // one persistent block per SM
+    fn<<<blocks, DT_THREADS, DT_SMEM, s>>>(p, scale_mode(p.kind), kmap, vmap);
+    CRIT_CHECK_LAUNCH();
+    return 0;
+}
+
 static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
+    if (p.flags & CRIT_B200_ATTEND_TCGEN05) return tc_serves(p) ? launch_decode_tc(p, s) : CRIT_B200_EUNSUPPORTED;
     const int G = p.q_heads / p.kv_heads;
     const int rows = p.columns * G;
     const int nt = row_tiles(rows, p.value_dim);

@@ -105,6 +105,11 @@ int crit_b200_slots(const crit_b200_slots_params* params, void* stream);
                                         device from the rows' lengths, instead of one block per (split, kv head, row)
                                         slot of a 3-D grid; the same bits; at most 256 rows, else the 3-D grid */
 
+#define CRIT_B200_ATTEND_TCGEN05 8   /* the tcgen05 kernel (E4M3 page bytes straight into kind::f8f6f4 MMAs, queries and
+                                       probabilities as two E4M3 terms each) or CRIT_B200_EUNSUPPORTED: E4M3 pages of
+                                       128-wide heads, columns x group heads <= 32, chunk a multiple of 128, slots set */
+#define CRIT_B200_ATTEND_MMA_SYNC 16 /* the m16n8k16 kernel even where the tcgen05 kernel serves the launch */
+
 /* -- split-K decode / speculative-verify attention ------------------------------------------------------------------
  * Replaces paged_kv_attention.attend (paged_kv_attention/__init__.py:396-576; kernels _kernels.py:263-478 and :558-604,
  * cuda_window.cu:284-1286) behind DeviceAttention._windows (inference/attention-state/code/device_attention.py:659-704).

@@ -149,6 +149,53 @@ def test_windows_match_the_oracle(pk, kind, hq, hkv, d, dv, page):
     assert_attention_close(out, lse, want, want_lse, tokens)
 
 
+# The tcgen05 engine: E4M3 page bytes straight into the tensor cores; the queries and probabilities enter as two E4M3
+# terms each (an error below 2^-8 of each value, like bf16's own rounding), so the same bounds hold.
+@pytest.mark.parametrize("kind", ["fp8", "fp8:row", "fp8:page"])
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (56, 8), (40, 8), (4, 4), (16, 1)])
+@pytest.mark.parametrize("page,chunk", [(16, 128), (48, 256), (16, 1024)])
+def test_windows_on_tcgen05_tiles_match_the_oracle(pk, kind, hq, hkv, page, chunk):
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, hkv, 128, 128, page, [130, 64, 1, 517, 1300])
+    G = hq // hkv
+    cols = max(1, min(5, 32 // G))
+    firsts = [125, 59, 0, 400, 1290]
+    counts = [min(cols, n) for n in [5, 5, 1, 3, 5]]
+    rows, starts = [0, 1, 2, 3, 4], [0, 5, 10, 15, 20]
+    q = queries(25, hq, 128, 3)
+    lse = torch.full((25, hq), 7.0, device="cuda")
+    out = cache.attend(q, rows, starts, firsts, cols, counts=counts, lse=lse, chunk=chunk, engine="tcgen05")
+    assert pk.status() == 0
+    want, want_lse = cache.oracle(q, rows, starts, firsts, cols, counts=counts)
+    tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
+    assert_attention_close(out, lse, want, want_lse, tokens)
+
+
+@pytest.mark.parametrize("kind", ["fp8:page", "fp8:row"])
+def test_tcgen05_tiles_with_outliers_and_long_rows(pk, kind):
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, 2, 128, 128, 16, [1000, 37, 16, 2049, 5000], outliers=True)
+    q = queries(5, 16, 128, 9)      # bf16 queries split into two E4M3 terms exactly; fp16 ones keep 8 of their 11 bits
+    rows, starts, firsts = [0, 1, 2, 3, 4], [0, 1, 2, 3, 4], [999, 36, 15, 2048, 4999]
+    lse = torch.empty(5, 16, device="cuda")
+    out = cache.attend(q, rows, starts, firsts, 1, lse=lse, chunk=1024, engine="tcgen05")
+    assert pk.status() == 0
+    want, want_lse = cache.oracle(q, rows, starts, firsts, 1)
+    assert_attention_close(out, lse, want, want_lse, [0, 1, 2, 3, 4], rel=2.0 ** -7)
+
+
+def test_tcgen05_tiles_refuse_launches_they_do_not_serve(pk):
+    from helpers import Cache, queries
+    cache = Cache("bf16", 2, 128, 128, 16, [100])
+    with pytest.raises(Exception):
+        cache.attend(queries(1, 8, 128, 1), [0], [0], [99], 1, engine="tcgen05")
+    cache = Cache("fp8:page", 2, 128, 128, 16, [100])
+    with pytest.raises(Exception):
+        cache.attend(queries(1, 8, 128, 1), [0], [0], [99], 1, chunk=64, engine="tcgen05")
+    with pytest.raises(Exception):        # 9 columns x 4 heads of a group: more than 32 query rows a unit
+        cache.attend(queries(9, 8, 128, 1), [0], [0], [91], 9, engine="tcgen05")
+
+
 @pytest.mark.parametrize("kind", ["bf16", "fp8:page"])
 @pytest.mark.parametrize("chunk", [16, 64, 1024])
 def test_splits_of_any_size_fold_to_the_same_attention(pk, kind, chunk):
