@@ -217,7 +217,7 @@ def step(state, launch="both", append=True):
     pk.attend(state["d_q"], state["k"], state["v"], w["kind"], state["tables"], state["rows"], state["starts"],
               state["firsts"], w["columns"], w["page"], key_scales=state["ks"], value_scales=state["vs"],
               out=state["out"], lse=state["lse"], launch=launch, staging=state.get("staging"),
-              engine=state.get("engine"))
+              engine=state.get("engine"), chunk=state.get("chunk"))
     if state["merger"] is not None and launch == "both":
         state["merged"] = state["merger"].merge(state["out"], state["lse"])
 
@@ -279,6 +279,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--staging", default=None, choices=["tma", "cp.async"])
     ap.add_argument("--engine", default=None, choices=["mma.sync", "tcgen05"], help="the attention kernel instead of the library's choice")
+    ap.add_argument("--chunk", type=int, default=None, help="positions per split instead of the library's choice")
     ap.add_argument("--batch", type=int, default=None,
                     help="sequences per GPU instead of the workload's own (a small case for a profiler capture)")
     args = ap.parse_args()
@@ -299,7 +300,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
     state = build_state(w, device, rank, world)
-    state["staging"], state["engine"] = args.staging, args.engine
+    state["staging"], state["engine"], state["chunk"] = args.staging, args.engine, args.chunk
     torch.cuda.synchronize()
     tokens_step = state["tokens"]
     steps_are = ("slot map + KV append + one prefill launch per sequence" if w["columns"] > 64

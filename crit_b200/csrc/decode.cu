@@ -299,7 +299,7 @@ static int launch_decode_tc(const crit_b200_attend_params& p, cudaStream_t s) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
         return CRIT_B200_EUNSUPPORTED;
     const int64_t most = (int64_t)p.max_splits * p.kv_heads * p.n_rows;        // units the launch can have
-    const unsigned blocks = (unsigned)(most < sms ? most : sms);               // one persistent block per SM
+    const unsigned blocks = (unsigned)(most < 2 * sms ? most : 2 * sms);       // two persistent blocks per SM
     fn<<<blocks, DT_THREADS, DT_SMEM, s>>>(p, scale_mode(p.kind), kmap, vmap);
     CRIT_CHECK_LAUNCH();
     return 0;

@@ -2,25 +2,28 @@
 // from HBM to shared memory by TMA and from there straight into tcgen05.mma (kind::f8f6f4); no thread ever converts a
 // key or a value.
 //
-// One persistent block per SM (256 threads) walks a work list of units (window row, split of `chunk` positions, kv
-// head), built on the device from the rows' lengths.  A unit's positions stream through a ring of DT_STAGES stages as
-// tiles of 128 positions (eight TMA boxes of [16 positions][1 kv head][128 bytes] for the keys, eight for the values,
-// 128-byte swizzle: the K-major / MN-major operand layouts of the MMA), and the ring runs on across units, so HBM never
-// waits for a unit's epilogue.  Warp roles:
+// Two persistent blocks per SM (192 threads, 256 TMEM columns and about 105 KB of shared memory each) walk a work list
+// of units (window row, split of `chunk` positions, kv head), built on the device from the rows' lengths: block b takes
+// units b, b + grid, ...  A unit's positions stream through a ring of DT_STAGES stages as tiles of 128 positions (eight
+// TMA boxes of [16 positions][1 kv head][128 bytes] for the keys, eight for the values, 128-byte swizzle: the K-major /
+// MN-major operand layouts of the MMA), and the ring runs on across units, so HBM never waits for a unit's epilogue.
+// One block's chain of dependent steps per tile (scores -> softmax -> probabilities -> outputs) is long; the SM's other
+// block fills its gaps.  Warp roles:
 //   warps 0-3  softmax: thread = one TMEM lane.  Reads its scores (tcgen05.ld), applies the row's and the pages' scales,
 //              keeps the running maximum (lazily) and sum, writes its probabilities as E4M3 into the A-operand tile of the
 //              second product, rescales its output lane in TMEM when the maximum moved, and folds / writes the unit's
 //              result;
-//   warp 4     producer: page-table and scale lookups two tiles ahead, TMA loads, scales into the stage;
-//   warp 5     MMA issuer (one lane): S = Q K^T (4 MMAs of M128 N128 K32 per tile) into one of two score buffers,
-//              O += P V (4 MMAs) one tile behind, so a tile's softmax overlaps the next tile's first product;
-//   warps 6-7  query preparation for the next unit.
+//   warp 4     producer: a unit's page ids and page scales in registers, loaded one and two units ahead; TMA loads;
+//   warp 5     query preparation for the next unit, then MMA issue (one lane): S = Q K^T (4 MMAs of M128 N128 K32 per
+//              tile), O += P V (4 MMAs) one tile behind.
 // The MMA multiplies E4M3 by E4M3, so the 16-bit queries and the probabilities are each split in two E4M3 terms:
-// x * 2^e = hi + lo + (error below 2^-8 of x), hi = e4m3(x * 2^e), lo = e4m3(x * 2^e - hi), 2^e a per-row power of two
-// that puts the row's largest magnitude in [128, 256).  hi and lo are separate rows of the M = 128 operand (TMEM lanes j
-// and j + 16 of a warp's 32), so one MMA computes both terms and their sum is one shuffle.  A launch has at most 32
-// query rows per unit (columns x heads of the group): 16 rows fill a quarter of the lanes and are replicated four
-// times, each replica owning a quarter of a tile's columns (its probabilities elsewhere are zeros), 32 rows twice.
+// x * 2^e = hi + lo, hi = e4m3(x * 2^e), lo = e4m3(x * 2^e - hi), 2^e a per-row power of two that puts the row's largest
+// magnitude in [128, 256): exact for bf16 queries (8 significant bits = 4 + 4), to 2^-9 of the value for FP16 queries
+// and for the probabilities.  hi and lo are separate rows of the M = 128 operand (TMEM lanes j and j + 8 of a group of
+// 16), so one MMA computes both terms and their sum is one shuffle.  A unit has at most 32 query rows (columns x heads
+// of the group) in NRG groups of 8; a group's 16 lanes are replicated 8 / NRG times over the 128 lanes, each replica
+// owning 16 * NRG columns of a tile (its probabilities elsewhere are zeros), and the two lanes of a row share those
+// columns, so every lane does distinct softmax work.
 // The page codes enter the products exactly; the scales of the keys multiply the scores' columns, those of the values
 // are folded into the probabilities as an exponent offset (p' = 2^(s + log2 vs - m)), so the accumulators need no
 // per-page pass.  Every wait is bounded in time and polls a block-wide abort flag; a wait that runs out sets the status
@@ -43,40 +46,42 @@ namespace crit_b200 {
 
 constexpr int DT_N = 128;                 // positions a tile holds
 constexpr int DT_D = 128;                 // head width (keys and values)
-constexpr int DT_STAGES = 4;
-constexpr int DT_THREADS = 256;
-constexpr int DT_MAX_LIST = 512;          // window rows a launch lists its work for
+constexpr int DT_STAGES = 2;
+constexpr int DT_THREADS = 192;
+constexpr int DT_MAX_LIST = 256;          // window rows a launch lists its work for
 constexpr int DT_MAX_CHUNK = 2048;        // positions of a split: the producer holds a unit's page ids in registers
 constexpr int DT_NB = DT_MAX_CHUNK / 512; // ... boxes of 16 positions per lane
 constexpr int DT_KV_BYTES = DT_N * 128;   // one tile of keys (or values): 16 KB
 constexpr int DT_STAGE = 2 * DT_KV_BYTES + 1024;     // keys | values | 128 key scales, 128 value scales
 constexpr int DT_OPER = 128 * 128;        // an A operand: 128 rows of 128 bytes
-constexpr float DT_LAZY = 4.f;            // the running maximum moves only when a tile beats it by 2^4 ...
-constexpr float DT_PSHIFT = 4.f;          // ... and the probabilities are stored times 2^4: at most 2^8, inside E4M3
-constexpr uint32_t DT_COLUMNS = 512;      // TMEM: scores 0..127 and 128..255, outputs 256..383
+constexpr float DT_LAZY = 8.f;            // the running maximum moves only when a tile beats it by 2^8: a probability is
+                                          // at most 2^8, inside E4M3's range, and the largest of a row is at least 1
+constexpr uint32_t DT_COLUMNS = 256;      // TMEM: scores 0..127, outputs 128..255
+constexpr uint32_t DT_O = 128;
 constexpr uint64_t DT_WAIT_NS = 250000000ull;
 
-// shared memory (after the 1 KB alignment): Q[2] | P[2] (the unit fold's scratch too) | stages | small
+// shared memory (after the 1 KB alignment): Q | P (the unit fold's scratch too) | stages | small
 constexpr int DT_OFF_Q = 0;
-constexpr int DT_OFF_P = 2 * DT_OPER;
-constexpr int DT_OFF_STAGES = 4 * DT_OPER;
+constexpr int DT_OFF_P = DT_OPER;
+constexpr int DT_OFF_STAGES = 2 * DT_OPER;
 constexpr int DT_OFF_SMALL = DT_OFF_STAGES + DT_STAGES * DT_STAGE;
-constexpr int DT_SMALL_QFAC = 0;                              // [2][32] floats
+constexpr int DT_SMALL_QFAC = 0;                              // [2][32] floats: the rows' score factors, by the unit's parity
 constexpr int DT_SMALL_FM = 256;                              // [64] floats
 constexpr int DT_SMALL_FL = 512;                              // [64] floats
-constexpr int DT_SMALL_BARS = 768;                            // 24 mbarriers
-constexpr int DT_SMALL_TMEM = 768 + 24 * 8;                   // the TMEM address
+constexpr int DT_SMALL_BARS = 768;                            // 16 mbarriers
+constexpr int DT_SMALL_TMEM = 768 + 16 * 8;                   // the TMEM address
 constexpr int DT_SMALL_ABORT = DT_SMALL_TMEM + 4;
 constexpr int DT_SMALL_LIST = 1024;                           // unit_first [DT_MAX_LIST + 1] ints (padded to 16 bytes)
 constexpr int DT_LIST_BYTES = (DT_MAX_LIST + 4) * 4;
-constexpr int DT_SMALL_COUNT = DT_SMALL_LIST + DT_LIST_BYTES; // the rows' counts, starts, table rows [DT_MAX_LIST] ints each
+constexpr int DT_SMALL_COUNT = DT_SMALL_LIST + DT_LIST_BYTES; // the rows' counts, starts, table rows, splits: ints each
 constexpr int DT_SMALL_START = DT_SMALL_COUNT + DT_MAX_LIST * 4;
 constexpr int DT_SMALL_ROW = DT_SMALL_START + DT_MAX_LIST * 4;
-constexpr int DT_SMALL_FIRST = DT_SMALL_ROW + DT_MAX_LIST * 4;   // the rows' first positions [DT_MAX_LIST] int64
+constexpr int DT_SMALL_SPLITS = DT_SMALL_ROW + DT_MAX_LIST * 4;
+constexpr int DT_SMALL_FIRST = DT_SMALL_SPLITS + DT_MAX_LIST * 4;   // the rows' first positions [DT_MAX_LIST] int64
 constexpr int DT_SMEM = 1024 + DT_OFF_SMALL + DT_SMALL_FIRST + DT_MAX_LIST * 8;
 
-enum { DT_FULL = 0, DT_EMPTY = 4, DT_SFULL = 8, DT_SFREE = 10, DT_PFULL = 12, DT_PVDONE = 14, DT_QFULL = 16, DT_QFREE = 18,
-       DT_FOLD_A = 20, DT_FOLD_B = 21 };
+enum { DT_FULL = 0, DT_EMPTY = 2, DT_SFULL = 4, DT_SFREE = 5, DT_PFULL = 6, DT_PVDONE = 7, DT_QFULL = 8, DT_QFREE = 9,
+       DT_FOLD_A = 10, DT_FOLD_B = 11 };
 
 __device__ __forceinline__ uint32_t idesc_f8(bool b_mn_major, int M, int N) {
     uint32_t d = 0;
@@ -102,34 +107,43 @@ __device__ __forceinline__ uint32_t f16x2_to_e4m3x2(uint32_t h2) {
     asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(r) : "r"(h2));
     return r;
 }
-// hi + lo = the pair to within 2^-8 of each value (two E4M3 bytes each, the first value in the low byte).
+// hi + lo / LOSCALE = the pair to within 2^-8 of each value (two E4M3 bytes each, the first value in the low byte).
+// LOSCALE 16 (the probabilities): the lo term is stored times 16, which keeps the small ones out of E4M3's subnormals
+// (a probability down to 2^-13 of the row's reference survives); the lo rows' outputs are divided by 16 at the end.
+template <int LOSCALE>
 __device__ __forceinline__ void split_e4m3x2(float a, float b, uint32_t& hi, uint32_t& lo) {
     __half2 h = __floats2half2_rn(a, b);
     const uint32_t hw = *reinterpret_cast<uint32_t*>(&h);
     hi = f16x2_to_e4m3x2(hw);
     const uint32_t back = e4m3x2_to_f16x2(hi);
     __half2 rest = __hsub2(h, *reinterpret_cast<const __half2*>(&back));
+    if (LOSCALE != 1) rest = __hmul2(rest, __float2half2_rn((float)LOSCALE));
     lo = f16x2_to_e4m3x2(*reinterpret_cast<uint32_t*>(&rest));
 }
 
 // With CRIT_DT_PROFILE defined, block 0 prints the cycles each role spent in each kind of wait (a tuning aid).
 #ifdef CRIT_DT_PROFILE
 #define DT_TIMED(slot, expr) ([&] { const long long t0_ = clock64(); const bool r_ = (expr); prof[slot] += clock64() - t0_; return r_; }())
-#define DT_PROF_BEGIN long long prof[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0}; const long long prof_t0 = clock64(); long long prof_mark = prof_t0;
+#define DT_PROF_BEGIN long long prof[16] = {0}; const long long prof_t0 = clock64(); long long prof_mark = prof_t0;
 #define DT_PHASE(slot) { const long long now_ = clock64(); prof[slot] += now_ - prof_mark; prof_mark = now_; }
-#define DT_PROF_END(name) if (blockIdx.x == 0 && lane == 0) printf("%s warp %d: total %lld waits %lld %lld %lld %lld %lld %lld %lld phases %lld %lld %lld %lld %lld\n", name, warp, clock64() - prof_t0, prof[0], prof[1], prof[2], prof[3], prof[4], prof[5], prof[6], prof[7], prof[8], prof[9], prof[10], prof[11]);
+#define DT_COUNT(slot) prof[slot] += 1;
+#define DT_PROF_END(name) if (blockIdx.x == 0 && lane == 0) printf("%s warp %d: total %lld waits %lld %lld %lld %lld %lld %lld %lld phases %lld %lld %lld %lld %lld %lld %lld count %lld\n", name, warp, clock64() - prof_t0, prof[0], prof[1], prof[2], prof[3], prof[4], prof[5], prof[6], prof[7], prof[8], prof[9], prof[10], prof[11], prof[12], prof[13], prof[15]);
 #else
 #define DT_TIMED(slot, expr) (expr)
 #define DT_PROF_BEGIN
 #define DT_PHASE(slot)
+#define DT_COUNT(slot)
 #define DT_PROF_END(name)
 #endif
 
-// A bounded wait that also gives up when another thread of the block already did.
+// A bounded wait that also gives up when another thread of the block already did.  BACKOFF: nanoseconds to sleep
+// between polls (the roles that wait long share their issue slots with the softmax warps; those poll without a pause).
+template <int BACKOFF = 0>
 __device__ __forceinline__ bool dt_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_ns();
     do {
+        if (BACKOFF) __nanosleep(BACKOFF);
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
     } while (global_ns() - t0 < DT_WAIT_NS);
@@ -143,6 +157,7 @@ struct DtRows {
     const int* count;
     const int* start;
     const int* row;
+    const int* splits;
     const int64_t* first;
     int units;
 };
@@ -153,49 +168,45 @@ struct DtUnit {
     int64_t first, L, begin;
     const int32_t* table;
 };
-__device__ __forceinline__ void dt_unit(const crit_b200_attend_params& p, const DtRows& rows, int unit, DtUnit& u) {
-    int lo = 0, hi = p.n_rows;
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        if (rows.unit_first[mid] <= unit) lo = mid;
-        else hi = mid;
-    }
+// `cursor`: a row at or before the unit's (a block's units come in rising order, so the search is a short walk).
+__device__ __forceinline__ void dt_unit(const crit_b200_attend_params& p, const DtRows& rows, int unit, int& cursor, DtUnit& u) {
+    int lo = cursor;
+    while (rows.unit_first[lo + 1] <= unit) ++lo;
+    cursor = lo;
     u.r = lo;
     u.count = rows.count[lo];
     u.first = rows.first[lo];
     u.L = u.first + u.count;
-    u.nsplit = (int)((u.L + p.chunk - 1) / p.chunk);
-    const int local = unit - rows.unit_first[lo];
-    u.h = local % p.kv_heads;
-    u.split = local / p.kv_heads;
+    u.nsplit = rows.splits[lo];
+    const unsigned local = (unsigned)(unit - rows.unit_first[lo]);
+    u.split = (int)(local / (unsigned)p.kv_heads);
+    u.h = (int)(local - (unsigned)u.split * (unsigned)p.kv_heads);
     u.begin = (int64_t)u.split * p.chunk;
-    const int64_t end = u.begin + p.chunk < u.L ? u.begin + p.chunk : u.L;
-    u.ntiles = (int)((end - u.begin + DT_N - 1) / DT_N);
+    const int span = (int)(u.begin + p.chunk < u.L ? p.chunk : u.L - u.begin);
+    u.ntiles = (span + DT_N - 1) / DT_N;
     u.table = p.tables + (int64_t)rows.row[lo] * p.table_stride;
     u.start = rows.start[lo];
 }
 
 // A walk over this block's tiles in order: units block, block + grid, ..., each unit's tiles 0..ntiles-1.
 struct DtWalk {
-    int unit, k, i;
+    int unit, k, i, cursor;
     bool live;
     DtUnit u;
     __device__ __forceinline__ void begin(const crit_b200_attend_params& p, const DtRows& rows) {
-        unit = blockIdx.x, k = 0, i = 0;
+        unit = blockIdx.x, k = 0, i = 0, cursor = 0;
         live = unit < rows.units;
-        if (live) dt_unit(p, rows, unit, u);
+        if (live) dt_unit(p, rows, unit, cursor, u);
     }
     __device__ __forceinline__ void next(const crit_b200_attend_params& p, const DtRows& rows) {
         if (!live) return;
         if (++i < u.ntiles) return;
-        i = 0, ++k, unit += gridDim.x;
-        live = unit < rows.units;
-        if (live) dt_unit(p, rows, unit, u);
+        next_unit(p, rows);
     }
     __device__ __forceinline__ void next_unit(const crit_b200_attend_params& p, const DtRows& rows) {
         i = 0, ++k, unit += gridDim.x;
         live = unit < rows.units;
-        if (live) dt_unit(p, rows, unit, u);
+        if (live) dt_unit(p, rows, unit, cursor, u);
     }
 };
 
@@ -203,7 +214,7 @@ struct DtWalk {
 // terms), so the 128 lanes hold 8 / NRG replicas of the unit's rows, each owning 16 * NRG columns of a tile.
 // smode: 0 static multipliers, 1 a scale per (slot, kv head), 2 a scale per (page, kv head).
 template <int NRG>
-__global__ void __launch_bounds__(DT_THREADS, 1)
+__global__ void __launch_bounds__(DT_THREADS, 2)
 decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
     constexpr int REPL = 8 / NRG;         // replicas of the unit's rows
@@ -229,6 +240,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
     int* m_count = reinterpret_cast<int*>(small + DT_SMALL_COUNT);
     int* m_start = reinterpret_cast<int*>(small + DT_SMALL_START);
     int* m_row = reinterpret_cast<int*>(small + DT_SMALL_ROW);
+    int* m_splits = reinterpret_cast<int*>(small + DT_SMALL_SPLITS);
     int64_t* m_first = reinterpret_cast<int64_t*>(small + DT_SMALL_FIRST);
     auto bar = [&](int which) { return bars + (uint32_t)which * 8u; };
 
@@ -239,20 +251,20 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
     if (warp == 0) tmem_alloc(smem_addr(tmem_slot), DT_COLUMNS);
     if (tid == 32) {
         for (int s = 0; s < DT_STAGES; ++s) mbar_init(bar(DT_FULL + s), 1), mbar_init(bar(DT_EMPTY + s), 1);
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(bar(DT_SFULL + b), 1), mbar_init(bar(DT_SFREE + b), 128);
-            mbar_init(bar(DT_PFULL + b), 128), mbar_init(bar(DT_PVDONE + b), 1);
-            mbar_init(bar(DT_QFULL + b), 64), mbar_init(bar(DT_QFREE + b), 129);
-        }
+        mbar_init(bar(DT_SFULL), 1), mbar_init(bar(DT_SFREE), 128);
+        mbar_init(bar(DT_PFULL), 128), mbar_init(bar(DT_PVDONE), 1);
+        mbar_init(bar(DT_QFULL), 32);
         mbar_init(bar(DT_FOLD_A), 128), mbar_init(bar(DT_FOLD_B), 128);
         *abort_flag = 0;
         mbar_init_fence();
     }
-    for (int idx = tid; idx < 2 * DT_OPER / 16; idx += DT_THREADS) reinterpret_cast<uint4*>(pbuf)[idx] = make_uint4(0, 0, 0, 0);
+    for (int idx = tid; idx < DT_OPER / 16; idx += DT_THREADS) reinterpret_cast<uint4*>(pbuf)[idx] = make_uint4(0, 0, 0, 0);
     for (int rr = tid; rr < p.n_rows; rr += DT_THREADS) {
         int cnt = p.counts ? p.counts[rr] : p.columns;
         cnt = cnt > p.columns ? p.columns : (cnt < 0 ? 0 : cnt);
-        m_count[rr] = cnt, m_start[rr] = p.starts[rr], m_row[rr] = p.rows[rr], m_first[rr] = p.firsts[rr];
+        const int64_t first = p.firsts[rr];
+        m_count[rr] = cnt, m_start[rr] = p.starts[rr], m_row[rr] = p.rows[rr], m_first[rr] = first;
+        m_splits[rr] = cnt > 0 ? (int)((first + cnt + p.chunk - 1) / p.chunk) : 0;
     }
     fence_proxy_async();
     tc_fence_before();
@@ -261,10 +273,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
         int carry = 0;
         for (int base = 0; base < p.n_rows; base += 32) {
             const int rr = base + lane;
-            int mine = 0;
-            if (rr < p.n_rows && m_count[rr] > 0)
-                mine = (int)((m_first[rr] + m_count[rr] + p.chunk - 1) / p.chunk) * p.kv_heads;
-            int scan = mine;
+            int scan = rr < p.n_rows ? m_splits[rr] * p.kv_heads : 0;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
                 const int up = __shfl_up_sync(FULLMASK, scan, o);
@@ -279,7 +288,8 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     DtRows rows;
-    rows.unit_first = unit_first, rows.count = m_count, rows.start = m_start, rows.row = m_row, rows.first = m_first;
+    rows.unit_first = unit_first, rows.count = m_count, rows.start = m_start, rows.row = m_row, rows.splits = m_splits;
+    rows.first = m_first;
     rows.units = unit_first[p.n_rows];
     const uint32_t tpp = (uint32_t)p.page >> 4;
     int where = 0;              // which role's wait gave up
@@ -338,7 +348,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                 const uint32_t tile16 = (uint32_t)(w0.u.begin >> 4) + (uint32_t)(i * 8 + (lane & 7));
                 const int slot0 = pgb >= 0 ? (int)((int64_t)pgb * p.page + ((tile16 % tpp) << 4)) : (int)p.slots;
                 const int stage = t % DT_STAGES;
-                ok = DT_TIMED(0, dt_wait(bar(DT_EMPTY + stage), (uint32_t)((t / DT_STAGES) & 1) ^ 1u, abort_flag));
+                ok = DT_TIMED(0, dt_wait<100>(bar(DT_EMPTY + stage), (uint32_t)((t / DT_STAGES) & 1) ^ 1u, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 unsigned char* st = stages + stage * DT_STAGE;
@@ -366,80 +376,42 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                 mbar_wait(bar(DT_FULL + tt % DT_STAGES), (uint32_t)(tt / DT_STAGES) & 1u, 20000000ull);
         }
     } else if (warp == 5) {
-        // -- MMA issuer -----------------------------------------------------------------------------------------------
+        // -- query preparation and MMA issue ------------------------------------------------------------------------------
         const uint32_t idesc_s = idesc_f8(false, 128, DT_N);
         const uint32_t idesc_o = idesc_f8(true, 128, DT_D);
+        const float sl2 = p.scale * LOG2E * (smode == 0 ? p.key_multiplier : 1.f);
+        const int qt = lane & 3;
         bool ok = true, have_prev = false, prev_acc = false;
         int prev_t = 0;
         DT_PROF_BEGIN
         auto issue_pv = [&]() {             // O (+)= P V of tile prev_t
-            const int pb = prev_t & 1, pstage = prev_t % DT_STAGES;
-            ok = DT_TIMED(3, dt_wait(bar(DT_PFULL + pb), (uint32_t)(prev_t >> 1) & 1u, abort_flag));
+            const int pstage = prev_t % DT_STAGES;
+            ok = DT_TIMED(3, dt_wait<32>(bar(DT_PFULL), (uint32_t)prev_t & 1u, abort_flag));
             ok = __all_sync(FULLMASK, ok);
             if (!ok) return;
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t pa = smem_addr(pbuf + pb * DT_OPER), va = smem_addr(stages + pstage * DT_STAGE + DT_KV_BYTES);
+                const uint32_t pa = smem_addr(pbuf), va = smem_addr(stages + pstage * DT_STAGE + DT_KV_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < DT_N / 32; ++kk)
-                    umma_f8(tmem + 256, smem_desc_sw128(pa + kk * 32, 0, 1024), smem_desc_sw128(va + kk * 4096, 16, 1024),
+                    umma_f8(tmem + DT_O, smem_desc_sw128(pa + kk * 32, 0, 1024), smem_desc_sw128(va + kk * 4096, 16, 1024),
                             idesc_o, prev_acc || kk > 0);
                 umma_commit(bar(DT_EMPTY + pstage));
-                umma_commit(bar(DT_PVDONE + pb));
+                umma_commit(bar(DT_PVDONE));
             }
             __syncwarp();
         };
-        DtWalk w;
-        w.begin(p, rows);
-        int t = 0;
-        while (w.live && ok) {
-            const int b = t & 1, stage = t % DT_STAGES;
-            if (w.i == 0) ok = DT_TIMED(0, dt_wait(bar(DT_QFULL + (w.k & 1)), (uint32_t)(w.k >> 1) & 1u, abort_flag));
-            ok = ok && DT_TIMED(1, dt_wait(bar(DT_FULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
-            ok = ok && DT_TIMED(2, dt_wait(bar(DT_SFREE + b), (uint32_t)((t >> 1) & 1) ^ 1u, abort_flag));
-            ok = __all_sync(FULLMASK, ok);
-            if (!ok) break;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t qa = smem_addr(qbuf + (w.k & 1) * DT_OPER), ka = smem_addr(stages + stage * DT_STAGE);
+        // The unit's queries as the A operand: 4 lanes a row, 8 rows a pass.  Row r of the unit goes to TMEM lanes
+        // 16 * lg + (r & 7) (hi) and + 8 (lo) of every lane group lg that serves its row group.
+        auto prepare_q = [&](const DtUnit& u, int k) {
 #pragma unroll
-                for (int kk = 0; kk < DT_D / 32; ++kk)
-                    umma_f8(tmem + b * DT_N, smem_desc_sw128(qa + kk * 32, 0, 1024), smem_desc_sw128(ka + kk * 32, 0, 1024),
-                            idesc_s, kk > 0);
-                umma_commit(bar(DT_SFULL + b));
-                if (w.i == w.u.ntiles - 1) umma_commit(bar(DT_QFREE + (w.k & 1)));
-            }
-            __syncwarp();
-            if (have_prev) issue_pv();
-            have_prev = true, prev_t = t, prev_acc = w.i > 0;
-            w.next(p, rows);
-            ++t;
-        }
-        if (ok && have_prev) issue_pv();
-        DT_PROF_END("mma")
-        if (!ok) where = 0x420;
-    } else if (warp >= 6) {
-        // -- query preparation: 4 threads a row, 16 rows a pass -----------------------------------------------------------
-        const int t64 = tid - 192, qt = t64 & 3;
-        const float sl2 = p.scale * LOG2E * (smode == 0 ? p.key_multiplier : 1.f);
-        bool ok = true;
-        DtWalk w;
-        w.begin(p, rows);
-        DT_PROF_BEGIN
-        while (w.live) {
-            const int kb = w.k & 1;
-            ok = DT_TIMED(0, dt_wait(bar(DT_QFREE + kb), (uint32_t)((w.k >> 1) & 1) ^ 1u, abort_flag));
-            ok = __all_sync(FULLMASK, ok);
-            if (!ok) break;
-            unsigned char* qdst = qbuf + kb * DT_OPER;
-#pragma unroll
-            for (int ps = 0; ps < (R + 15) / 16; ++ps) {
-                const int r = ps * 16 + (t64 >> 2);
+            for (int ps = 0; ps < NRG; ++ps) {
+                const int r = ps * 8 + (lane >> 2);
                 const int col = r / G, gq = r - col * G;
                 float x[32];
-                if (r < R && col < w.u.count) {
-                    const char* src = (const char*)p.q + ((int64_t)(w.u.start + col) * p.q_stride_token +
-                                                          (int64_t)(w.u.h * G + gq) * p.q_stride_head + qt * 32) * 2;
+                if (col < u.count) {
+                    const char* src = (const char*)p.q + ((int64_t)(u.start + col) * p.q_stride_token +
+                                                          (int64_t)(u.h * G + gq) * p.q_stride_head + qt * 32) * 2;
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const uint4 v = *reinterpret_cast<const uint4*>(src + c * 16);
@@ -472,33 +444,66 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     uint32_t h0, l0, h1, l1;
-                    split_e4m3x2(x[4 * c] * up, x[4 * c + 1] * up, h0, l0);
-                    split_e4m3x2(x[4 * c + 2] * up, x[4 * c + 3] * up, h1, l1);
+                    split_e4m3x2<1>(x[4 * c] * up, x[4 * c + 1] * up, h0, l0);
+                    split_e4m3x2<1>(x[4 * c + 2] * up, x[4 * c + 3] * up, h1, l1);
                     hi[c] = h0 | (h1 << 16), lo[c] = l0 | (l1 << 16);
                 }
-                if (r < R) {
 #pragma unroll
-                    for (int rep = 0; rep < REPL; ++rep) {
-                        const int lg = rep * NRG + (r >> 3);                        // the lane group: 16 TMEM lanes
-                        const int row_hi = 16 * lg + (r & 7), row_lo = row_hi + 8;
+                for (int rep = 0; rep < REPL; ++rep) {
+                    const int row_hi = 16 * (rep * NRG + ps) + (r & 7), row_lo = row_hi + 8;
 #pragma unroll
-                        for (int c = 0; c < 2; ++c) {
-                            const int chunk = 2 * qt + c;
-                            *reinterpret_cast<uint4*>(qdst + row_hi * 128 + ((chunk ^ (row_hi & 7)) << 4)) =
-                                make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-                            *reinterpret_cast<uint4*>(qdst + row_lo * 128 + ((chunk ^ (row_lo & 7)) << 4)) =
-                                make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
-                        }
+                    for (int c = 0; c < 2; ++c) {
+                        const int chunk = 2 * qt + c;
+                        *reinterpret_cast<uint4*>(qbuf + row_hi * 128 + ((chunk ^ (row_hi & 7)) << 4)) =
+                            make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
+                        *reinterpret_cast<uint4*>(qbuf + row_lo * 128 + ((chunk ^ (row_lo & 7)) << 4)) =
+                            make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
                     }
-                    if (qt == 0) qfac[kb * 32 + r] = down * sl2;
                 }
+                if (qt == 0) qfac[(k & 1) * 32 + r] = down * sl2;
             }
             fence_proxy_async();
-            mbar_arrive(bar(DT_QFULL + kb));
-            w.next_unit(p, rows);
+            mbar_arrive(bar(DT_QFULL));
+            __syncwarp();
+        };
+        DtWalk w;
+        w.begin(p, rows);
+        int t = 0;
+        while (w.live && ok) {
+            const int stage = t % DT_STAGES;
+            if (w.i == 0) {
+                // a new unit: its queries go over the last one's once the last first product has read them
+                // (and once every softmax thread has read those scores: it then has passed the wait for the last
+                // unit's queries, so the barrier of the queries never runs two phases ahead of a waiter)
+                if (t > 0) {
+                    ok = DT_TIMED(0, dt_wait<32>(bar(DT_SFULL), (uint32_t)(t - 1) & 1u, abort_flag) &&
+                                         dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag));
+                    ok = __all_sync(FULLMASK, ok);
+                    if (!ok) break;
+                }
+                prepare_q(w.u, w.k);
+            }
+            ok = DT_TIMED(1, dt_wait<32>(bar(DT_FULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
+            ok = ok && DT_TIMED(2, dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag));
+            ok = __all_sync(FULLMASK, ok);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t qa = smem_addr(qbuf), ka = smem_addr(stages + stage * DT_STAGE);
+#pragma unroll
+                for (int kk = 0; kk < DT_D / 32; ++kk)
+                    umma_f8(tmem, smem_desc_sw128(qa + kk * 32, 0, 1024), smem_desc_sw128(ka + kk * 32, 0, 1024), idesc_s, kk > 0);
+                umma_commit(bar(DT_SFULL));
+            }
+            __syncwarp();
+            if (have_prev) issue_pv();
+            have_prev = true, prev_t = t, prev_acc = w.i > 0;
+            w.next(p, rows);
+            ++t;
         }
-        DT_PROF_END("query")
-        if (!ok) where = 0x430;
+        if (ok && have_prev) issue_pv();
+        DT_PROF_END("mma")
+        if (!ok) where = 0x420;
     } else {
         // -- softmax: thread = TMEM lane 32 * warp + lane.  A lane group is 16 lanes: lanes 0-7 hold the hi terms of 8
         //    query rows, lanes 8-15 their lo terms; group lg serves query rows 8 * (lg % NRG) .. + 7 and owns columns
@@ -513,34 +518,35 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
         const int prow = warp * 32 + lane;
         const int row_hi = prow & ~8, row_lo = row_hi | 8;
         const int cmine = part * W + (second ? CT : 0);           // this thread's first column of a tile
-        const float vmul = (smode == 0 ? p.value_multiplier : 1.f) * (1.f / 16.f);
+        const float vmul = smode == 0 ? p.value_multiplier : 1.f;
+        const float lo_unscale = second ? 1.f / 16.f : 1.f;     // this lane's outputs: the lo probabilities were stored times 16
         const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
-        float* fo = reinterpret_cast<float*>(pbuf);         // the unit's fold: [64 (lane group, row) entries][128] floats
+        float* fo = reinterpret_cast<float*>(pbuf);         // the unit's fold: [64 (lane group, row) entries][64] floats
+        unsigned char* pb_hi = pbuf + row_hi * 128;
+        unsigned char* pb_lo = pbuf + row_lo * 128;
         bool ok = true;
         DtWalk w;
         w.begin(p, rows);
         int t = 0;
         DT_PROF_BEGIN
         while (w.live && ok) {
-            const int k = w.k, kb = k & 1;
-            ok = DT_TIMED(0, dt_wait(bar(DT_QFULL + kb), (uint32_t)(k >> 1) & 1u, abort_flag));
+            const int k = w.k;
+            ok = DT_TIMED(0, dt_wait(bar(DT_QFULL), (uint32_t)k & 1u, abort_flag));
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
-            const float a_r = qfac[kb * 32 + r];
-            mbar_arrive(bar(DT_QFREE + kb));
+            const float a_r = qfac[(k & 1) * 32 + r];
             const bool valid = col < w.u.count;
             const int lastpos = valid ? (int)(w.u.first + col) : -1;
             const int first32 = w.u.first > 0x7fffffffLL ? 0x7fffffff : (int)w.u.first;
             float m_run = -INFINITY, l_run = 0.f;
             for (int i = 0; i < w.u.ntiles; ++i, ++t) {
-                const int b = t & 1, stage = t % DT_STAGES;
+                const int stage = t % DT_STAGES;
                 const int tile_pos = (int)w.u.begin + i * DT_N;
-                ok = DT_TIMED(1, dt_wait(bar(DT_SFULL + b), (uint32_t)(t >> 1) & 1u, abort_flag) &&
+                ok = DT_TIMED(1, dt_wait(bar(DT_SFULL), (uint32_t)t & 1u, abort_flag) &&
                                      dt_wait(bar(DT_FULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 tc_fence_after();
-                DT_PHASE(7)
                 if (tile_pos + DT_N > w.u.L && (w.u.L & 15)) {
                     // the row's last page is partly filled: its value rows past the last position hold whatever the
                     // page held before, and a probability of 0 times a NaN code would not be 0.  Zeros instead (the
@@ -551,28 +557,27 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                         *reinterpret_cast<uint4*>(vst + (from + (idx >> 3)) * 128 + ((idx & 7) << 4)) = make_uint4(0, 0, 0, 0);
                 }
                 // this lane's scores of the group's W columns, then the exchange: each lane of a row ends with the sums
-                // hi + lo of its own CT columns
+                // hi + lo of its own CT columns.  (tcgen05.ld wants its first column on a multiple of 32 here: 16 columns
+                // are read as the half of 32.)
                 float s[CT];
                 {
                     float mine[W];
-                    const uint32_t at = tmem + lane_base + (uint32_t)(b * DT_N + part * W);
                     if constexpr (W == 16) {
-                        // 32 columns from a 32-column boundary, of which this group's half
                         float both[32];
-                        tmem_ld32(tmem + lane_base + (uint32_t)(b * DT_N + (part >> 1) * 32), both);
+                        tmem_ld32(tmem + lane_base + (uint32_t)((part >> 1) * 32), both);
 #pragma unroll
                         for (int c = 0; c < 16; ++c) mine[c] = (part & 1) ? both[16 + c] : both[c];
                     } else {
 #pragma unroll
                         for (int q = 0; q < W / 32; ++q) {
                             float part32[32];
-                            tmem_ld32(at + 32 * q, part32);
+                            tmem_ld32(tmem + lane_base + (uint32_t)(part * W + 32 * q), part32);
 #pragma unroll
                             for (int c = 0; c < 32; ++c) mine[32 * q + c] = part32[c];
                         }
                     }
                     tc_fence_before();
-                    mbar_arrive(bar(DT_SFREE + b));
+                    mbar_arrive(bar(DT_SFREE));
 #pragma unroll
                     for (int c = 0; c < CT; ++c) {
                         const float give = second ? mine[c] : mine[c + CT];
@@ -580,7 +585,6 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                         s[c] = keep + __shfl_xor_sync(FULLMASK, give, 8);
                     }
                 }
-                DT_PHASE(8)
                 const float* scs = reinterpret_cast<const float*>(stages + stage * DT_STAGE + 2 * DT_KV_BYTES);
                 const bool mask = !valid || tile_pos + DT_N - 1 > first32;
                 float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -620,15 +624,11 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                 const float alpha = moved ? ex2(m_run - sub) : 1.f;
                 const bool rescale = moved && top != m_run && i > 0;
                 m_run = top;
-                const float sub4 = sub - DT_PSHIFT;
 
-                DT_PHASE(9)
-                // the tile's P buffer is free once the second product of two tiles back has read it
-                ok = DT_TIMED(2, dt_wait(bar(DT_PVDONE + b), (uint32_t)((t >> 1) & 1) ^ 1u, abort_flag));
+                // the P tile is free (and the outputs settled) once the second product of the tile before has landed
+                ok = DT_TIMED(2, dt_wait(bar(DT_PVDONE), (uint32_t)(t & 1) ^ 1u, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
-                unsigned char* pb_hi = pbuf + b * DT_OPER + row_hi * 128;
-                unsigned char* pb_lo = pbuf + b * DT_OPER + row_lo * 128;
                 float l_tile = 0.f;
 #pragma unroll
                 for (int g = 0; g < NGC; ++g) {
@@ -638,7 +638,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                     const int slot0 = smode == 1 ? reinterpret_cast<const int*>(scs)[cb >> 4] : -1;
 #pragma unroll
                     for (int c2 = 0; c2 < GC / 2; ++c2) {
-                        const float pa = ex2(s[g * GC + 2 * c2] - sub4), pb = ex2(s[g * GC + 2 * c2 + 1] - sub4);
+                        const float pa = ex2(s[g * GC + 2 * c2] - sub), pb = ex2(s[g * GC + 2 * c2 + 1] - sub);
                         if (smode == 1) {
                             float va = 1.f, vb = 1.f;
                             if (slot0 >= 0) {
@@ -651,7 +651,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                             psum += pa + pb;
                         }
                         uint32_t h2, l2;
-                        split_e4m3x2(pa, pb, h2, l2);
+                        split_e4m3x2<16>(pa, pb, h2, l2);
                         if (c2 & 1) wh[c2 >> 1] |= h2 << 16, wl[c2 >> 1] |= l2 << 16;
                         else wh[c2 >> 1] = h2, wl[c2 >> 1] = l2;
                     }
@@ -665,121 +665,126 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                         *reinterpret_cast<uint4*>(pb_lo + ((chunk ^ (row_lo & 7)) << 4)) = make_uint4(wl[0], wl[1], wl[2], wl[3]);
                     }
                 }
-                l_run = l_run * alpha + l_tile * (1.f / 16.f);
+                l_run = l_run * alpha + l_tile;
 
                 if (__any_sync(FULLMASK, rescale)) {
-                    // a maximum moved: the warp brings its output lanes to the new reference, once the second product
-                    // of the tile before has landed
-                    ok = DT_TIMED(3, dt_wait(bar(DT_PVDONE + ((t - 1) & 1)), (uint32_t)((t - 1) >> 1) & 1u, abort_flag));
-                    ok = __all_sync(FULLMASK, ok);
-                    if (!ok) break;
+                    // a maximum moved: the warp brings its output lanes to the new reference
+                    DT_COUNT(15)
                     tc_fence_after();
 #pragma unroll
                     for (int c4 = 0; c4 < DT_D / 32; ++c4) {
                         float o[32];
-                        tmem_ld32(tmem + lane_base + 256u + 32u * c4, o);
+                        tmem_ld32(tmem + lane_base + DT_O + 32u * c4, o);
 #pragma unroll
                         for (int j = 0; j < 32; ++j) o[j] *= alpha;
-                        tmem_st32(tmem + lane_base + 256u + 32u * c4, o);
+                        tmem_st32(tmem + lane_base + DT_O + 32u * c4, o);
                     }
                 }
                 fence_proxy_async();
                 tc_fence_before();
-                mbar_arrive(bar(DT_PFULL + b));
-                DT_PHASE(10)
+                mbar_arrive(bar(DT_PFULL));
             }
             if (!ok) break;
+            DT_PHASE(7)
 
             // -- the unit's result: wait for its last second product, fold the replicas, write ------------------------------
             const int tl = t - 1;
-            ok = DT_TIMED(4, dt_wait(bar(DT_PVDONE + (tl & 1)), (uint32_t)(tl >> 1) & 1u, abort_flag));
+            ok = DT_TIMED(4, dt_wait(bar(DT_PVDONE), (uint32_t)tl & 1u, abort_flag));
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             tc_fence_after();
             // hi + lo of the outputs: the hi lane keeps value columns 0..63, the lo lane 64..127
-            const int entry = lg * 8 + jr, swz = entry & 15;
+            float keep[64];
 #pragma unroll
             for (int c4 = 0; c4 < 2; ++c4) {
                 float oa[32], ob[32];
-                tmem_ld32(tmem + lane_base + 256u + 32u * c4, oa);
-                tmem_ld32(tmem + lane_base + 256u + 64u + 32u * c4, ob);
+                tmem_ld32(tmem + lane_base + DT_O + 32u * c4, oa);
+                tmem_ld32(tmem + lane_base + DT_O + 64u + 32u * c4, ob);
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    const float give = second ? oa[j] : ob[j];
-                    const float keep = second ? ob[j] : oa[j];
-                    oa[j] = keep + __shfl_xor_sync(FULLMASK, give, 8);
+                    const float give = (second ? oa[j] : ob[j]) * lo_unscale;
+                    const float mine = (second ? ob[j] : oa[j]) * lo_unscale;
+                    keep[32 * c4 + j] = mine + __shfl_xor_sync(FULLMASK, give, 8);
                 }
-                const int slot_base = (second ? 16 : 0) + c4 * 8;
-#pragma unroll
-                for (int f4 = 0; f4 < 8; ++f4)
-                    *reinterpret_cast<float4*>(fo + entry * 128 + (((slot_base + f4) ^ swz) << 2)) =
-                        make_float4(oa[4 * f4], oa[4 * f4 + 1], oa[4 * f4 + 2], oa[4 * f4 + 3]);
             }
+            tc_fence_before();
+            const int entry = lg * 8 + jr, swz = entry & 15;
             {
                 const float l_row = l_run + __shfl_xor_sync(FULLMASK, l_run, 8);
                 if (!second) fm[entry] = m_run, fl[entry] = l_row;
             }
-            tc_fence_before();
-            mbar_arrive(bar(DT_FOLD_A));
-            ok = DT_TIMED(5, dt_wait(bar(DT_FOLD_A), (uint32_t)k & 1u, abort_flag));
-            ok = __all_sync(FULLMASK, ok);
-            if (!ok) break;
+            DT_PHASE(8)
             const bool whole = w.u.nsplit == 1;
-            for (int idx = tid; idx < R * 32; idx += 128) {
-                const int rr = idx >> 5, f = idx & 31;
-                const int rgx = rr >> 3, jx = rr & 7;
-                const int colx = rr / G, gqx = rr - colx * G;
-                if (colx >= w.u.count) continue;
-                float top = -INFINITY;
 #pragma unroll
-                for (int pt = 0; pt < REPL; ++pt) top = fmaxf(top, fm[(pt * NRG + rgx) * 8 + jx]);
-                const float sub = top == -INFINITY ? 0.f : top;
-                float l = 0.f;
-                float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int pass = 0; pass < 2; ++pass) {          // value columns 0..63, then 64..127
+                if ((int)second == pass) {
 #pragma unroll
-                for (int pt = 0; pt < REPL; ++pt) {
-                    const int e = (pt * NRG + rgx) * 8 + jx;
-                    const float fac = ex2(fm[e] - sub);
-                    l += fl[e] * fac;
-                    const float4 v = *reinterpret_cast<const float4*>(fo + e * 128 + ((f ^ (e & 15)) << 2));
-                    o.x += v.x * fac, o.y += v.y * fac, o.z += v.z * fac, o.w += v.w * fac;
+                    for (int f4 = 0; f4 < 16; ++f4)
+                        *reinterpret_cast<float4*>(fo + entry * 64 + ((f4 ^ swz) << 2)) =
+                            make_float4(keep[4 * f4], keep[4 * f4 + 1], keep[4 * f4 + 2], keep[4 * f4 + 3]);
                 }
-                o.x *= vmul, o.y *= vmul, o.z *= vmul, o.w *= vmul;
-                const int token = w.u.start + colx, head = w.u.h * G + gqx;
-                if (whole) {
-                    const float inv = l > 0.f ? 1.f / l : 0.f;
-                    char* dst = (char*)p.out + ((int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head + f * 4) * 2;
-                    uint2 packed;
-                    if (p.q_dtype == CRIT_B200_DTYPE_BF16) {
-                        packed.x = pack2<true>(o.x * inv, o.y * inv), packed.y = pack2<true>(o.z * inv, o.w * inv);
-                    } else {
-                        packed.x = pack2<false>(o.x * inv, o.y * inv), packed.y = pack2<false>(o.z * inv, o.w * inv);
-                    }
-                    *reinterpret_cast<uint2*>(dst) = packed;
-                    if (p.lse && f == 0) p.lse[(int64_t)token * p.q_heads + head] = l > 0.f ? top * LN2 + logf(l) : -INFINITY;
-                } else {
-                    const int prow_ws = (p.offsets ? p.offsets[w.u.r] - p.offsets[0] : w.u.r * p.columns) + colx;
-                    const int64_t at = ((int64_t)prow_ws * p.q_heads + head) * p.max_splits + w.u.split;
-                    *reinterpret_cast<float4*>(p.workspace + at * DT_D + f * 4) = o;
-                    if (f == 0) {
-                        p.workspace[states * DT_D + at] = top;
-                        p.workspace[states * (DT_D + 1) + at] = l;
+                mbar_arrive(bar(DT_FOLD_A));
+                ok = DT_TIMED(5, dt_wait(bar(DT_FOLD_A), (uint32_t)pass, abort_flag));
+                ok = __all_sync(FULLMASK, ok);
+                if (!ok) break;
+#pragma unroll
+                for (int it = 0; it < R / 8; ++it) {
+                    const int idx = tid + 128 * it;
+                    const int rr = idx >> 4, f = idx & 15;
+                    const int rgx = rr >> 3, jx = rr & 7;
+                    const int colx = rr / G, gqx = rr - colx * G;
+                    if (colx < w.u.count) {
+                        float top = -INFINITY;
+#pragma unroll
+                        for (int pt = 0; pt < REPL; ++pt) top = fmaxf(top, fm[(pt * NRG + rgx) * 8 + jx]);
+                        const float sub = top == -INFINITY ? 0.f : top;
+                        float l = 0.f;
+                        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int pt = 0; pt < REPL; ++pt) {
+                            const int e = (pt * NRG + rgx) * 8 + jx;
+                            const float fac = ex2(fm[e] - sub);
+                            l += fl[e] * fac;
+                            const float4 v = *reinterpret_cast<const float4*>(fo + e * 64 + ((f ^ (e & 15)) << 2));
+                            o.x += v.x * fac, o.y += v.y * fac, o.z += v.z * fac, o.w += v.w * fac;
+                        }
+                        o.x *= vmul, o.y *= vmul, o.z *= vmul, o.w *= vmul;
+                        const int token = w.u.start + colx, head = w.u.h * G + gqx, dv = pass * 64 + f * 4;
+                        if (whole) {
+                            const float inv = l > 0.f ? 1.f / l : 0.f;
+                            char* dst = (char*)p.out + ((int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head + dv) * 2;
+                            uint2 packed;
+                            if (p.q_dtype == CRIT_B200_DTYPE_BF16) {
+                                packed.x = pack2<true>(o.x * inv, o.y * inv), packed.y = pack2<true>(o.z * inv, o.w * inv);
+                            } else {
+                                packed.x = pack2<false>(o.x * inv, o.y * inv), packed.y = pack2<false>(o.z * inv, o.w * inv);
+                            }
+                            *reinterpret_cast<uint2*>(dst) = packed;
+                            if (p.lse && dv == 0) p.lse[(int64_t)token * p.q_heads + head] = l > 0.f ? top * LN2 + logf(l) : -INFINITY;
+                        } else {
+                            const int prow_ws = (p.offsets ? p.offsets[w.u.r] - p.offsets[0] : w.u.r * p.columns) + colx;
+                            const int64_t at = ((int64_t)prow_ws * p.q_heads + head) * p.max_splits + w.u.split;
+                            *reinterpret_cast<float4*>(p.workspace + at * DT_D + dv) = o;
+                            if (dv == 0) {
+                                p.workspace[states * DT_D + at] = top;
+                                p.workspace[states * (DT_D + 1) + at] = l;
+                            }
+                        }
                     }
                 }
+                mbar_arrive(bar(DT_FOLD_B));
+                ok = DT_TIMED(6, dt_wait(bar(DT_FOLD_B), (uint32_t)pass, abort_flag));
+                ok = __all_sync(FULLMASK, ok);
+                if (!ok) break;
             }
-            mbar_arrive(bar(DT_FOLD_B));
-            ok = DT_TIMED(6, dt_wait(bar(DT_FOLD_B), (uint32_t)k & 1u, abort_flag));
-            ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
-            // the fold used the P buffers: this thread's rows back to zeros (the columns it never writes stay zero)
+            DT_PHASE(9)
+            // the fold used the P tile: this thread's row back to zeros (the columns it never writes stay zero)
 #pragma unroll
-            for (int bb = 0; bb < 2; ++bb)
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    *reinterpret_cast<uint4*>(pbuf + bb * DT_OPER + prow * 128 + c * 16) = make_uint4(0, 0, 0, 0);
+            for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(pbuf + prow * 128 + c * 16) = make_uint4(0, 0, 0, 0);
             __syncwarp();               // a row's other lane writes into this row too
             w.next_unit(p, rows);
-            DT_PHASE(11)
+            DT_PHASE(10)
         }
         DT_PROF_END("softmax")
         if (!ok) where = 0x440;
