@@ -80,8 +80,10 @@ constexpr int DT_SMALL_SPLITS = DT_SMALL_ROW + DT_MAX_LIST * 4;
 constexpr int DT_SMALL_FIRST = DT_SMALL_SPLITS + DT_MAX_LIST * 4;   // the rows' first positions [DT_MAX_LIST] int64
 constexpr int DT_SMEM = 1024 + DT_OFF_SMALL + DT_SMALL_FIRST + DT_MAX_LIST * 8;
 
-enum { DT_FULL = 0, DT_EMPTY = 2, DT_SFULL = 4, DT_SFREE = 5, DT_PFULL = 6, DT_PVDONE = 7, DT_QFULL = 8, DT_QFREE = 9,
-       DT_FOLD_A = 10, DT_FOLD_B = 11 };
+// mbarriers: a stage's keys and values land and are released separately (the keys are free once the first product
+// has read them, long before the values), so the next keys stream in while a tile's softmax runs
+enum { DT_KFULL = 0, DT_VFULL = 2, DT_KEMPTY = 4, DT_VEMPTY = 6, DT_SFULL = 8, DT_SFREE = 9, DT_PFULL = 10, DT_PVDONE = 11,
+       DT_QFULL = 12, DT_FOLD_A = 13, DT_FOLD_B = 14 };
 
 __device__ __forceinline__ uint32_t idesc_f8(bool b_mn_major, int M, int N) {
     uint32_t d = 0;
@@ -250,7 +252,10 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
     // -- setup ---------------------------------------------------------------------------------------------------------
     if (warp == 0) tmem_alloc(smem_addr(tmem_slot), DT_COLUMNS);
     if (tid == 32) {
-        for (int s = 0; s < DT_STAGES; ++s) mbar_init(bar(DT_FULL + s), 1), mbar_init(bar(DT_EMPTY + s), 1);
+        for (int s = 0; s < DT_STAGES; ++s) {
+            mbar_init(bar(DT_KFULL + s), 1), mbar_init(bar(DT_KEMPTY + s), 1);
+            mbar_init(bar(DT_VFULL + s), 1), mbar_init(bar(DT_VEMPTY + s), 1);
+        }
         mbar_init(bar(DT_SFULL), 1), mbar_init(bar(DT_SFREE), 128);
         mbar_init(bar(DT_PFULL), 128), mbar_init(bar(DT_PVDONE), 1);
         mbar_init(bar(DT_QFULL), 32);
@@ -348,22 +353,27 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                 const uint32_t tile16 = (uint32_t)(w0.u.begin >> 4) + (uint32_t)(i * 8 + (lane & 7));
                 const int slot0 = pgb >= 0 ? (int)((int64_t)pgb * p.page + ((tile16 % tpp) << 4)) : (int)p.slots;
                 const int stage = t % DT_STAGES;
-                ok = DT_TIMED(0, dt_wait<100>(bar(DT_EMPTY + stage), (uint32_t)((t / DT_STAGES) & 1) ^ 1u, abort_flag));
+                const uint32_t free_parity = (uint32_t)((t / DT_STAGES) & 1) ^ 1u;
+                unsigned char* st = stages + stage * DT_STAGE;
+                ok = DT_TIMED(0, dt_wait<100>(bar(DT_KEMPTY + stage), free_parity, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
-                unsigned char* st = stages + stage * DT_STAGE;
+                if (lane == 0) mbar_expect_tx(bar(DT_KFULL + stage), (uint32_t)DT_KV_BYTES);
+                __syncwarp();
+                if (lane < 8) tma_load_3d(smem_addr(st) + lane * 2048, &kmap, 0, w0.u.h, slot0, bar(DT_KFULL + stage));
+                // the values, and with them the tile's scales (read by the softmax, which ends before the values are free)
+                ok = DT_TIMED(1, dt_wait<100>(bar(DT_VEMPTY + stage), free_parity, abort_flag));
+                ok = __all_sync(FULLMASK, ok);
+                if (!ok) break;
                 float* scs = reinterpret_cast<float*>(st + 2 * DT_KV_BYTES);
                 if (lane < 8) {
                     if (smode == 2) scs[lane] = ksb, scs[128 + lane] = vsb;
                     else if (smode == 1) reinterpret_cast<int*>(scs)[lane] = pgb >= 0 ? slot0 : -1;
                 }
                 __syncwarp();
-                if (lane == 0) mbar_expect_tx(bar(DT_FULL + stage), 2u * DT_KV_BYTES);
+                if (lane == 0) mbar_expect_tx(bar(DT_VFULL + stage), (uint32_t)DT_KV_BYTES);
                 __syncwarp();
-                if (lane < 8) {
-                    tma_load_3d(smem_addr(st) + lane * 2048, &kmap, 0, w0.u.h, slot0, bar(DT_FULL + stage));
-                    tma_load_3d(smem_addr(st) + DT_KV_BYTES + lane * 2048, &vmap, 0, w0.u.h, slot0, bar(DT_FULL + stage));
-                }
+                if (lane < 8) tma_load_3d(smem_addr(st) + DT_KV_BYTES + lane * 2048, &vmap, 0, w0.u.h, slot0, bar(DT_VFULL + stage));
             }
 #pragma unroll
             for (int j = 0; j < DT_NB; ++j) pg0[j] = pg1[j], ks0[j] = ks1[j], vs0[j] = vs1[j], pg1[j] = pg2[j];
@@ -372,8 +382,10 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
         DT_PROF_END("producer")
         if (!ok) {              // leaving early: the copies in flight land first (bounded)
             where = 0x410;
-            for (int tt = t > DT_STAGES ? t - DT_STAGES : 0; tt < t; ++tt)
-                mbar_wait(bar(DT_FULL + tt % DT_STAGES), (uint32_t)(tt / DT_STAGES) & 1u, 20000000ull);
+            for (int tt = t > DT_STAGES ? t - DT_STAGES : 0; tt <= t; ++tt) {
+                mbar_wait(bar(DT_KFULL + tt % DT_STAGES), (uint32_t)(tt / DT_STAGES) & 1u, 20000000ull);
+                if (tt < t) mbar_wait(bar(DT_VFULL + tt % DT_STAGES), (uint32_t)(tt / DT_STAGES) & 1u, 20000000ull);
+            }
         }
     } else if (warp == 5) {
         // -- query preparation and MMA issue ------------------------------------------------------------------------------
@@ -386,7 +398,8 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
         DT_PROF_BEGIN
         auto issue_pv = [&]() {             // O (+)= P V of tile prev_t
             const int pstage = prev_t % DT_STAGES;
-            ok = DT_TIMED(3, dt_wait<32>(bar(DT_PFULL), (uint32_t)prev_t & 1u, abort_flag));
+            ok = DT_TIMED(3, dt_wait<32>(bar(DT_PFULL), (uint32_t)prev_t & 1u, abort_flag)) &&
+                 dt_wait<32>(bar(DT_VFULL + pstage), (uint32_t)(prev_t / DT_STAGES) & 1u, abort_flag);
             ok = __all_sync(FULLMASK, ok);
             if (!ok) return;
             tc_fence_after();
@@ -396,7 +409,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                 for (int kk = 0; kk < DT_N / 32; ++kk)
                     umma_f8(tmem + DT_O, smem_desc_sw128(pa + kk * 32, 0, 1024), smem_desc_sw128(va + kk * 4096, 16, 1024),
                             idesc_o, prev_acc || kk > 0);
-                umma_commit(bar(DT_EMPTY + pstage));
+                umma_commit(bar(DT_VEMPTY + pstage));
                 umma_commit(bar(DT_PVDONE));
             }
             __syncwarp();
@@ -483,7 +496,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                 }
                 prepare_q(w.u, w.k);
             }
-            ok = DT_TIMED(1, dt_wait<32>(bar(DT_FULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
+            ok = DT_TIMED(1, dt_wait<32>(bar(DT_KFULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
             ok = ok && DT_TIMED(2, dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag));
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
@@ -494,6 +507,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                 for (int kk = 0; kk < DT_D / 32; ++kk)
                     umma_f8(tmem, smem_desc_sw128(qa + kk * 32, 0, 1024), smem_desc_sw128(ka + kk * 32, 0, 1024), idesc_s, kk > 0);
                 umma_commit(bar(DT_SFULL));
+                umma_commit(bar(DT_KEMPTY + stage));
             }
             __syncwarp();
             if (have_prev) issue_pv();
@@ -543,7 +557,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                 const int stage = t % DT_STAGES;
                 const int tile_pos = (int)w.u.begin + i * DT_N;
                 ok = DT_TIMED(1, dt_wait(bar(DT_SFULL), (uint32_t)t & 1u, abort_flag) &&
-                                     dt_wait(bar(DT_FULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
+                                     dt_wait(bar(DT_VFULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 tc_fence_after();
