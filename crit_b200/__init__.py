@@ -26,7 +26,7 @@ import torch
 from . import _lib
 
 __all__ = ["KINDS", "MAX_COLUMNS", "attend", "chunk_for", "gather", "merge_shards", "owner", "partitions", "parts_for",
-           "piece_size", "prefill", "prefill_serves", "release", "slots_at", "status", "tile_for", "workspace_floats", "write"]
+           "piece_size", "prefill", "prefill_serves", "release", "slots_at", "status", "tcgen05_serves", "tile_for", "workspace_floats", "write"]
 
 KINDS = {"bf16": 0, "fp16": 0, "fp8": 1, "fp8:row": 2, "int8": 3, "fp8:page": 4}
 MAX_COLUMNS = 64            # columns of one row a launch reads
@@ -138,6 +138,14 @@ def chunk_for(head_dim, value_dim, heads, kv_heads, page, kind="bf16"):
     """Positions per split of every launch over a cache of this geometry (a multiple of 16): fixed per cache, never by
     the batch, so a column's bits are the same alone and in any window."""
     return DEFAULT_CHUNK
+
+
+def tcgen05_serves(kind, head_dim, value_dim, heads, kv_heads, columns, chunk, rows=1):
+    """Whether attend(engine="tcgen05") takes a launch: E4M3 pages of 128-wide heads, at most 32 query rows a unit
+    (columns x heads of a kv head's group), splits of whole 128-position tiles up to 2,048 positions, up to 256 window
+    rows (the same test the library makes: decode.cu, tc_serves)."""
+    return (str(kind).startswith("fp8") and head_dim == 128 and value_dim == 128 and columns * (heads // kv_heads) <= 32
+            and chunk % 128 == 0 and chunk <= 2048 and rows <= 256)
 
 
 def parts_for(positions, chunk):

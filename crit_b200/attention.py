@@ -33,14 +33,20 @@ class Windows:
 class DeviceAttention:
     def __init__(self, kernels=None, mode="auto", int8_qk=False, decode="split", partitions=0, piece=0, device=None,
                  kernels_mib=128, flashinfer="off", flashinfer_mib=128, prompt_reader="prefill", reader="split",
-                 latent=None, scratch=None, chunk=0):
+                 latent=None, scratch=None, chunk=0, window_engine="mma.sync"):
         """kernels: the crit_b200 module (default).  partitions: the most splits of a partial row (0: what the tables
         need); chunk: positions per split (0: the kernels' rule).  kernels_mib: the most partials a launch takes from
         `scratch` (the engine's Scratch, crit_plugins.memory) when one is given.  prompt_reader: "prefill" or "decode".
+        window_engine: "mma.sync" (the m16n8k16 kernel: a column's bits are the same alone and in any window) or
+        "tcgen05" (E4M3 pages go straight into tcgen05.mma wherever that kernel serves a launch: faster on verify windows,
+        and a column's bits then depend on the window it is read in).
         mode "torch", decode "flashinfer", flashinfer "auto", int8_qk and latent are the reference's other readers: not
         served here."""
         if mode == "torch" or decode != "split" or flashinfer != "off" or int8_qk or latent is not None:
             raise ValueError("crit_b200 serves its own CUDA kernels only (mode auto, decode split, flashinfer off)")
+        if window_engine not in ("mma.sync", "tcgen05"):
+            raise ValueError(f"window_engine is mma.sync or tcgen05, not {window_engine!r}")
+        self.window_engine = window_engine
         if prompt_reader not in ("prefill", "decode"):
             raise ValueError(f"prompt_reader is prefill or decode, not {prompt_reader!r}")
         if kernels is None:
@@ -55,14 +61,16 @@ class DeviceAttention:
 
     # -- facts -----------------------------------------------------------------------------------------------------------
     def facts(self):
-        return {"reader": "crit_b200: a row's positions in contiguous splits of one chunk per pool, folded in split order; "
-                          "a column's bits are the same alone and in any window",
+        return {"reader": "crit_b200: a row's positions in contiguous splits of one chunk per pool, folded in split order; " +
+                          ("a column's bits are the same alone and in any window" if self.window_engine == "mma.sync" else
+                           "E4M3 pages through tcgen05.mma where served: a column's bits depend on its window"),
                 "prompt_reads": "through the prefill kernel" if self.prompt_reader == "prefill" else
                                 "in the decode's reduction (pieces of up to 64 columns)",
                 "split_kv_wide_windows": "16- or 32-row tiles; wider windows read their pages once per tile"}
 
     def exactness(self):
-        return {"decode": "row-exact", "prompt": "exact" if self.prompt_reader == "decode" else "repeatable"}
+        return {"decode": "row-exact" if self.window_engine == "mma.sync" else "repeatable",
+                "prompt": "exact" if self.prompt_reader == "decode" else "repeatable"}
 
     def close(self):
         self._steps.clear()
@@ -145,6 +153,13 @@ class DeviceAttention:
             most = max((cut.stop - cut.start) * meta.columns if tokens is None else tokens for cut, tokens in launches)
             import torch
             workspace = self.scratch.take(min(self.partial_bytes, 4 * per * most)).view(torch.float32)
+
+        def engine(rows):
+            if self.window_engine == "tcgen05" and kernels.tcgen05_serves(pool.dtype, pool.head_dim, pool.value_dim, q.shape[1],
+                                                                         pool.kv_heads, meta.columns, chunk, rows):
+                return "tcgen05"
+            return None
+
         for cut, tokens in launches:
             part = (lambda t: t[cut]) if not cut.start else (lambda t: t[cut].clone())
             offsets = part(meta.offsets) if meta.offsets is not None and tokens is not None else None
@@ -153,7 +168,8 @@ class DeviceAttention:
                            counts=part(meta.counts) if meta.counts is not None else None, offsets=offsets,
                            tokens=tokens if offsets is not None else None,
                            key_scales=pages[2] if scaled else None, value_scales=pages[3] if scaled else None,
-                           multipliers=multipliers, scale=scale, chunk=chunk, out=out, lse=found, workspace=workspace)
+                           multipliers=multipliers, scale=scale, chunk=chunk, out=out, lse=found, workspace=workspace,
+                           engine=engine(cut.stop - cut.start))
 
     # -- prompt rows -----------------------------------------------------------------------------------------------------
     def _prompts(self, layer, q, pool, batch, rows, scale, out, found):

@@ -415,31 +415,39 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
             __syncwarp();
         };
         // The unit's queries as the A operand: 4 lanes a row, 8 rows a pass.  Row r of the unit goes to TMEM lanes
-        // 16 * lg + (r & 7) (hi) and + 8 (lo) of every lane group lg that serves its row group.
-        auto prepare_q = [&](const DtUnit& u, int k) {
+        // 16 * lg + (r & 7) (hi) and + 8 (lo) of every lane group lg that serves its row group.  The global loads are
+        // issued a unit ahead (load_q), the split and the stores happen at the unit's start (store_q).
+        uint4 raw[NRG][4];
+        auto load_q = [&](const DtWalk& wq) {
 #pragma unroll
             for (int ps = 0; ps < NRG; ++ps) {
                 const int r = ps * 8 + (lane >> 2);
                 const int col = r / G, gq = r - col * G;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) raw[ps][c] = make_uint4(0, 0, 0, 0);
+                if (wq.live && col < wq.u.count) {
+                    const char* src = (const char*)p.q + ((int64_t)(wq.u.start + col) * p.q_stride_token +
+                                                          (int64_t)(wq.u.h * G + gq) * p.q_stride_head + qt * 32) * 2;
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) raw[ps][c] = *reinterpret_cast<const uint4*>(src + c * 16);
+                }
+            }
+        };
+        auto store_q = [&](int k) {
+#pragma unroll
+            for (int ps = 0; ps < NRG; ++ps) {
+                const int r = ps * 8 + (lane >> 2);
                 float x[32];
-                if (col < u.count) {
-                    const char* src = (const char*)p.q + ((int64_t)(u.start + col) * p.q_stride_token +
-                                                          (int64_t)(u.h * G + gq) * p.q_stride_head + qt * 32) * 2;
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const uint4 v = *reinterpret_cast<const uint4*>(src + c * 16);
-                        const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t wds[4] = {raw[ps][c].x, raw[ps][c].y, raw[ps][c].z, raw[ps][c].w};
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float2 f;
-                            if (p.q_dtype == CRIT_B200_DTYPE_BF16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wds[e]));
-                            else f = __half22float2(*reinterpret_cast<const __half2*>(&wds[e]));
-                            x[c * 8 + 2 * e] = f.x, x[c * 8 + 2 * e + 1] = f.y;
-                        }
+                    for (int e = 0; e < 4; ++e) {
+                        float2 f;
+                        if (p.q_dtype == CRIT_B200_DTYPE_BF16) f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wds[e]));
+                        else f = __half22float2(*reinterpret_cast<const __half2*>(&wds[e]));
+                        x[c * 8 + 2 * e] = f.x, x[c * 8 + 2 * e + 1] = f.y;
                     }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) x[c] = 0.f;
                 }
                 float amax = 0.f;
 #pragma unroll
@@ -481,6 +489,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
         };
         DtWalk w;
         w.begin(p, rows);
+        load_q(w);
         int t = 0;
         while (w.live && ok) {
             const int stage = t % DT_STAGES;
@@ -494,13 +503,26 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                     ok = __all_sync(FULLMASK, ok);
                     if (!ok) break;
                 }
-                prepare_q(w.u, w.k);
+                store_q(w.k);
+                {
+                    DtWalk after = w;           // the next unit's queries start their way from global memory now
+                    after.next_unit(p, rows);
+                    load_q(after);
+                }
+                DT_PHASE(7)
+                // the last unit's final second product goes first: its epilogue waits for it
+                if (have_prev) {
+                    issue_pv();
+                    have_prev = false;
+                    if (!ok) break;
+                }
             }
             ok = DT_TIMED(1, dt_wait<32>(bar(DT_KFULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
             ok = ok && DT_TIMED(2, dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag));
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             tc_fence_after();
+            DT_PHASE(8)
             if (lane == 0) {
                 const uint32_t qa = smem_addr(qbuf), ka = smem_addr(stages + stage * DT_STAGE);
 #pragma unroll
@@ -510,7 +532,9 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                 umma_commit(bar(DT_KEMPTY + stage));
             }
             __syncwarp();
+            DT_PHASE(9)
             if (have_prev) issue_pv();
+            DT_PHASE(10)
             have_prev = true, prev_t = t, prev_acc = w.i > 0;
             w.next(p, rows);
             ++t;
@@ -545,6 +569,8 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
         DT_PROF_BEGIN
         while (w.live && ok) {
             const int k = w.k;
+            DtWalk after = w;                   // the unit after this one, found while this one's first scores are on their way
+            after.next_unit(p, rows);
             ok = DT_TIMED(0, dt_wait(bar(DT_QFULL), (uint32_t)k & 1u, abort_flag));
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
@@ -797,7 +823,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
 #pragma unroll
             for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(pbuf + prow * 128 + c * 16) = make_uint4(0, 0, 0, 0);
             __syncwarp();               // a row's other lane writes into this row too
-            w.next_unit(p, rows);
+            w = after;
             DT_PHASE(10)
         }
         DT_PROF_END("softmax")

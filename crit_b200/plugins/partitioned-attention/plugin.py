@@ -16,5 +16,6 @@ def create(context, options, parts):
     form = DeviceAttention(None, "auto", partitions=options.get("partitions", 0), piece=options.get("piece", 0),
                            device=getattr(context, "device", None), kernels_mib=options.get("workspace_mib", 128),
                            prompt_reader="prefill" if reader == "auto" else reader,
-                           scratch=getattr(context, "scratch", None))
+                           scratch=getattr(context, "scratch", None),
+                           window_engine=options.get("window_engine", "mma.sync"))
     return PartitionedAttention(parts["kv_cache"], options, form)

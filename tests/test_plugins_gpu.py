@@ -138,6 +138,31 @@ def test_a_decode_step_and_a_verify_window_match_the_oracle(dtype):
         assert torch.equal(attention.forward(0, q[first:first + count], pool, alone), out[first:first + count])
 
 
+def test_verify_windows_through_the_tcgen05_engine_match_the_oracle():
+    """window_engine tcgen05: the verify windows it serves go through the tcgen05 kernel (within the bounds, not the
+    same bits as the m16n8k16 kernel), the launches it does not serve fall back."""
+    from crit_b200.attention import DeviceAttention, PartitionedAttention
+    from helpers import assert_attention_close
+    kv, plain = parts()
+    fast = PartitionedAttention(kv, {"world": 2, "page_size": 256}, DeviceAttention(device="cuda", window_engine="tcgen05"))
+    assert fast.exactness()["decode"] == "repeatable" and plain.exactness()["decode"] == "row-exact"
+    pool = kv.pool([0], 4, 128, 16 * 400, "cuda", "fp8:page")
+    for s, n in {"a": 700, "b": 64, "d": 2100}.items():
+        pool.open(s)
+        step(pool, [(s, 0, n)], seed=len(s) + n)
+        pool.keep(s, n)
+    batch, _, _ = step(pool, [("a", 700, 5), ("b", 64, 2), ("d", 2100, 4)], seed=77)
+    q = torch.randn(batch.tokens, 24, 128, generator=torch.Generator().manual_seed(5)).bfloat16().cuda()
+    out, lse = fast.forward(0, q, pool, batch, lse=True)
+    want, want_lse = oracle_rows(pool, batch, q)
+    assert_attention_close(out, lse, want, want_lse, list(range(batch.tokens)))
+    assert torch.equal(fast.forward(0, q, pool, batch), out)
+    other = plain.forward(0, q, pool, batch)
+    torch.testing.assert_close(out.float(), other.float(), atol=1e-2, rtol=2e-2)
+    import crit_b200
+    assert crit_b200.status() == 0
+
+
 def test_a_prompt_row_past_the_window_is_causal_over_its_own_chunk():
     from helpers import assert_attention_close
     kv, attention = parts()
