@@ -408,8 +408,8 @@ def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scale
             sinks=None, sliding=0, splits=None, workspace=None, derive=None, engine=None):
     """A prompt chunk of one sequence: q [T][heads][dim] at positions position.. (their keys and values written),
     table [pages] int32 -> out [T][heads][dim] in q's dtype (and lse [T][heads] FP32 when given), causal.  position: an
-    int, or a one-element int64 device tensor read on the device.  engine: None or "mma.sync" (m16n8k16 tiles, every
-    page kind) or "tcgen05" (tcgen05.mma tiles with TMEM accumulators: 16-bit pages of 128-wide heads only).
+    int, or a one-element int64 device tensor read on the device.  engine: None (tcgen05.mma tiles with TMEM accumulators
+    for 16-bit pages of 128-wide heads, m16n8k16 tiles otherwise), "mma.sync" or "tcgen05" (refused where not served).
     Reference: paged_kv_attention/__init__.py:1245-1332."""
     _refuse(int8_qk=int8_qk, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
     k_kind = _check_kind(kind, key_scales)

@@ -374,7 +374,7 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_prefill(const cr
     // tcgen05 tiles: 16-bit pages of 128-wide heads, with the pool's size known for the tensor maps
     const bool tc_serves = p.kind == CRIT_B200_KIND_16BIT && p.head_dim == TC_D && p.value_dim == TC_D && p.slots >= 16 && p.slots <= 0x7fffffffLL;
     if ((p.flags & CRIT_B200_PREFILL_TCGEN05) && !tc_serves) return CRIT_B200_EUNSUPPORTED;
-    if (tc_serves && (p.flags & CRIT_B200_PREFILL_TCGEN05)) {
+    if (tc_serves && !(p.flags & CRIT_B200_PREFILL_MMA_SYNC)) {
         const bool bf16 = p.page_dtype == CRIT_B200_DTYPE_BF16;
         CUtensorMap kmap, vmap;
         if (page_map(&kmap, p.key_pages, bf16 ? 0 : 1, p.head_dim, p.kv_heads, p.slots) &&

@@ -200,7 +200,8 @@ int crit_b200_merge_shards(const crit_b200_merge_shards_params* params, void* st
  * position.. (position_ptr, a device int64, wins over position when not NULL) over its page table, causal; the
  * chunk's keys and values are in the pages already.  16-bit pages of 128-wide heads run on tcgen05 tensor-core tiles
  * with TMEM accumulators (TMA-staged pages); every other geometry on m16n8k16 tiles. */
-#define CRIT_B200_PREFILL_MMA_SYNC 1   /* the m16n8k16 kernel (also what 0 selects) */
+#define CRIT_B200_PREFILL_MMA_SYNC 1   /* the m16n8k16 kernel even where the tcgen05 kernel serves the geometry (0: tcgen05
+                                          tiles for 16-bit pages of 128-wide heads, m16n8k16 tiles otherwise) */
 #define CRIT_B200_PREFILL_TCGEN05  2   /* the tcgen05 kernel or CRIT_B200_EUNSUPPORTED */
 
 typedef struct crit_b200_prefill_params {
