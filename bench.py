@@ -222,6 +222,19 @@ def step(state, launch="both", append=True):
         state["merged"] = state["merger"].merge(state["out"], state["lse"])
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of the decode launch, from one ncu capture per workload (profiles/): the
+# captured launch's traffic over its algorithmic bytes.  Traffic grows in proportion to the KV bytes (every byte is read
+# once; the writes are the partial states, a fixed number per 1,024 positions), so a launch's traffic is its algorithmic
+# bytes times the ratio.  None where no capture was made.
+TRAFFIC_RATIO = {("c2", None): (540.9e6 + 9.7e6) / 537.9e6,            # decode_kernel, configs[1] at full size
+                 ("c5", "tcgen05"): (167.9e6 + 6.3e6) / 167.0e6}       # decode_tc_kernel<4>, configs[4] at 8 sequences
+
+
+def traffic(args, w, state):
+    ratio = TRAFFIC_RATIO.get((args.workload, state.get("engine")))
+    return None if ratio is None or args.staging else ratio * state["kv_bytes"]
+
+
 def timed(fn, steps, warmup, stream):
     for _ in range(warmup):
         fn()
@@ -401,7 +414,7 @@ def main():
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_source, "us_per_launch": decode_step_s * 1e6,
                          "merge_us_per_launch": merge_s / max(20, args.steps // 4) * 1e6,
-                         "algorithmic_bytes_per_launch": state["kv_bytes"], "traffic": None},
+                         "algorithmic_bytes_per_launch": state["kv_bytes"], "traffic": traffic(args, w, state)},
             "graph_replay": graph is not None}
     if w["columns"] > 64:        # a dense contraction: the roofline is the tensor cores'
         cols, hq, d = w["columns"], w["hq"], w["d"]
