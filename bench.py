@@ -235,6 +235,20 @@ def traffic(args, w, state):
     return None if ratio is None or args.staging else ratio * state["kv_bytes"]
 
 
+def leave():
+    """The ranks leave together with nothing in flight; a communicator that will not close within 20 s (one whose
+    all-gather sits in a captured graph has done that) does not keep the launcher waiting."""
+    import torch.distributed as dist
+    sys.stdout.flush()
+    watchdog = threading.Timer(20.0, lambda: os._exit(0))
+    watchdog.daemon = True
+    watchdog.start()
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
+    watchdog.cancel()
+
+
 def timed(fn, steps, warmup, stream):
     for _ in range(warmup):
         fn()
@@ -391,8 +405,8 @@ def main():
     else:
         e2e_step_s, kv_total, tokens_total = e2e_s / e2e_steps, float(state["kv_bytes"]), float(tokens_step)
     if rank != 0:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+        graph = None
+        leave()
         return
     per_step = seconds / args.steps
     peak, peak_source = peaks()
@@ -436,10 +450,10 @@ def main():
     if world == 1:
         gbs, sample, spent, threads = cpu_reference(w, state, budget_s=args.cpu_seconds)
         line["cpu_baseline"] = {"value": gbs, "unit": unit, "cores": threads, "kind": "port", "sample": sample}
-    print(json.dumps(line))
+    print(json.dumps(line), flush=True)
     if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+        graph = None
+        leave()
 
 
 if __name__ == "__main__":
