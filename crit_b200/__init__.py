@@ -125,9 +125,10 @@ def _status_word(device):
 
 
 def status(device=None):
-    """0, or what a kernel recorded on `device` since load: 1 = a TMA copy's mbarrier wait ran out (that launch wrote
-    nothing for the block concerned), 0x100/0x200/0x300 + tile = a wait of the tcgen05 prefill kernel (loads/scores/outputs) ran out.  Reads the device word (one
-    wait)."""
+    """0, or what a kernel recorded on `device` since load, when one of its bounded waits ran out (the block concerned
+    wrote nothing): 1 = a TMA copy of the m16n8k16 decode kernel; 0x110 / 0x120 / 0x140 = the producer / MMA / softmax
+    warps of the tcgen05 prefill kernel (0x1ff: its shared memory was not 1 KB aligned); 0x410 / 0x420 / 0x440 = the
+    producer / MMA / softmax warps of the tcgen05 decode kernel.  Reads the device word (one synchronisation)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     found = _status.get(str(device))
     return 0 if found is None else int(found.item())

@@ -494,9 +494,15 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
         while (w.live && ok) {
             const int stage = t % DT_STAGES;
             if (w.i == 0) {
-                // a new unit: its queries go over the last one's once the last first product has read them
-                // (and once every softmax thread has read those scores: it then has passed the wait for the last
-                // unit's queries, so the barrier of the queries never runs two phases ahead of a waiter)
+                // A new unit.  The last unit's final second product goes first (its epilogue waits for it: by then every
+                // softmax thread has read the last scores and has passed the wait for the last unit's queries, so the
+                // barrier of the queries never runs two phases ahead of a waiter); then this unit's queries go over the
+                // last one's, while the softmax warps are busy with that epilogue.
+                if (have_prev) {
+                    issue_pv();
+                    have_prev = false;
+                    if (!ok) break;
+                }
                 if (t > 0) {
                     ok = DT_TIMED(0, dt_wait<32>(bar(DT_SFULL), (uint32_t)(t - 1) & 1u, abort_flag) &&
                                          dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag));
@@ -510,12 +516,6 @@ decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_
                     load_q(after);
                 }
                 DT_PHASE(7)
-                // the last unit's final second product goes first: its epilogue waits for it
-                if (have_prev) {
-                    issue_pv();
-                    have_prev = false;
-                    if (!ok) break;
-                }
             }
             ok = DT_TIMED(1, dt_wait<32>(bar(DT_KFULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
             ok = ok && DT_TIMED(2, dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag));

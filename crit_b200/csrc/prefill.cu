@@ -383,7 +383,7 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_prefill(const cr
             cudaError_t ce = cudaFuncSetAttribute((const void*)tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
             if (ce != cudaSuccess) return (int)ce;
             dim3 grid((unsigned)((p.tokens * G + TC_ROWS - 1) / TC_ROWS), (unsigned)p.kv_heads);
-            tc<<<grid, TC_ROWS, TC_SMEM, (cudaStream_t)stream>>>(p, kmap, vmap, p.status);
+            tc<<<grid, TC_THREADS, TC_SMEM, (cudaStream_t)stream>>>(p, kmap, vmap, p.status);
             CRIT_CHECK_LAUNCH();
             return 0;
         }

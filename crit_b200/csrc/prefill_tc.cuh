@@ -1,20 +1,22 @@
-// Chunked prefill on the fifth-generation tensor cores: tcgen05.mma with the accumulators in tensor memory.
+// Chunked prefill on the fifth-generation tensor cores: tcgen05.mma with the accumulators in tensor memory, in a
+// warp-specialised pipeline.
 //
 // A block holds 128 query rows (token-major (token, head of the kv head's group) pairs: a GQA group shares the keys and
-// values it reads) and walks the sequence's positions in tiles of 64 (four pages of 16).  Per tile:
-//   1. one thread issues the TMA tiled loads of the NEXT tile's pages (boxes of [16 positions][1 head][64 values],
-//      128-byte swizzle: exactly the K-major / MN-major operand layouts the MMA reads) into the other stage;
-//   2. one thread issues S = Q K^T: eight tcgen05.mma (M 128, N 64, K 16) from shared-memory descriptors into TMEM
-//      columns 0..63, and commits to an mbarrier;
-//   3. every thread owns one query row (= one TMEM lane): it reads its 64 scores with tcgen05.ld, masks the tile that
-//      straddles its own position, updates its running maximum and sum, and writes its probabilities as bf16/fp16 into
-//      shared memory in the A-operand layout (over the key tile, which is dead by then);
-//   4. when a row's maximum moved (lazily: by more than 2^8), the rows' partial outputs in TMEM columns 64..191 are
-//      rescaled with tcgen05.ld / tcgen05.st;
-//   5. one thread issues O += P V: four tcgen05.mma (M 128, N 128, K 16), V as the MN-major B operand, and commits.
-// Two blocks share an SM (99 KB of shared memory, 256 TMEM columns each), so one block's softmax overlaps the other's
-// MMAs.  Every wait is bounded; a wait that runs out sets the status word, and the block frees its TMEM and leaves
-// without writing.
+// values it reads) and walks the sequence's positions in tiles of 64 (four pages of 16).  Warp roles:
+//   warps 0-3  softmax: thread = one query row = one TMEM lane.  It reads its 64 scores of a tile (tcgen05.ld), masks the
+//              tile that straddles its own position, updates its running maximum (lazily: when beaten by 2^8) and sum,
+//              writes its probabilities as bf16/fp16 in the A-operand layout, and rescales its output lane in TMEM when
+//              its maximum moved;
+//   warp 4     producer: the next 32 boxes' page ids in registers, a batch ahead; TMA tiled loads (boxes of
+//              [16 positions][1 head][64 values], 128-byte swizzle: exactly the K-major / MN-major operand layouts the
+//              MMA reads) into a ring of two stages whose keys and values land and free separately (the keys are
+//              free once the first product has read them, so the next keys stream in during a tile's softmax);
+//   warp 5     MMA issue (one lane): S = Q K^T as eight tcgen05.mma (M 128, N 64, K 16) into one of TWO score buffers
+//              (TMEM columns 0..63 and 64..127), O += P V as four (M 128, N 128, K 16, V as the MN-major B operand) into
+//              columns 128..255, one tile behind: a tile's softmax overlaps the next tile's first product.
+// Two blocks share an SM (112 KB of shared memory, 256 TMEM columns each).  Every wait is bounded in time and polls a
+// block-wide abort flag; a wait that runs out sets the status word, and the block frees its TMEM and leaves without
+// writing.  tcgen05.ld / tcgen05.st are warp-collective: every lane of a warp issues them, whether its row exists or not.
 // Reference: paged_kv_attention/_kernels.py:610-726 (_prefill_kernel); the reference's sm_100 wrappers were never run
 // (kernels/core/include/crit_kcore/mma.cuh:349-354).
 #pragma once
@@ -28,38 +30,72 @@ namespace crit_b200 {
 constexpr int TC_ROWS = 128;       // query rows a block holds
 constexpr int TC_BN = 64;          // positions a tile holds
 constexpr int TC_D = 128;          // head width
+constexpr int TC_THREADS = 192;
 constexpr int TC_Q_BYTES = 2 * TC_ROWS * 128;               // two 64-value halves of [128 rows][128 bytes]
 constexpr int TC_K_BYTES = 2 * TC_BN * 128;                 // two halves of [64 positions][128 bytes]
 constexpr int TC_STAGE = 2 * TC_K_BYTES;                    // keys, values
-constexpr int TC_SMEM = 1024 + TC_Q_BYTES + 2 * TC_STAGE + 64;
-constexpr uint32_t TC_COLUMNS = 256;                        // TMEM: scores at 0..63, outputs at 64..191
+constexpr int TC_P_BYTES = TC_ROWS * 128;                   // the probabilities of a tile: [128 rows][64 positions]
+constexpr int TC_SMEM = TC_Q_BYTES + 2 * TC_STAGE + TC_P_BYTES + 128;      // two blocks an SM: no room for alignment slack
+constexpr uint32_t TC_COLUMNS = 256;                        // TMEM: scores at 0..63 and 64..127, outputs at 128..255
+constexpr uint32_t TC_O = 128;
+constexpr float TC_LAZY = 8.f;
+
+enum { TC_KFULL = 0, TC_VFULL = 2, TC_KEMPTY = 4, TC_VEMPTY = 6, TC_SFULL = 8, TC_SFREE = 10, TC_PFULL = 12, TC_PVDONE = 13 };
+
+__device__ __forceinline__ void tc_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// A bounded wait that also gives up when another thread of the block already did.
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    do {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    } while (global_ns() - t0 < 250000000ull);
+    *abort_flag = 1;
+    return false;
+}
 
 template <bool BF16>
-__global__ void __launch_bounds__(TC_ROWS) prefill_tc_kernel(const crit_b200_prefill_params p,
-                                                             const __grid_constant__ CUtensorMap kmap,
-                                                             const __grid_constant__ CUtensorMap vmap, int32_t* status) {
-    extern __shared__ unsigned char smem_raw[];
-    unsigned char* smem = smem_raw + ((1024 - (smem_addr(smem_raw) & 1023)) & 1023);
+__global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b200_prefill_params p,
+                                                                   const __grid_constant__ CUtensorMap kmap,
+                                                                   const __grid_constant__ CUtensorMap vmap, int32_t* status) {
+    constexpr uint32_t FULLMASK = 0xffffffffu;
+    extern __shared__ __align__(1024) unsigned char smem[];        // the 128-byte swizzle wants 1 KB alignment (checked below)
     unsigned char* qs = smem;
     unsigned char* stages = smem + TC_Q_BYTES;
-    const uint32_t bars = smem_addr(stages + 2 * TC_STAGE);   // [0], [1]: a stage's loads; [2]: scores; [3]: outputs
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stages + 2 * TC_STAGE + 32);
+    unsigned char* pbuf = stages + 2 * TC_STAGE;
+    const uint32_t bars = smem_addr(pbuf + TC_P_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pbuf + TC_P_BYTES + 112);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(pbuf + TC_P_BYTES + 116);
+    auto bar = [&](int which) { return bars + (uint32_t)which * 8u; };
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int h = blockIdx.y;
     const int G = p.q_heads / p.kv_heads;
     const int row0 = blockIdx.x * TC_ROWS;
     const int rows_total = p.tokens * G;
     const int pos32 = (int)(p.position_ptr ? *p.position_ptr : p.position);
 
+    if (smem_addr(smem) & 1023u) {              // never seen; the operand layouts would be wrong: say so and leave
+        if (tid == 0 && status) atomicExch(status, 0x1ff);
+        return;
+    }
     if (warp == 0) tmem_alloc(smem_addr(tmem_slot), TC_COLUMNS);
-    if (tid == 0) {
-        for (int b = 0; b < 4; ++b) mbar_init(bars + b * 8, 1);
+    if (tid == 32) {
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(TC_KFULL + b), 1), mbar_init(bar(TC_KEMPTY + b), 1);
+            mbar_init(bar(TC_VFULL + b), 1), mbar_init(bar(TC_VEMPTY + b), 1);
+            mbar_init(bar(TC_SFULL + b), 1), mbar_init(bar(TC_SFREE + b), 128);
+        }
+        mbar_init(bar(TC_PFULL), 128), mbar_init(bar(TC_PVDONE), 1);
+        *abort_flag = 0;
         mbar_init_fence();
     }
 
     // -- queries into shared memory, K-major with the 128-byte swizzle ---------------------------------------------------
-    for (int idx = tid; idx < TC_ROWS * 16; idx += TC_ROWS) {
+    for (int idx = tid; idx < TC_ROWS * 16; idx += TC_THREADS) {
         const int rr = idx >> 4, c = idx & 15;
         const int flat = row0 + rr;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -75,178 +111,223 @@ __global__ void __launch_bounds__(TC_ROWS) prefill_tc_kernel(const crit_b200_pre
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t t_s = tmem + ((uint32_t)(warp * 32) << 16);          // this warp's lanes, scores
-    const uint32_t t_o = t_s + 64;                                      // outputs
 
-    const int flat = row0 + tid;
-    const int lastpos = flat < rows_total ? pos32 + flat / G : -1;
     const int last_row = (row0 + TC_ROWS < rows_total ? row0 + TC_ROWS : rows_total) - 1;
     const int end = pos32 + last_row / G + 1;               // the block reads positions [0, end)
     const int clear = pos32 + row0 / G;                     // positions <= clear are seen by every row of the block
     const int ntiles = (end + TC_BN - 1) / TC_BN;
     const uint32_t tiles_per_page = (uint32_t)p.page >> 4;
-    const float sl2 = p.scale * LOG2E;
-    const uint32_t idesc_s = idesc_f16(BF16, false, TC_ROWS, TC_BN);
-    const uint32_t idesc_o = idesc_f16(BF16, true, TC_ROWS, TC_D);
+    int where = 0;                 // which role's wait gave up
 
-    auto load_tile = [&](int i) {           // one thread: the tile's live pages into stage i & 1
-        const int tile_pos = i * TC_BN;
-        const int live = end - tile_pos < TC_BN ? end - tile_pos : TC_BN;
-        const int boxes = (live + 15) >> 4;
-        const uint32_t ks = smem_addr(stages + (i & 1) * TC_STAGE), vs = ks + TC_K_BYTES;
-        const uint32_t bar = bars + (i & 1) * 8;
-        fence_proxy_async();
-        mbar_expect_tx(bar, (uint32_t)boxes * 4u * 2048u);
-        for (int b = 0; b < boxes; ++b) {
-            const uint32_t tile16 = (uint32_t)(i * (TC_BN / 16) + b);
-            const uint32_t pidx = tile16 / tiles_per_page;
-            const int slot0 = (int)((int64_t)p.table[pidx] * p.page + ((tile16 - pidx * tiles_per_page) << 4));
+    if (warp == 4) {
+        // -- producer: lane l holds the page id of box 32 * batch + l (a box is 16 positions), a batch ahead ---------------
+        const int nboxes = (end + 15) >> 4;
+        auto fetch = [&](int batch) {
+            const int box = batch * 32 + lane;
+            return box < nboxes ? p.table[(uint32_t)box / tiles_per_page] : 0;
+        };
+        int cur = fetch(0), nxt = fetch(1);
+        bool ok = true;
+        for (int i = 0; i < ntiles; ++i) {
+            if (i > 0 && (i & 7) == 0) cur = nxt, nxt = fetch((i >> 3) + 1);
+            const int s = i & 1;
+            const int live = end - i * TC_BN < TC_BN ? end - i * TC_BN : TC_BN;
+            const int boxes = (live + 15) >> 4;
+            const int pg = __shfl_sync(FULLMASK, cur, ((i & 7) << 2) + (lane & 3));
+            const uint32_t tile16 = (uint32_t)(i * (TC_BN / 16) + (lane & 3));
+            const int slot0 = (int)((int64_t)pg * p.page + ((tile16 % tiles_per_page) << 4));
+            const uint32_t ks = smem_addr(stages + s * TC_STAGE), vs = ks + TC_K_BYTES;
+            const uint32_t free_parity = (uint32_t)((i >> 1) & 1) ^ 1u;
+            ok = tc_wait(bar(TC_KEMPTY + s), free_parity, abort_flag);
+            ok = __all_sync(FULLMASK, ok);
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(bar(TC_KFULL + s), (uint32_t)boxes * 2u * 2048u);
+            __syncwarp();
+            if (lane < boxes) {
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                tma_load_3d(ks + half * (TC_BN * 128) + b * 2048, &kmap, half * 64, h, slot0, bar);
-                tma_load_3d(vs + half * (TC_BN * 128) + b * 2048, &vmap, half * 64, h, slot0, bar);
+                for (int half = 0; half < 2; ++half)
+                    tma_load_3d(ks + half * (TC_BN * 128) + lane * 2048, &kmap, half * 64, h, slot0, bar(TC_KFULL + s));
+            }
+            ok = tc_wait(bar(TC_VEMPTY + s), free_parity, abort_flag);
+            ok = __all_sync(FULLMASK, ok);
+            if (!ok) break;
+            if (lane == 0) mbar_expect_tx(bar(TC_VFULL + s), (uint32_t)boxes * 2u * 2048u);
+            __syncwarp();
+            if (lane < boxes) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+                    tma_load_3d(vs + half * (TC_BN * 128) + lane * 2048, &vmap, half * 64, h, slot0, bar(TC_VFULL + s));
             }
         }
-    };
-
-    float m_run = -INFINITY, l_run = 0.f;
-    bool dead = false;
-    int where = 0;                 // which wait gave up (0x100 loads, 0x200 scores, 0x300 outputs) + the tile
-    if (tid == 0 && ntiles > 0) load_tile(0);
-    for (int i = 0; i < ntiles && !dead; ++i) {
-        const int tile_pos = i * TC_BN;
-        unsigned char* kst = stages + (i & 1) * TC_STAGE;
-        unsigned char* vst = kst + TC_K_BYTES;
-        if (tid == 0 && i + 1 < ntiles) load_tile(i + 1);
-        dead = !mbar_wait(bars + (i & 1) * 8, (uint32_t)(i >> 1) & 1u);
-        if (dead) where = 0x100 + i;
-        const int live = end - tile_pos;
-        if (live < TC_BN) {
-            // value rows past the block's last position: zeros (a probability of 0 times stale bytes must stay 0)
-            for (int idx = tid; idx < TC_BN * 16; idx += TC_ROWS) {
-                const int rr = idx >> 4, c = idx & 15;
-                if (rr >= live)
-                    *reinterpret_cast<uint4*>(vst + (c >> 3) * (TC_BN * 128) + rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+        if (!ok) where = 0x110;
+    } else if (warp == 5) {
+        // -- MMA issue -------------------------------------------------------------------------------------------------------
+        const uint32_t idesc_s = idesc_f16(BF16, false, TC_ROWS, TC_BN);
+        const uint32_t idesc_o = idesc_f16(BF16, true, TC_ROWS, TC_D);
+        bool ok = true;
+        auto issue_pv = [&](int t) {        // O (+)= P V of tile t
+            ok = tc_wait(bar(TC_PFULL), (uint32_t)t & 1u, abort_flag) &&
+                 tc_wait(bar(TC_VFULL + (t & 1)), (uint32_t)(t >> 1) & 1u, abort_flag);
+            ok = __all_sync(FULLMASK, ok);
+            if (!ok) return;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t pa = smem_addr(pbuf), va = smem_addr(stages + (t & 1) * TC_STAGE + TC_K_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_BN / 16; ++kk)
+                    umma_f16(tmem + TC_O, smem_desc_sw128(pa + kk * 32, 0, 1024), smem_desc_sw128(va + kk * 2048, TC_BN * 128, 1024),
+                             idesc_o, t > 0 || kk > 0);
+                umma_commit(bar(TC_VEMPTY + (t & 1)));
+                umma_commit(bar(TC_PVDONE));
+            }
+            __syncwarp();
+        };
+        for (int i = 0; i < ntiles && ok; ++i) {
+            const int s = i & 1;
+            ok = tc_wait(bar(TC_KFULL + s), (uint32_t)(i >> 1) & 1u, abort_flag) &&
+                 tc_wait(bar(TC_SFREE + s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag);
+            ok = __all_sync(FULLMASK, ok);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t qa = smem_addr(qs), ka = smem_addr(stages + s * TC_STAGE);
+#pragma unroll
+                for (int ks = 0; ks < TC_D / 16; ++ks)
+                    umma_f16(tmem + (uint32_t)(s * TC_BN), smem_desc_sw128(qa + (ks >> 2) * (TC_ROWS * 128) + (ks & 3) * 32, 0, 1024),
+                             smem_desc_sw128(ka + (ks >> 2) * (TC_BN * 128) + (ks & 3) * 32, 0, 1024), idesc_s, ks > 0);
+                umma_commit(bar(TC_SFULL + s));
+                umma_commit(bar(TC_KEMPTY + s));
+            }
+            __syncwarp();
+            if (i > 0) issue_pv(i - 1);
+        }
+        if (ok && ntiles > 0) issue_pv(ntiles - 1);
+        if (!ok) where = 0x120;
+    } else {
+        // -- softmax: thread = query row row0 + tid = TMEM lane tid -------------------------------------------------------------
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const int flat = row0 + tid;
+        const bool has_row = flat < rows_total;
+        const int lastpos = has_row ? pos32 + flat / G : -1;
+        const float sl2 = p.scale * LOG2E;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool ok = true;
+        for (int i = 0; i < ntiles; ++i) {
+            const int s = i & 1;
+            const int tile_pos = i * TC_BN;
+            unsigned char* vst = stages + s * TC_STAGE + TC_K_BYTES;
+            ok = tc_wait(bar(TC_SFULL + s), (uint32_t)(i >> 1) & 1u, abort_flag);
+            ok = __all_sync(FULLMASK, ok);
+            if (!ok) break;
+            tc_fence_after();
+            float sc[TC_BN];
+            {
+                float half[32];
+                tmem_ld32(tmem + lane_base + (uint32_t)(s * TC_BN), half);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sc[j] = half[j];
+                tmem_ld32(tmem + lane_base + (uint32_t)(s * TC_BN + 32), half);
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sc[32 + j] = half[j];
+            }
+            tc_fence_before();
+            tc_arrive(bar(TC_SFREE + s));
+            const int live = end - tile_pos;
+            if (live < TC_BN) {
+                // value rows past the block's last position: zeros (a probability of 0 times stale bytes must stay 0),
+                // written once the tile's values have landed
+                ok = tc_wait(bar(TC_VFULL + s), (uint32_t)(i >> 1) & 1u, abort_flag);
+                ok = __all_sync(FULLMASK, ok);
+                if (!ok) break;
+                for (int idx = tid; idx < TC_BN * 16; idx += 128) {
+                    const int rr = idx >> 4, c = idx & 15;
+                    if (rr >= live)
+                        *reinterpret_cast<uint4*>(vst + (c >> 3) * (TC_BN * 128) + rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+                }
+            }
+            const bool masked = tile_pos + TC_BN - 1 > clear;
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < TC_BN; ++j) {
+                float x = sc[j] * sl2;
+                if (masked && tile_pos + j > lastpos) x = -INFINITY;
+                sc[j] = x;
+                if (j & 1) mx1 = fmaxf(mx1, x);
+                else mx0 = fmaxf(mx0, x);
+            }
+            const float mx = fmaxf(mx0, mx1);
+            const bool moved = mx > m_run + TC_LAZY || m_run == -INFINITY;
+            const float top = moved ? mx : m_run;
+            const float sub = top == -INFINITY ? 0.f : top;
+            const float alpha = moved ? ex2(m_run - sub) : 1.f;
+            const bool rescale = moved && top != m_run && i > 0;
+            m_run = top;
+            // the P tile is free (and the outputs settled) once the second product of the tile before has landed
+            if (i > 0) {
+                ok = tc_wait(bar(TC_PVDONE), (uint32_t)(i - 1) & 1u, abort_flag);
+                ok = __all_sync(FULLMASK, ok);
+                if (!ok) break;
+            }
+            float sum0 = 0.f, sum1 = 0.f;
+            unsigned char* prow = pbuf + tid * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float a = ex2(sc[c * 8 + 2 * e] - sub), b = ex2(sc[c * 8 + 2 * e + 1] - sub);
+                    sum0 += a, sum1 += b;
+                    w[e] = pack2<BF16>(a, b);
+                }
+                *reinterpret_cast<uint4*>(prow + ((c ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            l_run = l_run * alpha + (sum0 + sum1);
+            if (__any_sync(FULLMASK, rescale)) {
+                // a maximum of the warp's rows moved: their partial outputs go to the new reference
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < TC_D / 32; ++c) {
+                    float o[32];
+                    tmem_ld32(tmem + lane_base + TC_O + c * 32, o);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) o[j] *= alpha;
+                    tmem_st32(tmem + lane_base + TC_O + c * 32, o);
+                }
             }
             fence_proxy_async();
+            tc_fence_before();
+            tc_arrive(bar(TC_PFULL));
         }
-        tc_fence_before();
-        dead = __syncthreads_or(dead);
-        if (dead) break;
-        tc_fence_after();
-
-        // scores
-        if (tid == 0) {
-#pragma unroll
-            for (int ks = 0; ks < TC_D / 16; ++ks) {
-                const uint64_t a = smem_desc_sw128(smem_addr(qs) + (ks >> 2) * (TC_ROWS * 128) + (ks & 3) * 32, 0, 1024);
-                const uint64_t b = smem_desc_sw128(smem_addr(kst) + (ks >> 2) * (TC_BN * 128) + (ks & 3) * 32, 0, 1024);
-                umma_f16(tmem, a, b, idesc_s, ks > 0);
-            }
-            umma_commit(bars + 2 * 8);
+        // -- this thread's row out ---------------------------------------------------------------------------------------
+        if (ok && ntiles > 0) {
+            ok = tc_wait(bar(TC_PVDONE), (uint32_t)(ntiles - 1) & 1u, abort_flag);
+            ok = __all_sync(FULLMASK, ok);
         }
-        dead = !mbar_wait(bars + 2 * 8, (uint32_t)i & 1u);
-        if (dead) where = 0x200 + i;
-        dead = __syncthreads_or(dead);
-        if (dead) break;
-        tc_fence_after();
-
-        // this thread's row of the tile: scale, mask, running maximum (lazy), probabilities
-        float s[TC_BN];
-        {
-            float half[32];
-            tmem_ld32(t_s, half);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) s[j] = half[j];
-            tmem_ld32(t_s + 32, half);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) s[32 + j] = half[j];
-        }
-        const bool masked = tile_pos + TC_BN - 1 > clear;
-        float mx = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < TC_BN; ++j) {
-            float x = s[j] * sl2;
-            if (masked && tile_pos + j > lastpos) x = -INFINITY;
-            s[j] = x;
-            mx = fmaxf(mx, x);
-        }
-        const bool moved = mx > m_run + LAZY || m_run == -INFINITY;
-        const float top = moved ? mx : m_run;
-        const float sub = top == -INFINITY ? 0.f : top;
-        const float alpha = moved ? ex2(m_run - sub) : 1.f;
-        const bool rescale = moved && top != m_run && i > 0;
-        m_run = top;
-        float sum = 0.f;
-        unsigned char* prow = kst + tid * 128;              // the probabilities go over the key tile's first 16 KB
-#pragma unroll
-        for (int c = 0; c < 8; ++c) {
-            uint32_t w[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float a = ex2(s[c * 8 + 2 * e] - sub), b = ex2(s[c * 8 + 2 * e + 1] - sub);
-                sum += a + b;
-                w[e] = pack2<BF16>(a, b);
-            }
-            *reinterpret_cast<uint4*>(prow + ((c ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-        l_run = l_run * alpha + sum;
-        if (__syncthreads_or(rescale ? 1 : 0)) {
-            // the rows whose maximum moved bring their partial outputs to the new reference
+        if (ok) {
+            tc_fence_after();
+            const int tok = flat / G, gq = flat - tok * G, head = h * G + gq;
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            char* dst = (char*)p.out + ((int64_t)tok * p.out_stride_token + (int64_t)head * p.out_stride_head) * 2;
 #pragma unroll
             for (int c = 0; c < TC_D / 32; ++c) {
                 float o[32];
-                tmem_ld32(t_o + c * 32, o);
+                tmem_ld32(tmem + lane_base + TC_O + c * 32, o);
+                if (has_row) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) o[j] *= alpha;
-                tmem_st32(t_o + c * 32, o);
-            }
-        }
-        fence_proxy_async();
-        tc_fence_before();
-        __syncthreads();
-        tc_fence_after();
-
-        // outputs
-        if (tid == 0) {
-#pragma unroll
-            for (int kk = 0; kk < TC_BN / 16; ++kk) {
-                const uint64_t a = smem_desc_sw128(smem_addr(kst) + kk * 32, 0, 1024);
-                const uint64_t b = smem_desc_sw128(smem_addr(vst) + kk * 2048, TC_BN * 128, 1024);
-                umma_f16(tmem + 64, a, b, idesc_o, i > 0 || kk > 0);
-            }
-            umma_commit(bars + 3 * 8);
-        }
-        dead = !mbar_wait(bars + 3 * 8, (uint32_t)i & 1u);
-        if (dead) where = 0x300 + i;
-        dead = __syncthreads_or(dead);
-        tc_fence_after();
-    }
-
-    // -- this thread's row out ---------------------------------------------------------------------------------------
-    // tcgen05.ld is warp-collective: every lane of a warp issues it, the lanes without a row only skip the stores.
-    if (!dead) {
-        const bool has_row = flat < rows_total;
-        const int tok = flat / G, gq = flat - tok * G, head = h * G + gq;
-        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-        char* dst = (char*)p.out + ((int64_t)tok * p.out_stride_token + (int64_t)head * p.out_stride_head) * 2;
-#pragma unroll
-        for (int c = 0; c < TC_D / 32; ++c) {
-            float o[32];
-            tmem_ld32(t_o + c * 32, o);
-            if (has_row) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 8) {
-                    uint4 v;
-                    v.x = pack2<BF16>(o[j] * inv, o[j + 1] * inv), v.y = pack2<BF16>(o[j + 2] * inv, o[j + 3] * inv);
-                    v.z = pack2<BF16>(o[j + 4] * inv, o[j + 5] * inv), v.w = pack2<BF16>(o[j + 6] * inv, o[j + 7] * inv);
-                    *reinterpret_cast<uint4*>(dst + (c * 32 + j) * 2) = v;
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 v;
+                        v.x = pack2<BF16>(o[j] * inv, o[j + 1] * inv), v.y = pack2<BF16>(o[j + 2] * inv, o[j + 3] * inv);
+                        v.z = pack2<BF16>(o[j + 4] * inv, o[j + 5] * inv), v.w = pack2<BF16>(o[j + 6] * inv, o[j + 7] * inv);
+                        *reinterpret_cast<uint4*>(dst + (c * 32 + j) * 2) = v;
+                    }
                 }
             }
+            if (has_row && p.lse) p.lse[(int64_t)tok * p.q_heads + head] = l_run > 0.f ? m_run * LN2 + logf(l_run) : -INFINITY;
+        } else {
+            where = 0x140;
         }
-        if (has_row && p.lse) p.lse[(int64_t)tok * p.q_heads + head] = l_run > 0.f ? m_run * LN2 + logf(l_run) : -INFINITY;
     }
-    if (dead && where && status) atomicExch(status, where);
+    if (where && status) atomicExch(status, where);
     tc_fence_before();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem, TC_COLUMNS);
