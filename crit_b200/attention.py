@@ -139,7 +139,8 @@ class DeviceAttention:
         multipliers = pool.scale_values[pool.layers[layer]] if pool.dtype == "fp8" else (1.0, 1.0)
         kernels = self.kernels
         positions = meta.tables.shape[1] * pool.page
-        chunk = self.chunk or kernels.chunk_for(pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, pool.page, pool.dtype)
+        chunk = self.chunk or kernels.chunk_for(pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, pool.page, pool.dtype,
+                                                self.window_engine if self.window_engine == "tcgen05" else None)
         if self.partitions:
             chunk = max(chunk, -(-positions // self.partitions))
         chunk = -(-chunk // 16) * 16

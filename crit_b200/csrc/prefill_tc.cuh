@@ -245,17 +245,21 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
                         *reinterpret_cast<uint4*>(vst + (c >> 3) * (TC_BN * 128) + rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = make_uint4(0, 0, 0, 0);
                 }
             }
+            // The maximum is taken over the raw scores (the scale is positive), and a probability is one FFMA and one
+            // exp2: 2^(score * scale * log2 e - reference).  Only the tiles that straddle a row's own position mask.
             const bool masked = tile_pos + TC_BN - 1 > clear;
-            float mx0 = -INFINITY, mx1 = -INFINITY;
+            if (masked) {
 #pragma unroll
-            for (int j = 0; j < TC_BN; ++j) {
-                float x = sc[j] * sl2;
-                if (masked && tile_pos + j > lastpos) x = -INFINITY;
-                sc[j] = x;
-                if (j & 1) mx1 = fmaxf(mx1, x);
-                else mx0 = fmaxf(mx0, x);
+                for (int j = 0; j < TC_BN; ++j)
+                    if (tile_pos + j > lastpos) sc[j] = -INFINITY;
             }
-            const float mx = fmaxf(mx0, mx1);
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < TC_BN; j += 4) {
+                mx0 = fmaxf(mx0, sc[j]), mx1 = fmaxf(mx1, sc[j + 1]);
+                mx2 = fmaxf(mx2, sc[j + 2]), mx3 = fmaxf(mx3, sc[j + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * sl2;
             const bool moved = mx > m_run + TC_LAZY || m_run == -INFINITY;
             const float top = moved ? mx : m_run;
             const float sub = top == -INFINITY ? 0.f : top;
@@ -270,12 +274,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
             }
             float sum0 = 0.f, sum1 = 0.f;
             unsigned char* prow = pbuf + tid * 128;
+            const float nsub = -sub;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float a = ex2(sc[c * 8 + 2 * e] - sub), b = ex2(sc[c * 8 + 2 * e + 1] - sub);
+                    const float a = ex2(fmaf(sc[c * 8 + 2 * e], sl2, nsub)), b = ex2(fmaf(sc[c * 8 + 2 * e + 1], sl2, nsub));
                     sum0 += a, sum1 += b;
                     w[e] = pack2<BF16>(a, b);
                 }
