@@ -291,7 +291,13 @@ static int launch_decode_tc(const crit_b200_attend_params& p, cudaStream_t s) {
         !page_map(&vmap, p.value_pages, 2, p.value_dim, p.kv_heads, p.slots))
         return CRIT_B200_EUNSUPPORTED;
     const int rows = p.columns * (p.q_heads / p.kv_heads);
-    auto fn = rows <= 8 ? decode_tc_kernel<1> : (rows <= 16 ? decode_tc_kernel<2> : decode_tc_kernel<4>);
+    typedef void (*tc_fn)(const crit_b200_attend_params, const CUtensorMap, const CUtensorMap);
+    const int nrg = rows <= 8 ? 0 : (rows <= 16 ? 1 : 2);
+    static const tc_fn fns[3][3] = {
+        {decode_tc_kernel<1, 0>, decode_tc_kernel<1, 1>, decode_tc_kernel<1, 2>},
+        {decode_tc_kernel<2, 0>, decode_tc_kernel<2, 1>, decode_tc_kernel<2, 2>},
+        {decode_tc_kernel<4, 0>, decode_tc_kernel<4, 1>, decode_tc_kernel<4, 2>}};
+    const tc_fn fn = fns[nrg][scale_mode(p.kind)];
     cudaError_t ce = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, DT_SMEM);
     if (ce != cudaSuccess) return (int)ce;
     int device = 0, sms = 0;
@@ -300,7 +306,7 @@ static int launch_decode_tc(const crit_b200_attend_params& p, cudaStream_t s) {
         return CRIT_B200_EUNSUPPORTED;
     const int64_t most = (int64_t)p.max_splits * p.kv_heads * p.n_rows;        // units the launch can have
     const unsigned blocks = (unsigned)(most < 2 * sms ? most : 2 * sms);       // two persistent blocks per SM
-    fn<<<blocks, DT_THREADS, DT_SMEM, s>>>(p, scale_mode(p.kind), kmap, vmap);
+    fn<<<blocks, DT_THREADS, DT_SMEM, s>>>(p, kmap, vmap);
     CRIT_CHECK_LAUNCH();
     return 0;
 }

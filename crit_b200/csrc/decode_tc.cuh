@@ -214,11 +214,14 @@ struct DtWalk {
 
 // NRG: groups of 8 query rows a unit holds (1, 2 or 4: up to 8, 16 or 32 rows).  A group takes 16 TMEM lanes (hi and lo
 // terms), so the 128 lanes hold 8 / NRG replicas of the unit's rows, each owning 16 * NRG columns of a tile.
-// smode: 0 static multipliers, 1 a scale per (slot, kv head), 2 a scale per (page, kv head).
-template <int NRG>
+// SMODE: 0 static multipliers, 1 a scale per (slot, kv head), 2 a scale per (page, kv head): a template parameter, so
+// the loops hold one rule's code only (the kernel's instruction footprint is what its warps wait for most: taking the
+// other rules' code out of the loops cut a tile's softmax from 2,200 to 1,400 cycles).
+template <int NRG, int SMODE>
 __global__ void __launch_bounds__(DT_THREADS, 2)
-decode_tc_kernel(const crit_b200_attend_params p, const int smode, const __grid_constant__ CUtensorMap kmap,
+decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtensorMap kmap,
                  const __grid_constant__ CUtensorMap vmap) {
+    constexpr int smode = SMODE;
     constexpr int REPL = 8 / NRG;         // replicas of the unit's rows
     constexpr int R = 8 * NRG;            // query rows a unit holds (padded)
     constexpr int W = DT_N / REPL;        // columns of a tile one replica owns
