@@ -140,17 +140,33 @@ __device__ __forceinline__ void split_e4m3x2(float a, float b, uint32_t& hi, uin
 
 // A bounded wait that also gives up when another thread of the block already did.  BACKOFF: nanoseconds to sleep
 // between polls (the roles that wait long share their issue slots with the softmax warps; those poll without a pause).
-template <int BACKOFF = 0>
-__device__ __forceinline__ bool dt_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
+// The polling loop is one out-of-line function: the kernel has some thirty waits, and their loops inline would be a
+// good part of its instruction footprint.
+__device__ __noinline__ bool dt_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned backoff) {
     const uint64_t t0 = global_ns();
     do {
-        if (BACKOFF) __nanosleep(BACKOFF);
+        if (backoff) __nanosleep(backoff);
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
     } while (global_ns() - t0 < DT_WAIT_NS);
     *abort_flag = 1;
     return false;
+}
+template <int BACKOFF = 0>
+__device__ __forceinline__ bool dt_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return dt_wait_slow(bar, parity, abort_flag, BACKOFF);
+}
+// A warp's output lanes times a factor per lane (the rare move of a running maximum), out of line for the same reason.
+__device__ __noinline__ void dt_rescale(uint32_t taddr, float alpha) {
+#pragma unroll
+    for (int c4 = 0; c4 < DT_D / 32; ++c4) {
+        float o[32];
+        tmem_ld32(taddr + 32u * c4, o);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] *= alpha;
+        tmem_st32(taddr + 32u * c4, o);
+    }
 }
 
 // The launch's rows, copied to shared memory once: no role reads global memory to find its next unit.
@@ -714,14 +730,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                     // a maximum moved: the warp brings its output lanes to the new reference
                     DT_COUNT(15)
                     tc_fence_after();
-#pragma unroll
-                    for (int c4 = 0; c4 < DT_D / 32; ++c4) {
-                        float o[32];
-                        tmem_ld32(tmem + lane_base + DT_O + 32u * c4, o);
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) o[j] *= alpha;
-                        tmem_st32(tmem + lane_base + DT_O + 32u * c4, o);
-                    }
+                    dt_rescale(tmem + lane_base + DT_O, alpha);
                 }
                 fence_proxy_async();
                 tc_fence_before();
