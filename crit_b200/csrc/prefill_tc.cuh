@@ -5,8 +5,9 @@
 // values it reads) and walks the sequence's positions in tiles of 64 (four pages of 16).  Warp roles:
 //   warps 0-3  softmax: thread = one query row = one TMEM lane.  It reads its 64 scores of a tile (tcgen05.ld), masks the
 //              tile that straddles its own position, updates its running maximum (lazily: when beaten by 2^8) and sum,
-//              writes its probabilities as bf16/fp16 in the A-operand layout, and rescales its output lane in TMEM when
-//              its maximum moved;
+//              writes its probabilities as bf16/fp16 back into tensor memory, over its own scores (tcgen05.st: the
+//              second product takes its A operand from TMEM, so the probabilities never cross shared memory), and
+//              rescales its output lane in TMEM when its maximum moved;
 //   warp 4     producer: the next 32 boxes' page ids in registers, a batch ahead; TMA tiled loads (boxes of
 //              [16 positions][1 head][64 values], 128-byte swizzle: exactly the K-major / MN-major operand layouts the
 //              MMA reads) into a ring of two stages whose keys and values land and free separately (the keys are
@@ -14,7 +15,7 @@
 //   warp 5     MMA issue (one lane): S = Q K^T as eight tcgen05.mma (M 128, N 64, K 16) into one of TWO score buffers
 //              (TMEM columns 0..63 and 64..127), O += P V as four (M 128, N 128, K 16, V as the MN-major B operand) into
 //              columns 128..255, one tile behind: a tile's softmax overlaps the next tile's first product.
-// Two blocks share an SM (112 KB of shared memory, 256 TMEM columns each).  Every wait is bounded in time and polls a
+// Two blocks share an SM (96 KB of shared memory, 256 TMEM columns each).  Every wait is bounded in time and polls a
 // block-wide abort flag; a wait that runs out sets the status word, and the block frees its TMEM and leaves without
 // writing.  tcgen05.ld / tcgen05.st are warp-collective: every lane of a warp issues them, whether its row exists or not.
 // Reference: paged_kv_attention/_kernels.py:610-726 (_prefill_kernel); the reference's sm_100 wrappers were never run
@@ -34,8 +35,7 @@ constexpr int TC_THREADS = 192;
 constexpr int TC_Q_BYTES = 2 * TC_ROWS * 128;               // two 64-value halves of [128 rows][128 bytes]
 constexpr int TC_K_BYTES = 2 * TC_BN * 128;                 // two halves of [64 positions][128 bytes]
 constexpr int TC_STAGE = 2 * TC_K_BYTES;                    // keys, values
-constexpr int TC_P_BYTES = TC_ROWS * 128;                   // the probabilities of a tile: [128 rows][64 positions]
-constexpr int TC_SMEM = TC_Q_BYTES + 2 * TC_STAGE + TC_P_BYTES + 128;      // two blocks an SM: no room for alignment slack
+constexpr int TC_SMEM = TC_Q_BYTES + 2 * TC_STAGE + 128;
 constexpr uint32_t TC_COLUMNS = 256;                        // TMEM: scores at 0..63 and 64..127, outputs at 128..255
 constexpr uint32_t TC_O = 128;
 constexpr float TC_LAZY = 8.f;
@@ -65,10 +65,10 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
     extern __shared__ __align__(1024) unsigned char smem[];        // the 128-byte swizzle wants 1 KB alignment (checked below)
     unsigned char* qs = smem;
     unsigned char* stages = smem + TC_Q_BYTES;
-    unsigned char* pbuf = stages + 2 * TC_STAGE;
-    const uint32_t bars = smem_addr(pbuf + TC_P_BYTES);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pbuf + TC_P_BYTES + 112);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(pbuf + TC_P_BYTES + 116);
+    unsigned char* small = stages + 2 * TC_STAGE;
+    const uint32_t bars = smem_addr(small);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(small + 112);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(small + 116);
     auto bar = [&](int which) { return bars + (uint32_t)which * 8u; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -172,11 +172,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
             if (!ok) return;
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t pa = smem_addr(pbuf), va = smem_addr(stages + (t & 1) * TC_STAGE + TC_K_BYTES);
+                // the probabilities of tile t sit over its scores: 16 of them (8 columns) a K step
+                const uint32_t pa = tmem + (uint32_t)((t & 1) * TC_BN), va = smem_addr(stages + (t & 1) * TC_STAGE + TC_K_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < TC_BN / 16; ++kk)
-                    umma_f16(tmem + TC_O, smem_desc_sw128(pa + kk * 32, 0, 1024), smem_desc_sw128(va + kk * 2048, TC_BN * 128, 1024),
-                             idesc_o, t > 0 || kk > 0);
+                    umma_f16_ts(tmem + TC_O, pa + kk * 8, smem_desc_sw128(va + kk * 2048, TC_BN * 128, 1024), idesc_o, t > 0 || kk > 0);
                 umma_commit(bar(TC_VEMPTY + (t & 1)));
                 umma_commit(bar(TC_PVDONE));
             }
@@ -266,29 +266,25 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
             const float alpha = moved ? ex2(m_run - sub) : 1.f;
             const bool rescale = moved && top != m_run && i > 0;
             m_run = top;
-            // the P tile is free (and the outputs settled) once the second product of the tile before has landed
-            if (i > 0) {
+            float sum0 = 0.f, sum1 = 0.f;
+            uint32_t pw[32];
+            const float nsub = -sub;
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+                const float a = ex2(fmaf(sc[2 * e], sl2, nsub)), b = ex2(fmaf(sc[2 * e + 1], sl2, nsub));
+                sum0 += a, sum1 += b;
+                pw[e] = pack2<BF16>(a, b);
+            }
+            l_run = l_run * alpha + (sum0 + sum1);
+            // over this row's own scores (read above, and the buffer's next scores come after the second product that
+            // reads these probabilities: the MMA warp issues them in that order)
+            tmem_st32u(tmem + lane_base + (uint32_t)(s * TC_BN), pw);
+            if (__any_sync(FULLMASK, rescale)) {
+                // a maximum of the warp's rows moved: their partial outputs go to the new reference, once the second
+                // product of the tile before has landed
                 ok = tc_wait(bar(TC_PVDONE), (uint32_t)(i - 1) & 1u, abort_flag);
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
-            }
-            float sum0 = 0.f, sum1 = 0.f;
-            unsigned char* prow = pbuf + tid * 128;
-            const float nsub = -sub;
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float a = ex2(fmaf(sc[c * 8 + 2 * e], sl2, nsub)), b = ex2(fmaf(sc[c * 8 + 2 * e + 1], sl2, nsub));
-                    sum0 += a, sum1 += b;
-                    w[e] = pack2<BF16>(a, b);
-                }
-                *reinterpret_cast<uint4*>(prow + ((c ^ (tid & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-            }
-            l_run = l_run * alpha + (sum0 + sum1);
-            if (__any_sync(FULLMASK, rescale)) {
-                // a maximum of the warp's rows moved: their partial outputs go to the new reference
                 tc_fence_after();
 #pragma unroll
                 for (int c = 0; c < TC_D / 32; ++c) {
@@ -299,7 +295,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
                     tmem_st32(tmem + lane_base + TC_O + c * 32, o);
                 }
             }
-            fence_proxy_async();
+            if (live < TC_BN) fence_proxy_async();          // the zeros written over the last tile's values
             tc_fence_before();
             tc_arrive(bar(TC_PFULL));
         }
