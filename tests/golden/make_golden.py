@@ -1,7 +1,7 @@
 """Generates the golden fixtures of tests/golden/ by running the REFERENCE's own torch path (crit 0.21.0).
 
-Run where the reference checkout is present:  python tests/golden/make_golden.py [/path/to/reference]
-(default /root/reference).  It imports, unmodified, the reference's
+Run where a checkout of the reference is present:  python tests/golden/make_golden.py /path/to/reference
+(or with CRIT_REFERENCE set to that path).  It imports, unmodified, the reference's
   inference/attention-state/code/pages.py            (KVPool, fp8_rows, int8_rows)
   inference/attention-state/code/device_attention.py (DeviceAttention: _gathered SDPA, windows_dense, windows_torch)
   inference/partitioned-attention/plugin.py          (PartitionedAttention.merge)
@@ -20,7 +20,11 @@ from pathlib import Path
 import numpy as np
 import torch
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+import os  # noqa: E402
+
+if len(sys.argv) < 2 and "CRIT_REFERENCE" not in os.environ:
+    raise SystemExit("usage: python tests/golden/make_golden.py /path/to/reference")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["CRIT_REFERENCE"])
 OUT = Path(__file__).resolve().parent
 sys.path.insert(0, str(REF / "core" / "python"))
 from crit_plugins import StepBatch  # noqa: E402
