@@ -174,13 +174,30 @@ def build_state(w, device, rank, world):
                  h_q=torch.randn(max(tokens, 1), hq, d, generator=same if w["batch"] == 1 else cpu).bfloat16().pin_memory(),
                  h_k=torch.randn(max(tokens, 1), hkv, d, generator=cpu).bfloat16().pin_memory(),
                  h_v=torch.randn(max(tokens, 1), hkv, d, generator=cpu).bfloat16().pin_memory())
-    for name in ("q", "k", "v"):
-        state["d_" + name] = state["h_" + name].to(device)
-    state["slots"] = torch.empty(max(tokens, 1), dtype=torch.int64, device=device)
-    state["out"] = torch.empty(max(tokens, 1), hq, d, dtype=torch.bfloat16, device=device)
-    state["lse"] = torch.empty(max(tokens, 1), hq, dtype=torch.float32, device=device)
-    state["h_out"] = torch.empty(max(tokens, 1), hq, d, dtype=torch.bfloat16).pin_memory()
-    state["h_lse"] = torch.empty(max(tokens, 1), hq, dtype=torch.float32).pin_memory()
+    # The step's inputs (q, k, v) sit in ONE pinned host buffer and one device buffer, its results (out, lse) in another
+    # pair, so the end-to-end step is one copy in and one copy out (256-byte aligned parts).
+    def packed(parts, pin, where):
+        sizes = [(-(-(int(torch.tensor(shape).prod()) * torch.empty(0, dtype=dtype).element_size()) // 256) * 256) for shape, dtype in parts]
+        raw = torch.empty(sum(sizes), dtype=torch.uint8, device=where)
+        raw = raw.pin_memory() if pin else raw
+        views, at = [], 0
+        for (shape, dtype), size in zip(parts, sizes):
+            n = int(torch.tensor(shape).prod()) * torch.empty(0, dtype=dtype).element_size()
+            views.append(raw[at:at + n].view(dtype).view(*shape))
+            at += size
+        return raw, views
+    n = max(tokens, 1)
+    ins = [((n, hq, d), torch.bfloat16), ((n, hkv, d), torch.bfloat16), ((n, hkv, d), torch.bfloat16)]
+    outs = [((n, hq, d), torch.bfloat16), ((n, hq), torch.float32)]
+    state["h_in"], host_in = packed(ins, True, "cpu")
+    state["d_in"], dev_in = packed(ins, False, device)
+    for name, h, dv in zip(("q", "k", "v"), host_in, dev_in):
+        h.copy_(state["h_" + name])
+        state["h_" + name], state["d_" + name] = h, dv
+    state["d_in"].copy_(state["h_in"])
+    state["slots"] = torch.empty(n, dtype=torch.int64, device=device)
+    state["d_res"], (state["out"], state["lse"]) = packed(outs, False, device)
+    state["h_res"], (state["h_out"], state["h_lse"]) = packed(outs, True, "cpu")
     state["kv_bytes"] = sum(lens) * kv_bytes_per_token(w)
     state["merger"] = None
     if w["batch"] == 1 and world > 1:
@@ -385,12 +402,9 @@ def main():
 
         # end to end: the step's inputs from pinned host memory, the outputs read back, every step
         def e2e_step():
-            state["d_q"].copy_(state["h_q"], non_blocking=True)
-            state["d_k"].copy_(state["h_k"], non_blocking=True)
-            state["d_v"].copy_(state["h_v"], non_blocking=True)
+            state["d_in"].copy_(state["h_in"], non_blocking=True)          # q, k, v of the step: one copy
             run()
-            state["h_out"].copy_(state["out"], non_blocking=True)
-            state["h_lse"].copy_(state["lse"], non_blocking=True)
+            state["h_res"].copy_(state["d_res"], non_blocking=True)        # out and lse: one copy
             stream.synchronize()
         e2e_steps = max(20, args.steps // 2)
         e2e_s = timed(e2e_step, e2e_steps, 3, stream)
@@ -420,8 +434,7 @@ def main():
             "clocks": clocks.summary(),
             "e2e": {"value": kv_total / e2e_step_s / 1e9, "unit": unit, "tokens_per_s": tokens_total / e2e_step_s,
                     "ms_per_step": e2e_step_s * 1e3,
-                    "h2d_bytes_per_step": sum(state["h_" + n].numel() * 2 for n in ("q", "k", "v")),
-                    "d2h_bytes_per_step": state["h_out"].numel() * 2 + state["h_lse"].numel() * 4},
+                    "h2d_bytes_per_step": state["h_in"].numel(), "d2h_bytes_per_step": state["h_res"].numel()},
             "gpu_launches": (4 + (2 if state["merger"] is not None else 0)) * args.steps,
             "roofline": {"bound": "hbm", "kernel": ("decode_tc_kernel (tcgen05 split-K decode over paged E4M3 KV)" if state.get("engine") == "tcgen05"
                                                    else "decode_kernel (split-K decode over paged KV)"),
