@@ -6,7 +6,8 @@
 // of units (window row, split of `chunk` positions, kv head), built on the device from the rows' lengths: block b takes
 // units b, b + grid, ...  A unit's positions stream through a ring of DT_STAGES stages as tiles of 128 positions (eight
 // TMA boxes of [16 positions][1 kv head][128 bytes] for the keys, eight for the values, 128-byte swizzle: the K-major /
-// MN-major operand layouts of the MMA), and the ring runs on across units, so HBM never waits for a unit's epilogue.
+// MN-major operand layouts of the MMA); a stage's keys and values land and free on separate mbarriers (the keys are free
+// once the first product has read them), and the ring runs on across units, so HBM never waits for a unit's epilogue.
 // One block's chain of dependent steps per tile (scores -> softmax -> probabilities -> outputs) is long; the SM's other
 // block fills its gaps.  Warp roles:
 //   warps 0-3  softmax: thread = one TMEM lane.  Reads its scores (tcgen05.ld), applies the row's and the pages' scales,
@@ -14,8 +15,9 @@
 //              second product, rescales its output lane in TMEM when the maximum moved, and folds / writes the unit's
 //              result;
 //   warp 4     producer: a unit's page ids and page scales in registers, loaded one and two units ahead; TMA loads;
-//   warp 5     query preparation for the next unit, then MMA issue (one lane): S = Q K^T (4 MMAs of M128 N128 K32 per
-//              tile), O += P V (4 MMAs) one tile behind.
+//   warp 5     MMA issue (one lane): S = Q K^T (4 MMAs of M128 N128 K32 per tile), O += P V (4 MMAs) one tile behind; at a
+//              unit's start it first issues the last unit's final second product, then splits the unit's queries (whose
+//              global loads it started a unit earlier) into the A operand.
 // The MMA multiplies E4M3 by E4M3, so the 16-bit queries and the probabilities are each split in two E4M3 terms:
 // x * 2^e = hi + lo, hi = e4m3(x * 2^e), lo = e4m3(x * 2^e - hi), 2^e a per-row power of two that puts the row's largest
 // magnitude in [128, 256): exact for bf16 queries (8 significant bits = 4 + 4), to 2^-9 of the value for FP16 queries
