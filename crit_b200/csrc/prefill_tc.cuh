@@ -164,6 +164,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
         // -- MMA issue -------------------------------------------------------------------------------------------------------
         const uint32_t idesc_s = idesc_f16(BF16, false, TC_ROWS, TC_BN);
         const uint32_t idesc_o = idesc_f16(BF16, true, TC_ROWS, TC_D);
+        // The operands' descriptors are made once: a step of 16 bytes in the address is a step of 1 in the descriptor, so a
+        // tile's MMAs take theirs with one addition each (the issue of the twelve MMAs of a tile is what bounds the block).
+        const uint64_t q_desc = smem_desc_sw128(smem_addr(qs), 0, 1024);
+        const uint64_t k_desc0 = smem_desc_sw128(smem_addr(stages), 0, 1024);
+        const uint64_t v_desc0 = smem_desc_sw128(smem_addr(stages) + TC_K_BYTES, TC_BN * 128, 1024);
         bool ok = true;
         auto issue_pv = [&](int t) {        // O (+)= P V of tile t
             ok = tc_wait(bar(TC_PFULL), (uint32_t)t & 1u, abort_flag) &&
@@ -173,10 +178,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
             tc_fence_after();
             if (lane == 0) {
                 // the probabilities of tile t sit over its scores: 16 of them (8 columns) a K step
-                const uint32_t pa = tmem + (uint32_t)((t & 1) * TC_BN), va = smem_addr(stages + (t & 1) * TC_STAGE + TC_K_BYTES);
+                const uint32_t pa = tmem + (uint32_t)((t & 1) * TC_BN);
+                const uint64_t vd = v_desc0 + (uint64_t)(((t & 1) * TC_STAGE) >> 4);
+                if (t > 0) umma_f16_ts(tmem + TC_O, pa, vd, idesc_o, true);
+                else umma_f16_ts(tmem + TC_O, pa, vd, idesc_o, false);
 #pragma unroll
-                for (int kk = 0; kk < TC_BN / 16; ++kk)
-                    umma_f16_ts(tmem + TC_O, pa + kk * 8, smem_desc_sw128(va + kk * 2048, TC_BN * 128, 1024), idesc_o, t > 0 || kk > 0);
+                for (int kk = 1; kk < TC_BN / 16; ++kk) umma_f16_ts(tmem + TC_O, pa + kk * 8, vd + (uint64_t)(kk * 2048 >> 4), idesc_o, true);
                 umma_commit(bar(TC_VEMPTY + (t & 1)));
                 umma_commit(bar(TC_PVDONE));
             }
@@ -190,11 +197,11 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t qa = smem_addr(qs), ka = smem_addr(stages + s * TC_STAGE);
+                const uint64_t kd = k_desc0 + (uint64_t)((s * TC_STAGE) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < TC_D / 16; ++ks)
-                    umma_f16(tmem + (uint32_t)(s * TC_BN), smem_desc_sw128(qa + (ks >> 2) * (TC_ROWS * 128) + (ks & 3) * 32, 0, 1024),
-                             smem_desc_sw128(ka + (ks >> 2) * (TC_BN * 128) + (ks & 3) * 32, 0, 1024), idesc_s, ks > 0);
+                    umma_f16(tmem + (uint32_t)(s * TC_BN), q_desc + (uint64_t)(((ks >> 2) * (TC_ROWS * 128) + (ks & 3) * 32) >> 4),
+                             kd + (uint64_t)(((ks >> 2) * (TC_BN * 128) + (ks & 3) * 32) >> 4), idesc_s, ks > 0);
                 umma_commit(bar(TC_SFULL + s));
                 umma_commit(bar(TC_KEMPTY + s));
             }
