@@ -184,6 +184,47 @@ def test_tcgen05_tiles_with_outliers_and_long_rows(pk, kind):
     assert_attention_close(out, lse, want, want_lse, [0, 1, 2, 3, 4], rel=2.0 ** -7)
 
 
+def test_tcgen05_tiles_edge_cases(pk):
+    """The tcgen05 engine on the edges the m16n8k16 engine is held to: a NaN query stays in its own token, rows with no
+    columns and counts past the columns, FP16 queries, packed partial rows, and a row alone against the row in a batch."""
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache("fp8:page", 2, 128, 128, 16, [200, 1300, 40], spare=8)
+    q = queries(12, 8, 128, 2)
+    rows, starts, firsts = [0, 1, 2], [0, 4, 8], [196, 1296, 36]
+    clean = cache.attend(q, rows, starts, firsts, 4, engine="tcgen05")
+    q2 = q.clone()
+    q2[5, 3, 7] = float("nan")
+    got = cache.attend(q2, rows, starts, firsts, 4, engine="tcgen05")
+    assert torch.isnan(got[5, 3]).all()
+    keep = torch.ones(12, 8, dtype=torch.bool)
+    keep[5, 3] = False
+    assert torch.equal(got.cpu()[keep], clean.cpu()[keep])
+    # a row without columns writes nothing; a count past the columns reads as the columns
+    marked = torch.full_like(clean, 7.0)
+    some = cache.attend(q, rows, starts, firsts, 4, counts=[4, 0, 9], out=marked, engine="tcgen05")
+    assert torch.equal(some[0:4], clean[0:4]) and torch.equal(some[8:12], clean[8:12]) and bool((some[4:8] == 7.0).all())
+    # FP16 queries keep 8 of their 11 significant bits in the split: inside the bounds
+    qh = queries(12, 8, 128, 4, torch.float16)
+    cache16 = Cache("fp8:row", 2, 128, 128, 16, [200, 1300, 40], spare=8)
+    lse = torch.empty(12, 8, device="cuda")
+    out = cache16.attend(qh, rows, starts, firsts, 4, lse=lse, engine="tcgen05")
+    want, want_lse = cache16.oracle(qh, rows, starts, firsts, 4)
+    assert_attention_close(out, lse, want, want_lse, list(range(12)))
+    # packed partial rows (offsets) fold to the same bits as padded ones
+    offsets = torch.tensor([0, 2, 3], dtype=torch.int32, device="cuda")
+    splits = pk.parts_for(cache.tables.shape[1] * 16, 256)
+    space = torch.empty(pk.workspace_floats(7, 8, splits, 128), device="cuda")
+    padded = cache.attend(q, rows, starts, firsts, 4, counts=[2, 1, 4], chunk=256, engine="tcgen05")
+    packed = cache.attend(q, rows, starts, firsts, 4, counts=[2, 1, 4], offsets=offsets, tokens=7, workspace=space, chunk=256,
+                          engine="tcgen05")
+    for start, count in zip(starts, [2, 1, 4]):
+        assert torch.equal(packed[start:start + count], padded[start:start + count])
+    # a row alone and in a batch of the same columns: the same unit, the same bits
+    alone = cache.attend(q[4:8], [1], [0], [1296], 4, engine="tcgen05")
+    assert torch.equal(alone, clean[4:8])
+    assert pk.status() == 0
+
+
 def test_tcgen05_tiles_refuse_launches_they_do_not_serve(pk):
     from helpers import Cache, queries
     cache = Cache("bf16", 2, 128, 128, 16, [100])
