@@ -345,7 +345,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
     state = build_state(w, device, rank, world)
     # the verify workload runs on the tcgen05 engine (the library's default keeps a column's bits independent of its
-    # window, which costs 1.45x there); --engine mma.sync measures the default
+    # window, which costs 1.8-2x there); --engine mma.sync measures the default
     engine = args.engine or ("tcgen05" if args.workload == "c5" else None)
     state["staging"], state["engine"], state["chunk"] = args.staging, engine, args.chunk
     torch.cuda.synchronize()

@@ -318,7 +318,7 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     // The m16n8k16 kernel is the default for every launch: its bits do not depend on how many columns a launch has (a
     // draft verified in a window gets the bits a decode step gives it), which the tcgen05 kernel's column ownership
     // does not keep.  The tcgen05 kernel is the caller's choice (CRIT_B200_ATTEND_TCGEN05): on the speculative-verify
-    // workload it measured 316 us against 460 us, on decode rows of 8 heads 128 us against 112 us.
+    // workload it measured 250 us against 460-500 us, on decode rows of 8 heads 120 us against 112 us.
     const int nt = row_tiles(rows, p.value_dim);
     const int pk = page_class(p.kind, p.page_dtype);
     CUtensorMap kmap, vmap;
