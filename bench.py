@@ -203,7 +203,7 @@ def build_state(w, device, rank, world):
     if w["batch"] == 1 and world > 1:
         # one context over the ranks by KV range: every rank keeps the step's token rows, an empty rank sends -inf
         from crit_b200.dist import ShardMerge
-        state["merger"] = ShardMerge(cols, hq, d, device, out_dtype=torch.bfloat16)
+        state["merger"] = ShardMerge(cols, hq, d, device, out_dtype=torch.bfloat16, exchange=w.get("exchange", "auto"))
         state["out"].zero_()
         state["lse"].fill_(float("-inf"))
     return state
@@ -323,6 +323,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--staging", default=None, choices=["tma", "cp.async"])
     ap.add_argument("--engine", default=None, choices=["mma.sync", "tcgen05"], help="the attention kernel instead of the library's choice")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+                    help="how the KV-range shards' partials cross the GPUs (c3 on N > 1): stores into peer memory or NCCL's all-gather")
     ap.add_argument("--chunk", type=int, default=None, help="positions per split instead of the library's choice")
     ap.add_argument("--batch", type=int, default=None,
                     help="sequences per GPU instead of the workload's own (a small case for a profiler capture)")
@@ -333,6 +335,7 @@ def main():
     w = dict(WORKLOADS[args.workload])
     if args.batch:
         w["batch"], w["name"] = args.batch, w["name"] + f" [--batch {args.batch}: a reduced case]"
+    w["exchange"] = args.exchange
     reference = args.impl == "reference"
     if reference and rank != 0:
         return
@@ -352,6 +355,9 @@ def main():
     tokens_step = state["tokens"]
     steps_are = ("slot map + KV append + one prefill launch per sequence" if w["columns"] > 64
                  else "slot map + KV append + split-K decode + merge")
+    if state["merger"] is not None:
+        steps_are += (" + exchange of the shards' partials (" + ("stores into peer memory" if state["merger"].peer is not None
+                                                                  else "NCCL all-gather") + ") + merge of shards")
     config = {"workload": w["name"], "kv": w["kind"], "engine": engine or "library default", "steps_are": steps_are,
               "l2": "inputs larger than L2: every step reads the whole KV context "
                     f"({state['kv_bytes'] / 1e6:.1f} MB per GPU, L2 is 126 MB)",
@@ -435,7 +441,7 @@ def main():
             "e2e": {"value": kv_total / e2e_step_s / 1e9, "unit": unit, "tokens_per_s": tokens_total / e2e_step_s,
                     "ms_per_step": e2e_step_s * 1e3,
                     "h2d_bytes_per_step": state["h_in"].numel(), "d2h_bytes_per_step": state["h_res"].numel()},
-            "gpu_launches": (4 + (2 if state["merger"] is not None else 0)) * args.steps,
+            "gpu_launches": (4 + (0 if state["merger"] is None else (3 if state["merger"].peer is not None else 1))) * args.steps,
             "roofline": {"bound": "hbm", "kernel": ("decode_tc_kernel (tcgen05 split-K decode over paged E4M3 KV)" if state.get("engine") == "tcgen05"
                                                    else "decode_kernel (split-K decode over paged KV)"),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,

@@ -128,7 +128,8 @@ def status(device=None):
     """0, or what a kernel recorded on `device` since load, when one of its bounded waits ran out (the block concerned
     wrote nothing): 1 = a TMA copy of the m16n8k16 decode kernel; 0x110 / 0x120 / 0x140 = the producer / MMA / softmax
     warps of the tcgen05 prefill kernel (0x1ff: its shared memory was not 1 KB aligned); 0x410 / 0x420 / 0x440 = the
-    producer / MMA / softmax warps of the tcgen05 decode kernel.  Reads the device word (one synchronisation)."""
+    producer / MMA / softmax warps of the tcgen05 decode kernel; 0x800 + rank = the peer exchange of the shards' partials
+    waited in vain for another rank's message.  Reads the device word (one synchronisation)."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     found = _status.get(str(device))
     return 0 if found is None else int(found.item())

@@ -63,7 +63,12 @@ class PrefillParams(Structure):
                 ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float)]
 
 
-STRUCTS = (AppendParams, GatherParams, SlotsParams, AttendParams, MergeShardsParams, PrefillParams)
+class ExchangeParams(Structure):
+    _fields_ = [("mine", c_void_p), ("peers", c_void_p), ("step", c_void_p), ("gathered", c_void_p), ("status", c_void_p),
+                ("floats", c_int64), ("wait_ns", c_int64), ("world", c_int32), ("rank", c_int32)]
+
+
+STRUCTS = (AppendParams, GatherParams, SlotsParams, AttendParams, MergeShardsParams, PrefillParams, ExchangeParams)
 
 # name -> (restype, argtypes): every symbol include/crit_b200.h declares
 SYMBOLS = {
@@ -77,6 +82,9 @@ SYMBOLS = {
     "crit_b200_attend_static": (c_int, [POINTER(AttendParams), c_void_p]),
     "crit_b200_merge_shards": (c_int, [POINTER(MergeShardsParams), c_void_p]),
     "crit_b200_prefill": (c_int, [POINTER(PrefillParams), c_void_p]),
+    "crit_b200_shard_push": (c_int, [POINTER(ExchangeParams), c_void_p]),
+    "crit_b200_shard_wait": (c_int, [POINTER(ExchangeParams), c_void_p]),
+    "crit_b200_exchange_bytes": (c_int64, [c_int32, c_int64]),
     "crit_b200_abi_version": (c_int, []),
     "crit_b200_params_size": (c_int, [c_int32]),
     "crit_b200_error": (c_char_p, [c_int32]),

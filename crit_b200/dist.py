@@ -10,9 +10,14 @@ normalizers, reduce-scatter weighted outputs") and tests it with two pools on on
     disjoint rows.  assign_sequences() balances ranks by context length (longest first onto the lightest rank).
   - one long context shards BY KV RANGE: rank g owns a contiguous run of `partition`-position partitions, its pages are
     resident on its own GPU, every rank has the same queries.  Each rank runs the split-K decode over its own range
-    and folds its splits locally into one (out, lse) per (token, head); merge_across_ranks() all-gathers those
-    (tokens x heads x (dim + 1) floats a rank: 24.7 KB at 24 heads x 256) and folds them in rank order with the
-    merge-of-shards kernel, identically on every rank.  A rank with no positions contributes zeros and -inf.
+    and folds its splits locally into one (out, lse) per (token, head); ShardMerge exchanges those (tokens x heads x
+    (dim + 1) floats a rank: 24.7 KB at 24 heads x 256) and folds them in rank order with the merge-of-shards kernel,
+    identically on every rank.  A rank with no positions contributes zeros and -inf.  The exchange is the library's own
+    by default: every rank STORES its message into every other rank's buffer over NVLink peer memory (symmetric
+    memory mapped once; crit_b200_shard_push / crit_b200_shard_wait: two small launches, flags with system-scope
+    release / acquire, a bounded wait), because the payload is latency, not bandwidth: NCCL's all-gather of it measured
+    about 100 us on 8 GPUs, more than the decode launch it follows.  NCCL's all-gather stays as the fallback (no
+    symmetric memory) and as the baseline.
 
 Failure detection without faulting a GPU: every rank's message carries (rank, epoch, rows) in its last three floats;
 with check=True the gathered headers are read on the host and a stale, missing or foreign message raises before the
@@ -53,7 +58,10 @@ class ShardMerge:
     """Buffers (made once, so a captured step replays over them) and the exchange for rows of `tokens` x `heads`
     partials of width `dim`."""
 
-    def __init__(self, tokens, heads, dim, device, group=None, merge=None, out_dtype=None):
+    def __init__(self, tokens, heads, dim, device, group=None, merge=None, out_dtype=None, exchange="auto", wait_ms=2000):
+        """exchange: "peer" (stores into the ranks' symmetric buffers; raises where symmetric memory cannot be set up),
+        "nccl" (all_gather_into_tensor) or "auto" (peer where it can be set up, else nccl; the choice is agreed between
+        the ranks).  wait_ms: the bound of the peer exchange's wait for the other ranks' messages."""
         import torch
         import torch.distributed as dist
         self.torch, self.dist, self.group = torch, dist, group
@@ -66,6 +74,46 @@ class ShardMerge:
         self.all = torch.zeros(self.world, self.size, dtype=torch.float32, device=device)
         self.merge_fn, self.out_dtype = merge, out_dtype
         self.mine[-3], self.mine[-1] = float(self.rank), float(self.rows)
+        self.peer = None
+        if exchange not in ("auto", "peer", "nccl"):
+            raise ValueError(f"exchange is auto, peer or nccl, not {exchange!r}")
+        if self.world > 1 and exchange != "nccl" and torch.device(device).type == "cuda":
+            self.peer = self._peer_setup(device, wait_ms, must=exchange == "peer")
+
+    def _peer_setup(self, device, wait_ms, must):
+        """Maps one exchange buffer per rank into every rank (a collective) and returns the launch parameters, or None
+        when a rank could not (then every rank falls back together)."""
+        torch, dist = self.torch, self.dist
+        found, error = None, None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            from . import _lib
+            lib = _lib.load()
+            words = int(lib.crit_b200_exchange_bytes(self.world, self.size)) // 4
+            group = self.group if self.group is not None else dist.group.WORLD
+            buffer = symm.empty(words, dtype=torch.float32, device=device)
+            buffer.zero_()
+            handle = symm.rendezvous(buffer, group)
+            p = _lib.ExchangeParams()
+            peers = torch.tensor([int(a) for a in handle.buffer_ptrs], dtype=torch.int64, device=device)
+            step = torch.zeros(1, dtype=torch.int32, device=device)
+            p.mine, p.peers, p.step, p.gathered = self.mine.data_ptr(), peers.data_ptr(), step.data_ptr(), self.all.data_ptr()
+            import crit_b200
+            status = crit_b200._status_word(torch.device(device))
+            p.status = status.data_ptr() if status is not None else None
+            p.floats, p.wait_ns, p.world, p.rank = self.size, int(wait_ms) * 1000000, self.world, self.rank
+            found = dict(lib=lib, params=p, keep=(buffer, handle, peers, step, status), check=_lib.check)
+        except Exception as problem:       # no symmetric memory here (driver, permissions, an older torch)
+            error = problem
+        # every rank takes the same road, and nobody pushes before every buffer is zeroed
+        torch.cuda.synchronize()
+        agreed = torch.tensor([1 if found is not None else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=self.group)
+        if int(agreed.item()) == 0:
+            if must:
+                raise RuntimeError(f"the peer exchange could not be set up on every rank ({error})")
+            return None
+        return found
 
     def merge(self, out, lse, check=False, epoch=None):
         """This rank's (out [tokens][heads][dim], lse [tokens][heads]; lse -inf and out 0 where it saw no key) ->
@@ -80,7 +128,14 @@ class ShardMerge:
             self.mine[-2:-1].add_(1.0)
         else:
             self.mine[-2:-1].fill_(float(epoch))
-        if self.world > 1:
+        if self.peer is not None:
+            stream = self.torch.cuda.current_stream().cuda_stream
+            with self.torch.cuda.device(self.mine.device):
+                import ctypes
+                ref = ctypes.byref(self.peer["params"])
+                self.peer["check"](self.peer["lib"].crit_b200_shard_push(ref, stream), "crit_b200.dist.ShardMerge (push)")
+                self.peer["check"](self.peer["lib"].crit_b200_shard_wait(ref, stream), "crit_b200.dist.ShardMerge (wait)")
+        elif self.world > 1:
             self.dist.all_gather_into_tensor(self.all.view(-1), self.mine, group=self.group)
         else:
             self.all[0].copy_(self.mine)

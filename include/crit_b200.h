@@ -194,6 +194,31 @@ typedef struct crit_b200_merge_shards_params {
 
 int crit_b200_merge_shards(const crit_b200_merge_shards_params* params, void* stream);
 
+/* -- the exchange of the shards' partials over peer memory ---------------------------------------------------------------
+ * What an engine with one process per GPU runs between its ranks' partial attention and crit_b200_merge_shards, in place
+ * of a collective library's all-gather (the reference leaves "partitioning and collectives" to the engine:
+ * inference/partitioned-attention/README.md; its merge is plugin.py:52-64).  Every rank owns one exchange buffer of
+ * crit_b200_exchange_bytes(world, floats) bytes, zeroed before the first step, that every rank has mapped; `peers` is a
+ * DEVICE array of this GPU's addresses of all `world` buffers.  crit_b200_shard_push adds one to *step (a device
+ * counter, so the pair is capturable in a CUDA graph), stores `mine` into every rank's buffer and raises this rank's flag
+ * there; it never waits.  crit_b200_shard_wait waits at most wait_ns nanoseconds for the `world` messages of the step to
+ * land in this rank's own buffer and copies them to gathered [world][floats] (the layout crit_b200_merge_shards reads);
+ * when the wait runs out it copies nothing and sets *status (0x800 + rank).  Only stores cross NVLink. */
+typedef struct crit_b200_exchange_params {
+    const float* mine;           /* this rank's message, 16-byte aligned */
+    const uint64_t* peers;       /* [world] device array of buffer addresses */
+    int32_t* step;               /* device counter of steps, the same on every rank */
+    float* gathered;             /* [world][floats] */
+    int32_t* status;             /* or NULL */
+    int64_t floats;
+    int64_t wait_ns;
+    int32_t world, rank;
+} crit_b200_exchange_params;
+
+int crit_b200_shard_push(const crit_b200_exchange_params* params, void* stream);
+int crit_b200_shard_wait(const crit_b200_exchange_params* params, void* stream);
+int64_t crit_b200_exchange_bytes(int32_t world, int64_t floats);
+
 /* -- chunked prefill ---------------------------------------------------------------------------------------------
  * Replaces paged_kv_attention.prefill (paged_kv_attention/__init__.py:1245-1332; kernel _kernels.py:610-726) behind
  * DeviceAttention._prefill_rows (device_attention.py:901-916): one sequence's chunk of `tokens` queries at positions

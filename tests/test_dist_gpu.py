@@ -1,6 +1,7 @@
-"""Two GPUs, one process each (NCCL): a context sharded by KV range, each rank's split-K decode over its own pages,
-the (out, lse) partials all-gathered and merged, against the CPU oracle over the whole context.  Skipped with fewer
-than two GPUs."""
+"""Two GPUs, one process each: a context sharded by KV range, each rank's split-K decode over its own pages, the
+(out, lse) partials exchanged (NCCL all-gather, and the library's own stores into peer memory) and merged, against the
+CPU oracle over the whole context; the two exchanges give the same bits, step after step and from a CUDA graph.
+Skipped with fewer than two GPUs."""
 import os
 import socket
 
@@ -40,15 +41,33 @@ def _rank(rank, world, port, queue):
             i32 = dict(dtype=torch.int32, device=dev)
             pk.attend(q.to(dev), k, v, "bf16", table, torch.zeros(1, **i32), torch.zeros(1, **i32),
                       torch.tensor([mine - 1], device=dev), 1, page, out=out, lse=lse, chunk=256)
-        merger = ShardMerge(1, hq, d, dev)
+        merger = ShardMerge(1, hq, d, dev, exchange="nccl")
         merged, merged_lse = merger.merge(out, lse, check=True)
+        # the peer-memory exchange: the same bits, over several steps (the slots alternate) and replayed from a graph
+        peer = ShardMerge(1, hq, d, dev, exchange="auto", wait_ms=500)
+        same = peer.peer is not None
+        if same:
+            for _ in range(3):
+                again, again_lse = peer.merge(out, lse, check=True)
+                same = same and torch.equal(again, merged) and torch.equal(again_lse, merged_lse)
+            stream = torch.cuda.Stream(dev)
+            with torch.cuda.stream(stream):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    captured, captured_lse = peer.merge(out, lse)
+                for _ in range(3):
+                    graph.replay()
+                stream.synchronize()
+            peer.verify()
+            same = same and torch.equal(captured, merged) and torch.equal(captured_lse, merged_lse) and pk.status(dev) == 0
         whole_table = np.arange(-(-n // page), dtype=np.int32)
         kf = np.zeros((len(whole_table) * page, hkv, d), np.float32)
         vf = np.zeros_like(kf)
         kf[:n], vf[:n] = keys.float().numpy(), values.float().numpy()
         want, want_lse = oracle.attend(q.float().numpy(), kf, vf, whole_table, [0], [0], [n - 1], 1, page)
         err = np.abs(merged.float().cpu().numpy() - want)
-        queue.put((rank, float(err.max()), float(err.mean()), float(np.abs(merged_lse.cpu().numpy() - want_lse).max())))
+        queue.put((rank, float(err.max()), float(err.mean()), float(np.abs(merged_lse.cpu().numpy() - want_lse).max()),
+                   "peer exchange not set up" if peer.peer is None else bool(same)))
     finally:
         dist.destroy_process_group()
 
@@ -68,5 +87,6 @@ def test_kv_range_shards_over_two_gpus_merge_to_the_whole():
     found = [queue.get(timeout=300) for _ in procs]
     for p in procs:
         p.join(60)
-    for rank, max_abs, mean_abs, lse_abs in found:
+    for rank, max_abs, mean_abs, lse_abs, peer in found:
         assert max_abs <= 2e-2 and mean_abs <= 2e-3 and lse_abs <= 2e-3, (rank, max_abs, mean_abs, lse_abs)
+        assert peer is True, (rank, peer)
