@@ -54,6 +54,41 @@ def kv_ranges(context, world, partition=4096):
             for r in range(world)]
 
 
+class PeerExchange:
+    """The two launches of the peer-memory exchange for one rank (crit_b200_shard_push / crit_b200_shard_wait): `peers`
+    is an int64 device tensor of this GPU's addresses of every rank's exchange buffer (exchange_bytes() each, zeroed
+    before the first step), `mine` this rank's FP32 message and `gathered` [world][floats] where the ranks' messages
+    land.  status: an int32 device tensor the wait sets (0x800 + rank) when it ran out, or None."""
+
+    def __init__(self, peers, rank, world, mine, gathered, wait_ms=2000, status=None):
+        import ctypes
+        import torch
+        from . import _lib
+        self._lib, self._ctypes, self._torch = _lib, ctypes, torch
+        self.step = torch.zeros(1, dtype=torch.int32, device=mine.device)
+        p = self.params = _lib.ExchangeParams()
+        p.mine, p.peers, p.step, p.gathered = mine.data_ptr(), peers.data_ptr(), self.step.data_ptr(), gathered.data_ptr()
+        p.status = status.data_ptr() if status is not None else None
+        p.floats, p.wait_ns, p.world, p.rank = mine.numel(), int(wait_ms) * 1000000, world, rank
+        self._keep = (peers, mine, gathered, status)
+
+    @staticmethod
+    def exchange_bytes(world, floats):
+        from . import _lib
+        return int(_lib.load().crit_b200_exchange_bytes(world, floats))
+
+    def _launch(self, fn, what):
+        stream = self._torch.cuda.current_stream().cuda_stream
+        with self._torch.cuda.device(self._keep[1].device):
+            self._lib.check(fn(self._ctypes.byref(self.params), stream), what)
+
+    def push(self):
+        self._launch(self._lib.load().crit_b200_shard_push, "crit_b200.dist.PeerExchange.push")
+
+    def wait(self):
+        self._launch(self._lib.load().crit_b200_shard_wait, "crit_b200.dist.PeerExchange.wait")
+
+
 class ShardMerge:
     """Buffers (made once, so a captured step replays over them) and the exchange for rows of `tokens` x `heads`
     partials of width `dim`."""
@@ -87,22 +122,16 @@ class ShardMerge:
         found, error = None, None
         try:
             import torch.distributed._symmetric_memory as symm
-            from . import _lib
-            lib = _lib.load()
-            words = int(lib.crit_b200_exchange_bytes(self.world, self.size)) // 4
+            import crit_b200
+            words = PeerExchange.exchange_bytes(self.world, self.size) // 4
             group = self.group if self.group is not None else dist.group.WORLD
             buffer = symm.empty(words, dtype=torch.float32, device=device)
             buffer.zero_()
             handle = symm.rendezvous(buffer, group)
-            p = _lib.ExchangeParams()
             peers = torch.tensor([int(a) for a in handle.buffer_ptrs], dtype=torch.int64, device=device)
-            step = torch.zeros(1, dtype=torch.int32, device=device)
-            p.mine, p.peers, p.step, p.gathered = self.mine.data_ptr(), peers.data_ptr(), step.data_ptr(), self.all.data_ptr()
-            import crit_b200
-            status = crit_b200._status_word(torch.device(device))
-            p.status = status.data_ptr() if status is not None else None
-            p.floats, p.wait_ns, p.world, p.rank = self.size, int(wait_ms) * 1000000, self.world, self.rank
-            found = dict(lib=lib, params=p, keep=(buffer, handle, peers, step, status), check=_lib.check)
+            found = PeerExchange(peers, self.rank, self.world, self.mine, self.all, wait_ms,
+                                 crit_b200._status_word(torch.device(device)))
+            found._symmetric = (buffer, handle)
         except Exception as problem:       # no symmetric memory here (driver, permissions, an older torch)
             error = problem
         # every rank takes the same road, and nobody pushes before every buffer is zeroed
@@ -129,12 +158,8 @@ class ShardMerge:
         else:
             self.mine[-2:-1].fill_(float(epoch))
         if self.peer is not None:
-            stream = self.torch.cuda.current_stream().cuda_stream
-            with self.torch.cuda.device(self.mine.device):
-                import ctypes
-                ref = ctypes.byref(self.peer["params"])
-                self.peer["check"](self.peer["lib"].crit_b200_shard_push(ref, stream), "crit_b200.dist.ShardMerge (push)")
-                self.peer["check"](self.peer["lib"].crit_b200_shard_wait(ref, stream), "crit_b200.dist.ShardMerge (wait)")
+            self.peer.push()
+            self.peer.wait()
         elif self.world > 1:
             self.dist.all_gather_into_tensor(self.all.view(-1), self.mine, group=self.group)
         else:

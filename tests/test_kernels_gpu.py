@@ -451,3 +451,45 @@ def test_merged_shards_equal_attention_over_the_whole_sequence(pk):
     merged, merged_lse = pk.merge_shards([o for o, _ in parts], [x for _, x in parts])
     torch.testing.assert_close(merged, out.float(), atol=2e-2, rtol=2e-2)
     torch.testing.assert_close(merged_lse, lse, atol=2e-3, rtol=1e-4)
+
+
+# -- the exchange of the shards' partials over peer memory ----------------------------------------------------------------
+def test_the_peer_exchange_lands_every_ranks_message_and_a_missing_rank_runs_the_wait_out(pk):
+    """Two ranks' exchange buffers on one GPU, the launches one after another on one stream: messages land in both
+    buffers, the slots alternate from step to step, and a rank whose partner never pushes gets the status word after its
+    bounded wait and no data (the way the path detects a lost rank without any GPU fault)."""
+    from crit_b200.dist import PeerExchange
+    dev, world, floats = torch.device("cuda"), 2, 1003
+    size = PeerExchange.exchange_bytes(world, floats)
+    buffers = [torch.zeros(size // 4, dtype=torch.float32, device=dev) for _ in range(world)]
+    peers = torch.tensor([b.data_ptr() for b in buffers], dtype=torch.int64, device=dev)
+    mine = [torch.zeros(floats, device=dev) for _ in range(world)]
+    gathered = [torch.full((world, floats), -1.0, device=dev) for _ in range(world)]
+    status = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(world)]
+    ranks = [PeerExchange(peers, r, world, mine[r], gathered[r], wait_ms=30, status=status[r]) for r in range(world)]
+    g = torch.Generator().manual_seed(3)
+    # step 1: rank 1 never pushes; rank 0's wait runs out, says so and publishes nothing
+    mine[0].copy_(torch.randn(floats, generator=g))
+    ranks[0].push()
+    ranks[0].wait()
+    torch.cuda.synchronize()
+    assert int(status[0].item()) == 0x800 and bool((gathered[0] == -1.0).all())
+    status[0].zero_()
+    # ... then rank 1 joins the step: both ranks see both messages
+    mine[1].copy_(torch.randn(floats, generator=g))
+    ranks[1].push()
+    for r in range(world):
+        ranks[r].wait()
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.equal(gathered[r][0], mine[0]) and torch.equal(gathered[r][1], mine[1]) and int(status[r].item()) == 0
+    # steps 2 and 3: new messages through the other slot and back
+    for _ in range(2):
+        for r in range(world):
+            mine[r].copy_(torch.randn(floats, generator=g))
+            ranks[r].push()
+        for r in range(world):
+            ranks[r].wait()
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.equal(gathered[r][0], mine[0]) and torch.equal(gathered[r][1], mine[1]) and int(status[r].item()) == 0
