@@ -403,7 +403,19 @@ def main():
             seconds = timed(run, args.steps, args.warmup, stream)
             # the dominant kernel alone (same stream, CUDA events): the split-K decode launch
             decode_s = timed(lambda: step(state, launch="decode", append=False), max(20, args.steps // 4), 3, stream)
-            merge_s = timed(lambda: step(state, launch="merge", append=False), max(20, args.steps // 4), 3, stream)
+            # the fold of the splits is a few microseconds: launched back to back from a graph, so that the launches' host
+            # cost is not what is timed
+            merge_fn, merge_reps = (lambda: step(state, launch="merge", append=False)), 1
+            if not args.no_graph and w["columns"] <= 64:
+                try:
+                    merge_graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(merge_graph, stream=stream):
+                        for _ in range(10):
+                            step(state, launch="merge", append=False)
+                    merge_fn, merge_reps = merge_graph.replay, 10
+                except Exception:
+                    torch.cuda.synchronize()
+            merge_s = timed(merge_fn, max(20, args.steps // 4), 3, stream) / merge_reps
         barrier()
 
         # end to end: the step's inputs from pinned host memory, the outputs read back, every step
