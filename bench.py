@@ -244,6 +244,7 @@ def step(state, launch="both", append=True):
 # once; the writes are the partial states, a fixed number per 1,024 positions), so a launch's traffic is its algorithmic
 # bytes times the ratio.  None where no capture was made.
 TRAFFIC_RATIO = {("c2", None): (540.9e6 + 9.7e6) / 537.9e6,            # decode_kernel, configs[1] at full size
+                 ("c3", None): (819.4e6 + 7.6e6) / 819.2e6,            # decode_kernel (TMA), configs[2] at full size
                  ("c5", "tcgen05"): (167.9e6 + 4.7e6) / 167.0e6}       # decode_tc_kernel<4>, configs[4] at 8 sequences
 
 
