@@ -26,7 +26,7 @@ import torch
 from . import _lib
 
 __all__ = ["KINDS", "MAX_COLUMNS", "attend", "chunk_for", "gather", "merge_shards", "owner", "partitions", "parts_for",
-           "piece_size", "prefill", "prefill_serves", "release", "slots_at", "status", "tcgen05_serves", "tile_for", "workspace_floats", "write"]
+           "piece_size", "plan", "prefill", "prefill_serves", "release", "slots_at", "status", "tcgen05_serves", "tile_for", "workspace_floats", "write"]
 
 KINDS = {"bf16": 0, "fp16": 0, "fp8": 1, "fp8:row": 2, "int8": 3, "fp8:page": 4}
 MAX_COLUMNS = 64            # columns of one row a launch reads
@@ -136,17 +136,22 @@ def status(device=None):
 
 
 # -- geometry rules -----------------------------------------------------------------------------------------------------
-def chunk_for(head_dim, value_dim, heads, kv_heads, page, kind="bf16", engine=None):
-    """Positions per split of every launch over a cache of this geometry (a multiple of 16): fixed per cache, never by
-    the batch, so a column's bits are the same alone and in any window.  The tcgen05 engine takes splits of 2,048 (a
-    unit's fold of its lane replicas is paid once per split: 277 us against 350 us on the speculative-verify workload)."""
-    return 2 * DEFAULT_CHUNK if engine == "tcgen05" else DEFAULT_CHUNK
+def chunk_for(head_dim, value_dim, heads, kv_heads, page, kind="bf16", engine=None, columns=1):
+    """Positions per split of a launch over a cache of this geometry (a multiple of 16).  One per cache for the
+    m16n8k16 kernel, never by the batch, so a column's bits are the same alone and in any window.  Launches the tcgen05
+    kernel takes (engine "tcgen05", or the library's choice for windows of several columns over E4M3 pages) use splits
+    of 2,048: a unit's fold of its lane replicas is paid once per split."""
+    if engine == "tcgen05" or (engine is None and columns > 1 and
+                               tcgen05_serves(kind, head_dim, value_dim, heads, kv_heads, columns, 2 * DEFAULT_CHUNK)):
+        return 2 * DEFAULT_CHUNK
+    return DEFAULT_CHUNK
 
 
 def tcgen05_serves(kind, head_dim, value_dim, heads, kv_heads, columns, chunk, rows=1):
-    """Whether attend(engine="tcgen05") takes a launch: E4M3 pages of 128-wide heads, at most 32 query rows a unit
-    (columns x heads of a kv head's group), splits of whole 128-position tiles up to 2,048 positions, up to 256 window
-    rows (the same test the library makes: decode.cu, tc_serves)."""
+    """Whether the tcgen05 kernel takes a launch: E4M3 pages of 128-wide heads, at most 32 query rows a unit (columns
+    x heads of a kv head's group), splits of whole 128-position tiles up to 2,048 positions, up to 256 window rows (the
+    same test the library makes: decode.cu, tc_serves).  The library sends such launches there by itself when they have
+    more than one column; engine="mma.sync" keeps them on the m16n8k16 kernel."""
     return (str(kind).startswith("fp8") and head_dim == 128 and value_dim == 128 and columns * (heads // kv_heads) <= 32
             and chunk % 128 == 0 and chunk <= 2048 and rows <= 256)
 
@@ -156,11 +161,37 @@ def parts_for(positions, chunk):
     return max(1, -(-int(positions) // int(chunk)))
 
 
+_plans = {}
+
+
+def plan(heads, kv_heads, head_dim, value_dim, page, kind="bf16", columns=1, device=None):
+    """What the library would launch for a cache of this geometry on `device`: a dict of chunk (positions per split),
+    smem (bytes of shared memory a block takes), rows (query rows a block's tile holds), per_sm (blocks resident per
+    SM) and sms.  Asked of the library once per geometry and device (crit_b200_attend_plan)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (str(device), heads, kv_heads, head_dim, value_dim, page, kind, columns)
+    found = _plans.get(key)
+    if found is None:
+        out = (ctypes.c_int32 * 5)()
+        dtype = _lib.DTYPE_FP16 if kind == "fp16" else _lib.DTYPE_BF16
+        with torch.cuda.device(device):
+            _lib.check(_lib.load().crit_b200_attend_plan(heads, kv_heads, head_dim, value_dim, page, KINDS[kind], dtype, columns, out),
+                       "crit_b200.plan")
+        found = _plans[key] = dict(chunk=out[0], smem=out[1], rows=out[2], per_sm=out[3], sms=out[4])
+    return found
+
+
 def partitions(device, kv_heads, kind, head_dim=None, value_dim=None):
     """The most splits a partial row takes in a launch whose caller sizes the workspace by a count per cache
-    (reference: paged_kv_attention/__init__.py:260-273).  attend(partitions=P) never makes more than P splits: it
-    raises the chunk where a row's tables hold more than P * chunk positions."""
-    return 64
+    (reference: paged_kv_attention/__init__.py:260-273, a rule over the device's SMs, the kv heads and the code width).
+    Here: enough splits for two waves of the device's resident blocks from ONE row (its splits x kv_heads blocks), as
+    a power of two in 8..128.  attend(partitions=P) never makes more than P splits: it raises the chunk where a row's
+    tables hold more than P * chunk positions."""
+    head_dim = head_dim or 128
+    value_dim = value_dim or head_dim
+    found = plan(kv_heads, kv_heads, head_dim, value_dim, TILE, kind, 1, device)
+    want = max(1, 2 * found["sms"] * max(found["per_sm"], 1) // max(kv_heads, 1))
+    return min(128, max(8, 1 << (want.bit_length() - 1)))
 
 
 def piece_size(head_dim, value_dim, kind="bf16", kv_heads=None):
@@ -169,9 +200,12 @@ def piece_size(head_dim, value_dim, kind="bf16", kv_heads=None):
 
 
 def tile_for(columns, group, capability, fused=False):
-    """(rows, warps, stages) of a launch's query tile: 16 query rows (columns x the group's heads), 32 where they pass
-    16 and the heads are up to 128 wide; four warps, each with its own ring of stages (reference: __init__.py:335-356)."""
-    return (32 if columns * group > 16 else 16), 4, 4
+    """(rows, warps, stages) of a launch's query tile (reference: __init__.py:335-356): 8, 16 or 32 query rows (columns
+    x the group's heads, in tiles of 8), four warps, each with its own ring of 3 or 4 stages (4 where a warp's
+    iteration takes two 16-position tiles, which 8-bit pages of heads up to 128 wide do; the width is not an argument
+    here, so the deeper ring is reported)."""
+    rows = columns * group
+    return (8 if rows <= 8 else (16 if rows <= 16 else 32)), 4, 4
 
 
 def workspace_floats(tokens, heads, partitions, value_dim):
@@ -217,6 +251,8 @@ def write(keys, values, slots, key_pages, value_pages, kind, key_scales=None, va
     p.key_pages, p.value_pages = _ptr(key_pages), _ptr(value_pages)
     p.key_scales, p.value_scales = _ptr(key_scales), _ptr(value_scales)
     p.tokens = T
+    p.slots_total = key_pages.numel() // (hkv * d)
+    p.status = _ptr(_status_word(keys.device))
     p.key_stride_token, p.key_stride_head = keys.stride(0), keys.stride(1)
     if values is not None:
         p.value_stride_token, p.value_stride_head = values.stride(0), values.stride(1)
@@ -249,6 +285,10 @@ def gather(pages, kind, page, *, table=None, slots=None, count=None, scales=None
     p.pages, p.scales, p.out = _ptr(pages), _ptr(scales), _ptr(out)
     p.table = _ptr(table.contiguous()) if table is not None else None
     p.slots = _ptr(slots)
+    if not pages.is_contiguous():
+        raise ValueError("pages are contiguous [slots][kv_heads][dim] storage")
+    p.slots_total = pages.numel() // (hkv * dim)
+    p.status = _ptr(_status_word(pages.device))
     p.count, p.kv_heads, p.dim, p.page = count, hkv, dim, int(page)
     p.kind, p.page_dtype, p.out_dtype = k_kind, _page_dtype(kind, pages), _DTYPES[dtype]
     p.multiplier = float(multiplier)
@@ -290,7 +330,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
            partitions=None, parents=None, blocks=None, block_size=None, out=None, lse=None, workspace=None, piece=None,
            fused=False, fresh=None, vsplit=None, tile=None, num_warps=None, num_stages=None, maxnreg=None,
            flash=False, chunk=None, ramp=None, sinks=None, sliding=0, derive=None, launch="both", staging=None,
-           persistent=False, engine=None):
+           persistent=False, engine=None, shards=None):
     """Decode and verify windows over paged KV (reference: paged_kv_attention/__init__.py:396-445, same arguments).
 
     q [tokens][heads][dim] bf16 or fp16 (fp16 for "fp16" pages); key_pages / value_pages one layer's pages
@@ -308,7 +348,10 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     number of blocks walk a work list built on the device from the rows' lengths, instead of one block per (split, kv
     head, row) of a 3-D grid (the same bits; measured slower on the bench workloads, hence off).  engine: None (the
     library's choice), "mma.sync" (the m16n8k16 kernel) or "tcgen05" (E4M3 page bytes straight into tcgen05.mma: E4M3
-    pages of 128-wide heads, columns x group heads <= 32, chunk a multiple of 128; refused elsewhere)."""
+    pages of 128-wide heads, columns x group heads <= 32, chunk a multiple of 128; refused elsewhere).
+    shards: a crit_b200.dist.ShardMerge: these pages hold one KV range of a context sharded over the ranks; every
+    split state stays in the workspace, the fold of this rank's splits is stored into every rank's exchange buffer and
+    out / lse get the merge over all ranks (three launches: decode, fold + push, wait + merge)."""
     _refuse(parents=parents, blocks=blocks, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
@@ -329,9 +372,11 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     page = int(page)
     if page % TILE:
         raise ValueError(f"crit_b200 reads pages of a multiple of {TILE} positions, not {page}")
+    if not key_pages.is_contiguous() or not value_pages.is_contiguous():
+        raise ValueError("pages are contiguous [slots][kv_heads][dim] storage")
     device = q.device
     positions = tables.shape[1] * page
-    chunk = int(chunk or chunk_for(d, dv, hq, hkv, page, kind, engine))
+    chunk = int(chunk or chunk_for(d, dv, hq, hkv, page, kind, engine, int(columns)))
     if partitions:
         chunk = max(chunk, -(-positions // int(partitions)))
     chunk = -(-chunk // TILE) * TILE
@@ -341,7 +386,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     if out.dtype != q.dtype or out.stride(-1) != 1:
         raise ValueError("out is in q's dtype, its last dimension contiguous")
     p = _lib.AttendParams()
-    if splits > 1:
+    if splits > 1 or shards is not None:
         floats = workspace_floats(partial_rows, hq, splits, dv)
         space = _workspace(device, floats, workspace)
         p.workspace, p.workspace_floats = _ptr(space), space.numel()
@@ -363,11 +408,20 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     if staging not in (None, "tma", "cp.async"):
         raise ValueError("staging is None, tma or cp.async")
     p.flags = ({None: 0, "cp.async": 1, "tma": 2}[staging] | (4 if persistent else 0) |
-               {None: 0, "tcgen05": 8, "mma.sync": 16}[engine])
+               {None: 0, "tcgen05": 8, "mma.sync": 16}[engine] | (32 if shards is not None else 0))
     p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])
     lib = _lib.load()
+    if shards is not None:
+        if lse is None:
+            raise ValueError("a sharded context's merge writes lse too: pass lse")
+        with torch.cuda.device(device):
+            if launch in ("both", "decode"):
+                _lib.check(lib.crit_b200_decode(ctypes.byref(p), _stream(device)), "crit_b200.attend")
+            if launch in ("both", "merge"):
+                shards.attend(p, out, lse)
+        return out
     call = {"both": lib.crit_b200_attend, "decode": lib.crit_b200_decode, "merge": lib.crit_b200_merge}[launch]
     with torch.cuda.device(device):
         _lib.check(call(ctypes.byref(p), _stream(device)), "crit_b200.attend")
@@ -421,6 +475,8 @@ def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scale
     hkv = key_pages.shape[-2]
     if value_pages.shape[-1] != d:
         raise ValueError("prompt chunks read keys and values of one width")
+    if not key_pages.is_contiguous() or not value_pages.is_contiguous():
+        raise ValueError("pages are contiguous [slots][kv_heads][dim] storage")
     out = torch.empty_like(q) if out is None else out
     if q.stride(-1) != 1 or out.stride(-1) != 1 or table.dtype != torch.int32 or not table.is_contiguous():
         raise ValueError("q and out have contiguous last dimensions, table is contiguous int32")

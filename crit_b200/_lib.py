@@ -5,7 +5,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 from pathlib import Path
 
 LIBRARY = Path(__file__).resolve().parent / "_native" / "libcrit_b200.so"
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 KIND_16BIT, KIND_FP8, KIND_FP8_ROW, KIND_INT8, KIND_FP8_PAGE = range(5)
 DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = range(3)
@@ -13,8 +13,8 @@ DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = range(3)
 
 class AppendParams(Structure):
     _fields_ = [("keys", c_void_p), ("values", c_void_p), ("slots", c_void_p), ("key_pages", c_void_p),
-                ("value_pages", c_void_p), ("key_scales", c_void_p), ("value_scales", c_void_p),
-                ("tokens", c_int64), ("key_stride_token", c_int64), ("key_stride_head", c_int64),
+                ("value_pages", c_void_p), ("key_scales", c_void_p), ("value_scales", c_void_p), ("status", c_void_p),
+                ("tokens", c_int64), ("slots_total", c_int64), ("key_stride_token", c_int64), ("key_stride_head", c_int64),
                 ("value_stride_token", c_int64), ("value_stride_head", c_int64),
                 ("kv_heads", c_int32), ("head_dim", c_int32), ("value_dim", c_int32), ("page", c_int32),
                 ("kind", c_int32), ("in_dtype", c_int32), ("page_dtype", c_int32),
@@ -23,7 +23,7 @@ class AppendParams(Structure):
 
 class GatherParams(Structure):
     _fields_ = [("pages", c_void_p), ("scales", c_void_p), ("table", c_void_p), ("slots", c_void_p), ("out", c_void_p),
-                ("count", c_int64), ("kv_heads", c_int32), ("dim", c_int32), ("page", c_int32),
+                ("status", c_void_p), ("count", c_int64), ("slots_total", c_int64), ("kv_heads", c_int32), ("dim", c_int32), ("page", c_int32),
                 ("kind", c_int32), ("page_dtype", c_int32), ("out_dtype", c_int32), ("multiplier", c_float)]
 
 
@@ -84,6 +84,8 @@ SYMBOLS = {
     "crit_b200_prefill": (c_int, [POINTER(PrefillParams), c_void_p]),
     "crit_b200_shard_push": (c_int, [POINTER(ExchangeParams), c_void_p]),
     "crit_b200_shard_wait": (c_int, [POINTER(ExchangeParams), c_void_p]),
+    "crit_b200_merge_push": (c_int, [POINTER(AttendParams), POINTER(ExchangeParams), c_void_p]),
+    "crit_b200_wait_merge": (c_int, [POINTER(ExchangeParams), POINTER(MergeShardsParams), c_void_p]),
     "crit_b200_exchange_bytes": (c_int64, [c_int32, c_int64]),
     "crit_b200_abi_version": (c_int, []),
     "crit_b200_params_size": (c_int, [c_int32]),

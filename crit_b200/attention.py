@@ -33,19 +33,20 @@ class Windows:
 class DeviceAttention:
     def __init__(self, kernels=None, mode="auto", int8_qk=False, decode="split", partitions=0, piece=0, device=None,
                  kernels_mib=128, flashinfer="off", flashinfer_mib=128, prompt_reader="prefill", reader="split",
-                 latent=None, scratch=None, chunk=0, window_engine="mma.sync"):
+                 latent=None, scratch=None, chunk=0, window_engine="auto"):
         """kernels: the crit_b200 module (default).  partitions: the most splits of a partial row (0: what the tables
         need); chunk: positions per split (0: the kernels' rule).  kernels_mib: the most partials a launch takes from
         `scratch` (the engine's Scratch, crit_plugins.memory) when one is given.  prompt_reader: "prefill" or "decode".
-        window_engine: "mma.sync" (the m16n8k16 kernel: a column's bits are the same alone and in any window) or
-        "tcgen05" (E4M3 pages go straight into tcgen05.mma wherever that kernel serves a launch: faster on verify windows,
-        and a column's bits then depend on the window it is read in).
+        window_engine: "auto" (the kernels' choice: windows of several columns over E4M3 pages on tcgen05 tiles, decode
+        rows on m16n8k16 tiles; a column's bits then depend on the window it is read in: exactness "repeatable"),
+        "mma.sync" (the m16n8k16 kernel always: a column's bits are the same alone and in any window, "row-exact") or
+        "tcgen05" (tcgen05 tiles wherever that kernel serves a launch, decode rows included).
         mode "torch", decode "flashinfer", flashinfer "auto", int8_qk and latent are the reference's other readers: not
         served here."""
         if mode == "torch" or decode != "split" or flashinfer != "off" or int8_qk or latent is not None:
             raise ValueError("crit_b200 serves its own CUDA kernels only (mode auto, decode split, flashinfer off)")
-        if window_engine not in ("mma.sync", "tcgen05"):
-            raise ValueError(f"window_engine is mma.sync or tcgen05, not {window_engine!r}")
+        if window_engine not in ("auto", "mma.sync", "tcgen05"):
+            raise ValueError(f"window_engine is auto, mma.sync or tcgen05, not {window_engine!r}")
         self.window_engine = window_engine
         if prompt_reader not in ("prefill", "decode"):
             raise ValueError(f"prompt_reader is prefill or decode, not {prompt_reader!r}")
@@ -63,7 +64,7 @@ class DeviceAttention:
     def facts(self):
         return {"reader": "crit_b200: a row's positions in contiguous splits of one chunk per pool, folded in split order; " +
                           ("a column's bits are the same alone and in any window" if self.window_engine == "mma.sync" else
-                           "E4M3 pages through tcgen05.mma where served: a column's bits depend on its window"),
+                           "windows over E4M3 pages through tcgen05.mma where served: a column's bits depend on its window"),
                 "prompt_reads": "through the prefill kernel" if self.prompt_reader == "prefill" else
                                 "in the decode's reduction (pieces of up to 64 columns)",
                 "split_kv_wide_windows": "16- or 32-row tiles; wider windows read their pages once per tile"}
@@ -140,7 +141,7 @@ class DeviceAttention:
         kernels = self.kernels
         positions = meta.tables.shape[1] * pool.page
         chunk = self.chunk or kernels.chunk_for(pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, pool.page, pool.dtype,
-                                                self.window_engine if self.window_engine == "tcgen05" else None)
+                                                None if self.window_engine == "auto" else self.window_engine, meta.columns)
         if self.partitions:
             chunk = max(chunk, -(-positions // self.partitions))
         chunk = -(-chunk // 16) * 16
@@ -156,10 +157,11 @@ class DeviceAttention:
             workspace = self.scratch.take(min(self.partial_bytes, 4 * per * most)).view(torch.float32)
 
         def engine(rows):
-            if self.window_engine == "tcgen05" and kernels.tcgen05_serves(pool.dtype, pool.head_dim, pool.value_dim, q.shape[1],
-                                                                         pool.kv_heads, meta.columns, chunk, rows):
-                return "tcgen05"
-            return None
+            if self.window_engine == "tcgen05":
+                serves = kernels.tcgen05_serves(pool.dtype, pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads,
+                                                meta.columns, chunk, rows)
+                return "tcgen05" if serves else "mma.sync"
+            return None if self.window_engine == "auto" else "mma.sync"
 
         for cut, tokens in launches:
             part = (lambda t: t[cut]) if not cut.start else (lambda t: t[cut].clone())

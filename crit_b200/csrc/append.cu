@@ -72,6 +72,10 @@ __global__ void __launch_bounds__(APPEND_WARPS * 32) append_kernel(const crit_b2
     const int h = is_v ? hh - p.kv_heads : hh;
     const int64_t slot = p.slots[t];
     if (slot < 0) return;
+    if (p.slots_total && slot >= p.slots_total) {         // outside the page tensor: skipped and reported, never written
+        if (lane == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_BOUNDS);
+        return;
+    }
     const int dim = is_v ? p.value_dim : p.head_dim;
     const int per = dim >> 5;
     const TIN* src = is_v ? (const TIN*)p.values + t * p.value_stride_token + (int64_t)h * p.value_stride_head

@@ -2,8 +2,11 @@
 // launches (variant choice, TMA tensor maps).  The decode kernel itself is decode_kernel.cuh.
 // Reference: paged_kv_attention/_kernels.py:558-604 (_merge_kernel), cuda_window.cu:1071-1286 (cw_merge, cw_merge2),
 // :1482-1535 (the C ABI this one mirrors).
+#include <mutex>
+
 #include "decode_kernel.cuh"
 #include "decode_tc.cuh"
+#include "exchange.cuh"
 #include "tensor_map.cuh"
 
 namespace crit_b200 {
@@ -22,10 +25,14 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     if (col >= count) return;
     const int64_t L = p.firsts[r] + count;
     const int nsplit = (int)((L + p.chunk - 1) / p.chunk);
-    if (nsplit <= 1) return;
+    if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS))) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int DV = p.value_dim, per = DV >> 5;
     const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
+    if (nsplit > p.max_splits || prow < 0 || prow >= p.partial_rows) {      // a plan too small for this row: nothing is read
+        if (p.status && threadIdx.x == 0) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
+        return;
+    }
     const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
     const int64_t base = ((int64_t)prow * p.q_heads + head) * p.max_splits;
     const float* pm = p.workspace + states * DV;
@@ -91,8 +98,12 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
     if (col >= count) return;
     const int64_t L = p.firsts[r] + count;
     const int nsplit = (int)((L + p.chunk - 1) / p.chunk);
-    if (nsplit <= 1) return;
+    if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS))) return;
     const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
+    if (nsplit > p.max_splits || prow < 0 || prow >= p.partial_rows) {      // a plan too small for this row: nothing is read
+        if (p.status && lane == 0) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
+        return;
+    }
     const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
     const int64_t base = ((int64_t)prow * p.q_heads + head) * p.max_splits;
     const float* pm = p.workspace + states * DV;
@@ -132,6 +143,91 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
         *reinterpret_cast<uint32_t*>((char*)p.out + (at + i) * 2) = packed;
     }
     if (p.lse && lane == 0) p.lse[(int64_t)token * p.q_heads + head] = total > 0.f ? top * LN2 + logf(total) : -INFINITY;
+}
+
+
+// The fold of a rank's splits, sent: what merge_warp_kernel computes for a (token, head), normalised, goes as FP32 into
+// slot [step & 1][rank] of EVERY rank's exchange buffer (peer stores over NVLink; this rank's own buffer too) instead of
+// into `out`: a message is [tokens x heads][DV] outputs, [tokens x heads] log-sum-exps (natural log), then (rank, step,
+// tokens x heads) as int32 bits.  A column past its row's count, and a row that holds no position, send zeros and -inf.
+// The blocks count themselves on a ticket in this rank's buffer; the last one stores the header, raises this rank's
+// flag in every buffer (system-scope release) and moves the step counter on.  Nothing here waits.
+template <int DV>
+__global__ void __launch_bounds__(128) merge_push_kernel(const crit_b200_attend_params p, const crit_b200_exchange_params x) {
+    constexpr int PER = DV / 32;
+    const int lane = threadIdx.x & 31;
+    const int32_t step = *x.step + 1;
+    const int64_t item = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int64_t items = (int64_t)p.n_rows * p.columns * p.q_heads;
+    const int64_t stride = ex_stride(x.floats);
+    const int64_t n = (x.floats - EX_HEADER) / (DV + 1);           // (token, head) pairs of a message
+    if (item < items) {
+        const int head = (int)(item % p.q_heads);
+        const int rc = (int)(item / p.q_heads);
+        const int r = rc / p.columns, col = rc - r * p.columns;
+        int count = p.counts ? p.counts[r] : p.columns;
+        count = count > p.columns ? p.columns : count;
+        const int64_t L = p.firsts[r] + (count > 0 ? count : 0);
+        const int nsplit = count > 0 ? (int)((L + p.chunk - 1) / p.chunk) : 0;
+        const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
+        const int64_t entry = (int64_t)(p.starts[r] + col) * p.q_heads + head;
+        float total = 0.f, top = -INFINITY, acc[PER];
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+        bool fits = entry >= 0 && entry < n;
+        if (col < count && nsplit > 0 && fits) {
+            fits = nsplit <= p.max_splits && prow >= 0 && prow < p.partial_rows;
+            if (fits) {
+                const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
+                const int64_t base = ((int64_t)prow * p.q_heads + head) * p.max_splits;
+                const float* pm = p.workspace + states * DV;
+                const float* pl = p.workspace + states * (DV + 1);
+                for (int s = lane; s < nsplit; s += 32) top = fmaxf(top, pm[base + s]);
+                top = warp_max(top);
+                const float sub = top == -INFINITY ? 0.f : top;
+#pragma unroll 4
+                for (int s = 0; s < nsplit; ++s) {
+                    const float w = ex2(pm[base + s] - sub);
+                    total += pl[base + s] * w;
+                    const float* o = p.workspace + (base + s) * DV + lane * PER;
+#pragma unroll
+                    for (int i = 0; i < PER; i += 2) {
+                        const float2 v = *reinterpret_cast<const float2*>(o + i);
+                        acc[i] += v.x * w, acc[i + 1] += v.y * w;
+                    }
+                }
+            }
+        }
+        if (!fits && lane == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
+        if (entry >= 0 && entry < n) {
+            const float inv = total > 0.f ? 1.f / total : 0.f;
+            const float lse = total > 0.f ? top * LN2 + logf(total) : -INFINITY;
+            for (int peer = 0; peer < x.world; ++peer) {
+                float* slot = ex_slot(x.peers[peer], step, x.world, x.rank, stride);
+                float* dst = slot + entry * DV + lane * PER;
+#pragma unroll
+                for (int i = 0; i < PER; i += 2) *reinterpret_cast<float2*>(dst + i) = make_float2(acc[i] * inv, acc[i + 1] * inv);
+                if (lane == 0) slot[n * DV + entry] = lse;
+            }
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int32_t* mine = reinterpret_cast<int32_t*>(x.peers[x.rank]);
+        const int done = atomicAdd(mine + EX_TICKET, 1);
+        if (done == (int)gridDim.x - 1) {
+            mine[EX_TICKET] = 0;
+            __threadfence_system();
+            for (int peer = 0; peer < x.world; ++peer) {
+                float* header = ex_slot(x.peers[peer], step, x.world, x.rank, stride) + n * (DV + 1);
+                header[0] = __int_as_float(x.rank), header[1] = __int_as_float(step), header[2] = __int_as_float((int)n);
+            }
+            __threadfence_system();
+            for (int peer = 0; peer < x.world; ++peer) st_release_sys(reinterpret_cast<int32_t*>(x.peers[peer]) + x.rank, step);
+            *x.step = step;
+        }
+    }
 }
 
 // -- host side --------------------------------------------------------------------------------------------------------
@@ -237,8 +333,10 @@ static int resident_blocks(const void* fn, int smem) {
     struct Entry { const void* fn; int smem, device, blocks; };
     static Entry seen[256];
     static int n = 0;
+    static std::mutex guard;            // calls may come from several host threads (one per device or engine)
     int device = 0;
     if (cudaGetDevice(&device) != cudaSuccess) return 0;
+    std::lock_guard<std::mutex> lock(guard);
     for (int i = 0; i < n; ++i)
         if (seen[i].fn == fn && seen[i].smem == smem && seen[i].device == device) return seen[i].blocks;
     int sms = 0, per_sm = 0;
@@ -265,9 +363,15 @@ static int check(const crit_b200_attend_params& p) {
     if (!aligned(p.q, 16) || p.q_stride_token % 8 || p.q_stride_head % 8 || !aligned(p.key_pages, 16) ||
         !aligned(p.value_pages, 16) || !aligned(p.out, 8) || p.out_stride_token % 4 || p.out_stride_head % 4)
         return CRIT_B200_EALIGN;
-    if (p.max_splits > 1) {
-        const int64_t need = (int64_t)p.partial_rows * p.q_heads * p.max_splits * (p.value_dim + 2);
-        if (!p.workspace || p.workspace_floats < need || p.partial_rows < 1) return CRIT_B200_EWORKSPACE;
+    if (p.head_dim < 1 || p.value_dim < 1 || p.head_dim > 1024 || p.value_dim > 1024) return CRIT_B200_EUNSUPPORTED;
+    if (p.max_splits > 1 || (p.flags & CRIT_B200_ATTEND_PARTIALS)) {
+        // partial_rows <= 2^31, q_heads and max_splits below 2^31, value_dim + 2 <= 1026: compared by division, so that no
+        // product of the four can wrap
+        if (p.partial_rows < 1 || (!p.offsets && (int64_t)p.partial_rows < (int64_t)p.n_rows * p.columns)) return CRIT_B200_EINVAL;
+        if (!p.workspace || p.workspace_floats < 1) return CRIT_B200_EWORKSPACE;
+        const int64_t per_row = (int64_t)p.q_heads * (p.value_dim + 2);              // < 2^31 * 1026
+        if (per_row > p.workspace_floats / p.max_splits) return CRIT_B200_EWORKSPACE;
+        if ((int64_t)p.partial_rows > p.workspace_floats / (per_row * p.max_splits)) return CRIT_B200_EWORKSPACE;
         if (!aligned(p.workspace, 16)) return CRIT_B200_EALIGN;
     }
     return 0;
@@ -313,12 +417,14 @@ static int launch_decode_tc(const crit_b200_attend_params& p, cudaStream_t s) {
 
 static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     if (p.flags & CRIT_B200_ATTEND_TCGEN05) return tc_serves(p) ? launch_decode_tc(p, s) : CRIT_B200_EUNSUPPORTED;
+    // The library's choice: windows of several columns over E4M3 pages go to the tcgen05 kernel where it serves them
+    // (the page bytes feed the tensor cores as they are; the m16n8k16 kernel converts every byte in registers and holds
+    // 32 query rows of accumulators a warp, which makes it issue-bound there), everything else, single-column decode
+    // rows above all, to the m16n8k16 kernel.  A column's bits then depend on whether it is read alone or in a window;
+    // CRIT_B200_ATTEND_MMA_SYNC keeps every launch on the m16n8k16 kernel, whose bits do not.
+    if (!(p.flags & CRIT_B200_ATTEND_MMA_SYNC) && p.columns > 1 && tc_serves(p)) return launch_decode_tc(p, s);
     const int G = p.q_heads / p.kv_heads;
     const int rows = p.columns * G;
-    // The m16n8k16 kernel is the default for every launch: its bits do not depend on how many columns a launch has (a
-    // draft verified in a window gets the bits a decode step gives it), which the tcgen05 kernel's column ownership
-    // does not keep.  The tcgen05 kernel is the caller's choice (CRIT_B200_ATTEND_TCGEN05): on the speculative-verify
-    // workload it measured 250 us against 460-500 us, on decode rows of 8 heads 120 us against 112 us.
     const int nt = row_tiles(rows, p.value_dim);
     const int pk = page_class(p.kind, p.page_dtype);
     CUtensorMap kmap, vmap;
@@ -353,7 +459,7 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
 }
 
 static int launch_merge(const crit_b200_attend_params& p, cudaStream_t s) {
-    if (p.max_splits <= 1) return 0;
+    if (p.max_splits <= 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS)) return 0;
     if (p.value_dim > 256 || p.value_dim % 32) return CRIT_B200_EUNSUPPORTED;
     if (p.max_splits <= 32) {
         const int64_t items = (int64_t)p.n_rows * p.columns * p.q_heads;
@@ -379,10 +485,12 @@ static __device__ __align__(256) float static_scratch[CRIT_B200_STATIC_SCRATCH_F
 static int static_scratch_address(float** out) {
     constexpr int MOST = 64;
     static float* found[MOST];
+    static std::mutex guard;
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return (int)e;
     if (device < 0 || device >= MOST) return CRIT_B200_EUNSUPPORTED;
+    std::lock_guard<std::mutex> lock(guard);
     if (!found[device]) {
         void* address = nullptr;
         e = cudaGetSymbolAddress(&address, static_scratch);
@@ -400,17 +508,43 @@ using namespace crit_b200;
 extern "C" __attribute__((visibility("default"))) int crit_b200_attend_static(const crit_b200_attend_params* params, void* stream) {
     if (!params) return CRIT_B200_EINVAL;
     crit_b200_attend_params p = *params;
-    const int64_t need = p.max_splits > 1 ? (int64_t)p.partial_rows * p.q_heads * p.max_splits * (p.value_dim + 2) : 0;
-    if (need > CRIT_B200_STATIC_SCRATCH_FLOATS) return CRIT_B200_ESTATIC;
     float* scratch = nullptr;
     int e = static_scratch_address(&scratch);
     if (e) return e;
     p.workspace = scratch;
     p.workspace_floats = CRIT_B200_STATIC_SCRATCH_FLOATS;
+    // check() validates every field first and compares the partials with the scratch by division (no product of the
+    // caller's integers is formed): a launch that does not fit is refused with the entry point's own code
     e = check(p);
+    if (e == CRIT_B200_EWORKSPACE) return CRIT_B200_ESTATIC;
     if (e) return e;
     e = launch_decode(p, (cudaStream_t)stream);
     return e ? e : launch_merge(p, (cudaStream_t)stream);
+}
+
+namespace crit_b200 {
+int check_exchange(const crit_b200_exchange_params& p, bool with_message);      // exchange.cu
+}
+
+extern "C" __attribute__((visibility("default"))) int crit_b200_merge_push(const crit_b200_attend_params* attend,
+                                                                           const crit_b200_exchange_params* exchange, void* stream) {
+    if (!attend || !exchange) return CRIT_B200_EINVAL;
+    const crit_b200_attend_params p = *attend;
+    const crit_b200_exchange_params x = *exchange;
+    if (!(p.flags & CRIT_B200_ATTEND_PARTIALS)) return CRIT_B200_EINVAL;
+    int e = check(p);
+    if (!e) e = check_exchange(x, false);
+    if (e) return e;
+    if (x.floats < EX_HEADER + p.value_dim + 1 || (x.floats - EX_HEADER) % (p.value_dim + 1)) return CRIT_B200_EINVAL;
+    const int64_t items = (int64_t)p.n_rows * p.columns * p.q_heads;
+    const unsigned blocks = (unsigned)((items + 3) / 4);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (p.value_dim == 128) merge_push_kernel<128><<<blocks, 128, 0, s>>>(p, x);
+    else if (p.value_dim == 256) merge_push_kernel<256><<<blocks, 128, 0, s>>>(p, x);
+    else if (p.value_dim == 64) merge_push_kernel<64><<<blocks, 128, 0, s>>>(p, x);
+    else return CRIT_B200_EUNSUPPORTED;
+    CRIT_CHECK_LAUNCH();
+    return 0;
 }
 
 extern "C" __attribute__((visibility("default"))) int crit_b200_attend_plan(int32_t q_heads, int32_t kv_heads, int32_t head_dim,

@@ -284,6 +284,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     const int64_t krow_stride = (int64_t)p.kv_heads * C::KROW, vrow_stride = (int64_t)p.kv_heads * C::VROW;
     const uint32_t scale_bytes = smode == 2 ? (uint32_t)p.kv_heads * 4u : (smode == 1 ? (uint32_t)p.kv_heads * 64u : 0u);
     const uint32_t tiles_per_page = (uint32_t)p.page >> 4;
+    const uint32_t pages_total = p.slots > 0 ? (uint32_t)(p.slots / p.page) : 0u;      // 0: the tensor's size is not known
     const int Lr = (int)L;
 
     auto issue = [&](int i) {
@@ -291,7 +292,11 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
             const uint32_t tile = (uint32_t)(tile0 + warp + i * DECODE_WARPS);
             const uint32_t pidx = tile / tiles_per_page;
             const int off = (int)(tile - pidx * tiles_per_page) << 4;
-            const int pg = table[pidx];
+            int pg = table[pidx];
+            if (pages_total && (uint32_t)pg >= pages_total) {     // a page id outside the page tensor: the last page is read
+                pg = (int)pages_total - 1;                        // instead and the launch reports it
+                if (lane == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_BOUNDS);
+            }
             const int64_t slot0 = (int64_t)pg * p.page + off;
             const int stage = (tbase + i) % C::STAGES;
             const uint32_t ks = smem_addr(tiles + stage * C::TILES), vs = ks + C::KTILE;
@@ -555,7 +560,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
         if (__any_sync(0xffffffffu, dead)) {
             // Give every copy this warp still has in flight a last bounded chance to land before the block leaves.
             for (int s = 0; s < C::STAGES; ++s) mbar_wait(bars + s * 8, 0, 1000000ull);
-            if (lane == 0 && p.status) atomicExch(p.status, 1);
+            if (lane == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_TMA);
             dead = true;
         }
     } else {
@@ -598,8 +603,13 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     __syncthreads();
 
     const float vmul = (PK == 2 && smode == 0) ? p.value_multiplier : 1.f;
-    const bool whole = nsplit == 1;
+    const bool whole = nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS);
     const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
+    const int prow0 = p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns;
+    // a plan too small for this unit (more splits or partial rows than the workspace was sized for): the unit's state
+    // is dropped and the status word says so, rather than written past the partials
+    const bool fits = whole || (p.workspace && split < p.max_splits && prow0 >= 0 && prow0 + count <= p.partial_rows);
+    if (!fits && tid == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
     for (int idx = tid; idx < ROWS * (DV / 4); idx += DECODE_THREADS) {
         const int rr = idx / (DV / 4), c4 = idx - rr * (DV / 4);
         const int flat = ct * ROWS + rr;
@@ -631,8 +641,8 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
             }
             *reinterpret_cast<uint2*>(dst) = packed;
             if (p.lse && c4 == 0) p.lse[(int64_t)token * p.q_heads + head] = l > 0.f ? top * LN2 + logf(l) : -INFINITY;
-        } else {
-            const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
+        } else if (fits) {
+            const int prow = prow0 + col;
             const int64_t at = ((int64_t)prow * p.q_heads + head) * p.max_splits + split;
             *reinterpret_cast<float4*>(p.workspace + at * DV + c4 * 4) = o;
             if (c4 == 0) {

@@ -318,6 +318,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
     rows.first = m_first;
     rows.units = unit_first[p.n_rows];
     const uint32_t tpp = (uint32_t)p.page >> 4;
+    const uint32_t pages_total = (uint32_t)(p.slots / p.page);
     int where = 0;              // which role's wait gave up
 
     if (warp == 4) {
@@ -338,7 +339,13 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
 #pragma unroll
             for (int j = 0; j < DT_NB; ++j) {
                 const int64_t pos0 = w.u.begin + (int64_t)(lane + 32 * j) * 16;
-                if (pos0 < end) pg[j] = w.u.table[(uint32_t)(pos0 >> 4) / tpp];
+                if (pos0 < end) {
+                    pg[j] = w.u.table[(uint32_t)(pos0 >> 4) / tpp];
+                    if ((uint32_t)pg[j] >= pages_total) {       // outside the page tensor: read as past the end (zeros), reported
+                        pg[j] = -1;
+                        if (p.status) atomicExch(p.status, CRIT_B200_STATUS_BOUNDS);
+                    }
+                }
             }
         };
         auto fetch_scales = [&](const DtWalk& w, const int (&pg)[DT_NB], float (&ks)[DT_NB], float (&vs)[DT_NB]) {
@@ -768,7 +775,10 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 if (!second) fm[entry] = m_run, fl[entry] = l_row;
             }
             DT_PHASE(8)
-            const bool whole = w.u.nsplit == 1;
+            const bool whole = w.u.nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS);
+            const int prow_first = p.offsets ? p.offsets[w.u.r] - p.offsets[0] : w.u.r * p.columns;
+            const bool fits = whole || (p.workspace && w.u.split < p.max_splits && prow_first >= 0 && prow_first + w.u.count <= p.partial_rows);
+            if (!fits && tid == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
 #pragma unroll
             for (int pass = 0; pass < 2; ++pass) {          // value columns 0..63, then 64..127
                 if ((int)second == pass) {
@@ -815,8 +825,8 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                             }
                             *reinterpret_cast<uint2*>(dst) = packed;
                             if (p.lse && dv == 0) p.lse[(int64_t)token * p.q_heads + head] = l > 0.f ? top * LN2 + logf(l) : -INFINITY;
-                        } else {
-                            const int prow_ws = (p.offsets ? p.offsets[w.u.r] - p.offsets[0] : w.u.r * p.columns) + colx;
+                        } else if (fits) {
+                            const int prow_ws = prow_first + colx;
                             const int64_t at = ((int64_t)prow_ws * p.q_heads + head) * p.max_splits + w.u.split;
                             *reinterpret_cast<float4*>(p.workspace + at * DT_D + dv) = o;
                             if (dv == 0) {

@@ -1,48 +1,41 @@
 // The exchange of the shards' partials over NVLink peer memory, without a collective library on the path.
 //
 // Every rank owns one exchange buffer that every other rank of the node has mapped (symmetric memory: the caller makes
-// and maps the buffers and passes this GPU's view of all of them).  Layout of a buffer, in 4-byte words:
-//   [0, 64)                              flags: flag[r] = the last step whose message from rank r has landed here
-//   [64, 64 + 2 * world * stride)        messages: slot [step & 1][r] of `stride` floats (the message padded to 16 bytes)
-// A step is two launches on every rank, in stream order:
+// and maps the buffers and passes this GPU's view of all of them); exchange.cuh has its layout.  A step is two launches
+// on every rank, in stream order:
 //   push   one more on this rank's step counter (a device word: the step is captured in a CUDA graph), then this rank's
 //          message is STORED into slot [step & 1][rank] of every rank's buffer (plain peer stores: posted writes over
 //          NVLink, 16 bytes a thread), a system-scope fence, and flag[rank] = step in every buffer;
-//   wait   waits (bounded in time) until all `world` flags of this rank's OWN buffer are at the step, then copies the
-//          `world` messages of slot [step & 1] into a fixed local array for the merge-of-shards kernel.
-// A push never waits, so no rank's progress depends on another rank's kernel having started; a wait that runs out sets the
-// status word and copies nothing (the host reads the status and does not publish).  Slot [step & 1] of rank y is written
-// again at step + 2, which rank x starts only after its own wait of step + 1, which needed y's push of step + 1, which y
-// launched after its wait of `step` had read the slot: no message is overwritten before it was read.
+//   wait   waits (bounded in time) until all `world` flags of this rank's OWN buffer are at the step, then reads the
+//          `world` messages of slot [step & 1].
+// Two forms of each.  The plain pair moves a message the caller packed (crit_b200_shard_push) and copies the messages
+// to a fixed local array for a later merge (crit_b200_shard_wait).  The fused pair does the arithmetic either side of
+// the wire in the same launches: crit_b200_merge_push (decode.cu) folds this rank's split-K partials and stores each
+// (token, head)'s result straight into the peers' slots, and crit_b200_wait_merge here merges the ranks' partials out
+// of this rank's own buffer into the step's output as soon as the flags are up.
+// A push never waits, so no rank's progress depends on another rank's kernel having started; a wait that runs out sets
+// the status word (0x800 + rank) and writes nothing, and so does a message whose header is not the step's (0x900 + the
+// sender): the host reads the status and does not publish.  After either, the exchange is out of step: the buffers are
+// zeroed and the ranks synchronised again before the next step (slot [step & 1] of rank y is written again at step + 2,
+// which rank x starts only after its own wait of step + 1 saw y's push of step + 1, which y launched after its wait of
+// `step` had read the slot; that chain holds only while every wait succeeds).
 // Loads never touch a peer's memory here: a rank reads only what the others stored into its own buffer.
 // Reference: the reference states the technique on the host only (inference/partitioned-attention/README.md, "all-gather
 // normalizers"); its merge is inference/partitioned-attention/plugin.py:52-64.
-#include "common.cuh"
+#include "exchange.cuh"
 
 namespace crit_b200 {
-
-constexpr int EX_FLAG_WORDS = 64;
-
-__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
-    int32_t v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 
 __global__ void __launch_bounds__(1024) shard_push_kernel(const crit_b200_exchange_params p) {
     __shared__ int32_t step_now;
     if (threadIdx.x == 0) step_now = ++*p.step;
     __syncthreads();
     const int32_t step = step_now;
-    const int64_t stride = (p.floats + 3) / 4 * 4;
+    const int64_t stride = ex_stride(p.floats);
     const int64_t vec = stride / 4;
     const float4* src = reinterpret_cast<const float4*>(p.mine);
     for (int r = 0; r < p.world; ++r) {
-        float* base = reinterpret_cast<float*>(p.peers[r]) + EX_FLAG_WORDS + ((int64_t)(step & 1) * p.world + p.rank) * stride;
-        float4* dst = reinterpret_cast<float4*>(base);
+        float4* dst = reinterpret_cast<float4*>(ex_slot(p.peers[r], step, p.world, p.rank, stride));
         for (int64_t i = threadIdx.x; i < vec; i += blockDim.x) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (4 * i + 3 < p.floats) {
@@ -61,29 +54,78 @@ __global__ void __launch_bounds__(1024) shard_push_kernel(const crit_b200_exchan
     if (threadIdx.x < p.world) st_release_sys(reinterpret_cast<int32_t*>(p.peers[threadIdx.x]) + p.rank, step);
 }
 
-__global__ void __launch_bounds__(256) shard_wait_kernel(const crit_b200_exchange_params p) {
+// One block: its first thread waits, then every thread copies.  (Several blocks, each with its own wait, could disagree
+// near the limit and leave `gathered` half written beside the status word.)
+__global__ void __launch_bounds__(1024) shard_wait_kernel(const crit_b200_exchange_params p) {
     __shared__ int landed;
     const int32_t step = *p.step;
-    const int32_t* flags = reinterpret_cast<const int32_t*>(p.peers[p.rank]);
     if (threadIdx.x == 0) {
-        const uint64_t t0 = global_ns();
-        int ok = 0;
-        do {
-            ok = 1;
-            for (int r = 0; r < p.world; ++r)
-                if (ld_acquire_sys(flags + r) - step < 0) ok = 0;
-        } while (!ok && global_ns() - t0 < (uint64_t)p.wait_ns);
-        landed = ok;
-        if (!ok && p.status) atomicExch(p.status, 0x800 + p.rank);
+        landed = ex_wait_flags(reinterpret_cast<const int32_t*>(p.peers[p.rank]), p.world, step, (uint64_t)p.wait_ns) ? 1 : 0;
+        if (!landed && p.status) atomicExch(p.status, 0x800 + p.rank);
     }
     __syncthreads();
     if (!landed) return;
-    const int64_t stride = (p.floats + 3) / 4 * 4;
-    const float* slot = reinterpret_cast<const float*>(p.peers[p.rank]) + EX_FLAG_WORDS + (int64_t)(step & 1) * p.world * stride;
+    const int64_t stride = ex_stride(p.floats);
+    const float* slot = ex_slot(p.peers[p.rank], step, p.world, 0, stride);
     const int64_t total = (int64_t)p.world * p.floats;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    for (int64_t i = threadIdx.x; i < total; i += blockDim.x) {
         const int64_t r = i / p.floats, at = i - r * p.floats;
         p.gathered[i] = slot[r * stride + at];
+    }
+}
+
+// The merge of the ranks' partials, read where the peers stored them.  A message is [n][dim] outputs, [n] log-sum-exps,
+// then (rank, step, n) as the bits of three int32.  One block: thread 0 waits for the flags and checks the headers; then thread t takes
+// 4-float pieces t, t + 1024, ... of the n x dim outputs: top = max lse over the ranks, w = exp(lse - top) (0 for -inf),
+// out = sum w o / sum w in rank order, lse = top + log(sum w); a (token, head) no rank saw gets zeros and -inf.
+// Reference: inference/partitioned-attention/plugin.py:52-64.
+template <typename TOUT>
+__global__ void __launch_bounds__(1024) wait_merge_kernel(const crit_b200_exchange_params p, const crit_b200_merge_shards_params m) {
+    __shared__ int landed;
+    const int32_t step = *p.step;
+    const int64_t stride = ex_stride(p.floats);
+    const float* slot = ex_slot(p.peers[p.rank], step, p.world, 0, stride);
+    const int64_t n = m.n;
+    const int dim = m.dim;
+    if (threadIdx.x == 0) {
+        int ok = ex_wait_flags(reinterpret_cast<const int32_t*>(p.peers[p.rank]), p.world, step, (uint64_t)p.wait_ns) ? 1 : 0;
+        if (!ok) {
+            if (p.status) atomicExch(p.status, 0x800 + p.rank);
+        } else {
+            for (int r = 0; r < p.world && ok; ++r) {
+                const float* header = slot + r * stride + n * (dim + 1);
+                if (__float_as_int(header[0]) != r || __float_as_int(header[1]) != step || __float_as_int(header[2]) != (int)n) {
+                    if (p.status) atomicExch(p.status, 0x900 + r);
+                    ok = 0;
+                }
+            }
+        }
+        landed = ok;
+    }
+    __syncthreads();
+    if (!landed) return;
+    const int quads = dim >> 2;
+    for (int64_t idx = threadIdx.x; idx < n * quads; idx += blockDim.x) {
+        const int64_t i = idx / quads;
+        const int c4 = (int)(idx - i * quads);
+        float top = -INFINITY;
+        for (int r = 0; r < p.world; ++r) top = fmaxf(top, slot[r * stride + n * dim + i]);
+        const float sub = top == -INFINITY ? 0.f : top;
+        float total = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < p.world; ++r) {
+            const float l = slot[r * stride + n * dim + i];
+            const float w = l == -INFINITY ? 0.f : expf(l - sub);
+            total += w;
+            const float4 v = *reinterpret_cast<const float4*>(slot + r * stride + i * dim + c4 * 4);
+            acc.x += w * v.x, acc.y += w * v.y, acc.z += w * v.z, acc.w += w * v.w;
+        }
+        const float denom = fmaxf(total, 1e-30f);
+        const float inv = total > 0.f ? 1.f / denom : 0.f;
+        TOUT* dst = (TOUT*)m.out + i * dim + c4 * 4;
+        dst[0] = from_float<TOUT>(acc.x * inv), dst[1] = from_float<TOUT>(acc.y * inv);
+        dst[2] = from_float<TOUT>(acc.z * inv), dst[3] = from_float<TOUT>(acc.w * inv);
+        if (c4 == 0 && m.lse) m.lse[i] = total > 0.f ? sub + logf(denom) : -INFINITY;
     }
 }
 
@@ -91,17 +133,20 @@ __global__ void __launch_bounds__(256) shard_wait_kernel(const crit_b200_exchang
 
 using namespace crit_b200;
 
-static int check_exchange(const crit_b200_exchange_params& p) {
-    if (!p.mine || !p.peers || !p.step || !p.gathered) return CRIT_B200_EINVAL;
-    if (p.floats < 1 || p.world < 1 || p.world > 32 || p.rank < 0 || p.rank >= p.world || p.wait_ns < 1) return CRIT_B200_EINVAL;
-    if (!aligned(p.mine, 16)) return CRIT_B200_EALIGN;
+namespace crit_b200 {
+int check_exchange(const crit_b200_exchange_params& p, bool with_message) {
+    if (!p.peers || !p.step) return CRIT_B200_EINVAL;
+    if (with_message && (!p.mine || !p.gathered)) return CRIT_B200_EINVAL;
+    if (p.floats < 1 || p.world < 1 || p.world > EX_MAX_WORLD || p.rank < 0 || p.rank >= p.world || p.wait_ns < 1) return CRIT_B200_EINVAL;
+    if (with_message && !aligned(p.mine, 16)) return CRIT_B200_EALIGN;
     return 0;
 }
+}  // namespace crit_b200
 
 extern "C" __attribute__((visibility("default"))) int crit_b200_shard_push(const crit_b200_exchange_params* params, void* stream) {
     if (!params) return CRIT_B200_EINVAL;
     const crit_b200_exchange_params p = *params;
-    if (int e = check_exchange(p)) return e;
+    if (int e = check_exchange(p, true)) return e;
     shard_push_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(p);
     CRIT_CHECK_LAUNCH();
     return 0;
@@ -110,15 +155,32 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_shard_push(const
 extern "C" __attribute__((visibility("default"))) int crit_b200_shard_wait(const crit_b200_exchange_params* params, void* stream) {
     if (!params) return CRIT_B200_EINVAL;
     const crit_b200_exchange_params p = *params;
-    if (int e = check_exchange(p)) return e;
-    const int64_t total = (int64_t)p.world * p.floats;
-    const unsigned blocks = (unsigned)((total + 255) / 256 < 64 ? (total + 255) / 256 : 64);
-    shard_wait_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(p);
+    if (int e = check_exchange(p, true)) return e;
+    shard_wait_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(p);
+    CRIT_CHECK_LAUNCH();
+    return 0;
+}
+
+extern "C" __attribute__((visibility("default"))) int crit_b200_wait_merge(const crit_b200_exchange_params* exchange,
+                                                                           const crit_b200_merge_shards_params* merge, void* stream) {
+    if (!exchange || !merge) return CRIT_B200_EINVAL;
+    const crit_b200_exchange_params p = *exchange;
+    const crit_b200_merge_shards_params m = *merge;
+    if (int e = check_exchange(p, false)) return e;
+    if (m.n < 1 || m.dim < 4 || m.dim % 4 || !m.out || m.parts != p.world) return CRIT_B200_EINVAL;
+    if (p.floats != m.n * (m.dim + 1) + EX_HEADER) return CRIT_B200_EINVAL;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (m.out_dtype) {
+        case CRIT_B200_DTYPE_BF16: wait_merge_kernel<__nv_bfloat16><<<1, 1024, 0, s>>>(p, m); break;
+        case CRIT_B200_DTYPE_FP16: wait_merge_kernel<__half><<<1, 1024, 0, s>>>(p, m); break;
+        case CRIT_B200_DTYPE_FP32: wait_merge_kernel<float><<<1, 1024, 0, s>>>(p, m); break;
+        default: return CRIT_B200_EINVAL;
+    }
     CRIT_CHECK_LAUNCH();
     return 0;
 }
 
 extern "C" __attribute__((visibility("default"))) int64_t crit_b200_exchange_bytes(int32_t world, int64_t floats) {
     if (world < 1 || floats < 1) return CRIT_B200_EINVAL;
-    return (EX_FLAG_WORDS + 2 * (int64_t)world * ((floats + 3) / 4 * 4)) * 4;
+    return (EX_FLAG_WORDS + 2 * (int64_t)world * ex_stride(floats)) * 4;
 }

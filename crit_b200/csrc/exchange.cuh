@@ -1,0 +1,42 @@
+// The layout of a rank's exchange buffer and the two memory operations the peer exchange stands on (exchange.cu has the
+// protocol).  In 4-byte words:
+//   [0, 32)                              flags: flag[r] = the last step whose message from rank r has landed here
+//   [32]                                 the ticket the blocks of a multi-block push count themselves on (own buffer only)
+//   [64, 64 + 2 * world * stride)        messages: slot [step & 1][r] of `stride` floats (the message padded to 16 bytes)
+#pragma once
+
+#include "common.cuh"
+
+namespace crit_b200 {
+
+constexpr int EX_FLAG_WORDS = 64;
+constexpr int EX_TICKET = 32;
+constexpr int EX_MAX_WORLD = 32;
+constexpr int EX_HEADER = 3;            // words after a fused message's payload: rank, step, rows (int32 bits)
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__host__ __device__ __forceinline__ int64_t ex_stride(int64_t floats) { return (floats + 3) / 4 * 4; }
+// Slot [step & 1][rank] of the buffer at `buffer`.
+__device__ __forceinline__ float* ex_slot(uint64_t buffer, int32_t step, int world, int rank, int64_t stride) {
+    return reinterpret_cast<float*>(buffer) + EX_FLAG_WORDS + ((int64_t)(step & 1) * world + rank) * stride;
+}
+// Waits (at most wait_ns) until every rank's flag in this rank's own buffer is at `step`; one thread calls it.
+__device__ __forceinline__ bool ex_wait_flags(const int32_t* flags, int world, int32_t step, uint64_t wait_ns) {
+    const uint64_t t0 = global_ns();
+    do {
+        bool ok = true;
+        for (int r = 0; r < world; ++r)
+            if (ld_acquire_sys(flags + r) - step < 0) ok = false;
+        if (ok) return true;
+    } while (global_ns() - t0 < wait_ns);
+    return false;
+}
+
+}  // namespace crit_b200

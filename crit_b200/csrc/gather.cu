@@ -15,11 +15,16 @@ __global__ void __launch_bounds__(128) gather_kernel(const crit_b200_gather_para
     int64_t slot;
     if (p.slots) slot = p.slots[n];
     else slot = (int64_t)p.table[n / p.page] * p.page + n % p.page;
+    TOUT* dst = (TOUT*)p.out + item * p.dim;
+    if (p.slots_total && (slot < 0 || slot >= p.slots_total)) {      // outside the page tensor: zeros, and reported
+        if (lane == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_BOUNDS);
+        for (int i = lane; i < p.dim; i += 32) dst[i] = from_float<TOUT>(0.f);
+        return;
+    }
     const int64_t row = slot * p.kv_heads + h;
     float scale = p.multiplier;
     if (p.kind == CRIT_B200_KIND_FP8_ROW || p.kind == CRIT_B200_KIND_INT8) scale = p.scales[row];
     else if (p.kind == CRIT_B200_KIND_FP8_PAGE) scale = p.scales[(slot / p.page) * p.kv_heads + h];
-    TOUT* dst = (TOUT*)p.out + item * p.dim;
     for (int i = lane; i < p.dim; i += 32) {
         float v;
         if (p.kind == CRIT_B200_KIND_16BIT) {

@@ -13,11 +13,12 @@ normalizers, reduce-scatter weighted outputs") and tests it with two pools on on
     and folds its splits locally into one (out, lse) per (token, head); ShardMerge exchanges those (tokens x heads x
     (dim + 1) floats a rank: 24.7 KB at 24 heads x 256) and folds them in rank order with the merge-of-shards kernel,
     identically on every rank.  A rank with no positions contributes zeros and -inf.  The exchange is the library's own
-    by default: every rank STORES its message into every other rank's buffer over NVLink peer memory (symmetric
-    memory mapped once; crit_b200_shard_push / crit_b200_shard_wait: two small launches, flags with system-scope
-    release / acquire, a bounded wait), because the payload is latency, not bandwidth: NCCL's all-gather of it measured
-    about 100 us on 8 GPUs, more than the decode launch it follows.  NCCL's all-gather stays as the fallback (no
-    symmetric memory) and as the baseline.
+    by default, fused with the arithmetic either side of it: the launch that folds a rank's splits STORES each (token,
+    head)'s result straight into every rank's buffer over NVLink peer memory (symmetric memory mapped once;
+    crit_b200_merge_push), and the launch that waits for the ranks' flags (system-scope release / acquire, a bounded
+    wait) merges the shards out of its own buffer (crit_b200_wait_merge): a decode step is decode, merge+push,
+    wait+merge, three launches, because the payload is latency, not bandwidth.  NCCL's all-gather stays as the
+    fallback (no symmetric memory) and as the baseline.
 
 Failure detection without faulting a GPU: every rank's message carries (rank, epoch, rows) in its last three floats;
 with check=True the gathered headers are read on the host and a stale, missing or foreign message raises before the
@@ -47,11 +48,26 @@ def assign_sequences(lengths, world, balance=True):
 
 def kv_ranges(context, world, partition=4096):
     """[(first, end)] positions each rank owns of one context: contiguous runs of whole partitions, ceil(parts / world)
-    a rank; ranks past the context get an empty range."""
+    a rank; ranks past the context get an empty range.  partition: the unit ownership is cut at.  A page (or a few) is
+    the natural unit: every rank then gets work (49 partitions of 4,096 leave the eighth of 8 ranks with none, 3,125
+    pages of 64 give each 388 to 391); the split-K partitions INSIDE a rank's range are the kernels' own matter."""
     parts = -(-context // partition)
     per = -(-parts // world)
     return [(min(min(r * per, parts) * partition, context), min(min((r + 1) * per, parts) * partition, context))
             for r in range(world)]
+
+
+def chunk_to_fill(positions, kv_heads, blocks, chunk=1024, tile=16):
+    """Positions per split for ONE long row of `positions` so that its launch's blocks (splits x kv_heads) fill the
+    device's `blocks` resident blocks in whole waves: the default chunk where the row gives several waves anyway, else
+    the chunk whose splits come to the largest whole number of waves not above what the default gives (at least one).
+    A row's own choice: it changes the split boundaries, so only a caller that always reads the row alone (one long
+    context over a KV range) uses it."""
+    positions, blocks = max(int(positions), 1), max(int(blocks), 1)
+    units = -(-positions // chunk) * kv_heads
+    waves = max(1, round(units / blocks))
+    splits = max(1, waves * blocks // kv_heads)
+    return max(tile, -(-(-(-positions // splits)) // tile) * tile)
 
 
 class PeerExchange:
@@ -109,7 +125,7 @@ class ShardMerge:
         self.all = torch.zeros(self.world, self.size, dtype=torch.float32, device=device)
         self.merge_fn, self.out_dtype = merge, out_dtype
         self.mine[-3], self.mine[-1] = float(self.rank), float(self.rows)
-        self.peer = None
+        self.peer, self.status = None, None
         if exchange not in ("auto", "peer", "nccl"):
             raise ValueError(f"exchange is auto, peer or nccl, not {exchange!r}")
         if self.world > 1 and exchange != "nccl" and torch.device(device).type == "cuda":
@@ -129,8 +145,8 @@ class ShardMerge:
             buffer.zero_()
             handle = symm.rendezvous(buffer, group)
             peers = torch.tensor([int(a) for a in handle.buffer_ptrs], dtype=torch.int64, device=device)
-            found = PeerExchange(peers, self.rank, self.world, self.mine, self.all, wait_ms,
-                                 crit_b200._status_word(torch.device(device)))
+            self.status = crit_b200._status_word(torch.device(device))
+            found = PeerExchange(peers, self.rank, self.world, self.mine, self.all, wait_ms, self.status)
             found._symmetric = (buffer, handle)
         except Exception as problem:       # no symmetric memory here (driver, permissions, an older torch)
             error = problem
@@ -143,6 +159,47 @@ class ShardMerge:
                 raise RuntimeError(f"the peer exchange could not be set up on every rank ({error})")
             return None
         return found
+
+    def attend(self, params, out, lse):
+        """The fused step after a decode launch that left every split state in its workspace (crit_b200.attend with
+        shards=self passes its parameter block here): fold + push, wait + merge of shards into out [tokens][heads][dim]
+        and lse [tokens][heads].  Device work only, capturable.  Without the peer exchange: the fold into out / lse and
+        merge() over NCCL."""
+        import ctypes
+        torch = self.torch
+        from . import _lib
+        lib = _lib.load()
+        stream = ctypes.c_void_p(torch.cuda.current_stream(out.device).cuda_stream)
+        if self.peer is None:
+            _lib.check(lib.crit_b200_merge(ctypes.byref(params), stream), "crit_b200.dist.ShardMerge.attend")
+            merged, merged_lse = self.merge(out, lse)
+            out.copy_(merged)
+            lse.copy_(merged_lse)
+            return out, lse
+        if not out.is_contiguous() or not lse.is_contiguous() or out.numel() != self.rows * self.dim:
+            raise ValueError(f"the merged output is contiguous [{self.tokens}][{self.heads}][{self.dim}]")
+        m = _lib.MergeShardsParams()
+        m.out, m.lse, m.n, m.parts, m.dim = out.data_ptr(), lse.data_ptr(), self.rows, self.world, self.dim
+        m.in_dtype = _lib.DTYPE_FP32
+        m.out_dtype = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16, torch.float32: _lib.DTYPE_FP32}[out.dtype]
+        x = self.peer.params
+        with torch.cuda.device(out.device):
+            _lib.check(lib.crit_b200_merge_push(ctypes.byref(params), ctypes.byref(x), stream), "crit_b200.dist.ShardMerge.attend (push)")
+            _lib.check(lib.crit_b200_wait_merge(ctypes.byref(x), ctypes.byref(m), stream), "crit_b200.dist.ShardMerge.attend (wait)")
+        return out, lse
+
+    def raise_on_status(self):
+        """Reads this device's status word (one wait) and raises when the exchange recorded a wait that ran out
+        (0x800 + rank) or a message of another step or shape (0x900 + sender): the step's output is not published."""
+        if self.status is None:
+            return
+        word = int(self.status.item())
+        if word & 0xf00 in (0x800, 0x900):
+            what = "waited in vain for the other ranks' partials" if word & 0xf00 == 0x800 else \
+                f"got a partial of another step or shape from rank {word & 0xff}"
+            raise RuntimeError(f"rank {self.rank}: the exchange {what} (status {word:#x}): the partial is missing or stale, "
+                               "the merged attention is not published; zero the exchange buffers and synchronise the "
+                               "ranks before the next step")
 
     def merge(self, out, lse, check=False, epoch=None):
         """This rank's (out [tokens][heads][dim], lse [tokens][heads]; lse -inf and out 0 where it saw no key) ->
@@ -174,9 +231,12 @@ class ShardMerge:
         return crit_b200.merge_shards(outs, lses, dtype=self.out_dtype)
 
     def verify(self):
-        """Raise unless every rank's message of this epoch and shape arrived (host read of world x 3 floats)."""
+        """Raise unless every rank's message of this epoch and shape arrived (host read of world x 3 floats and of this
+        rank's own message: the epoch every header must carry is the one this rank SENT, not the one it finds in the
+        gathered copy, which a wait that ran out leaves at the step before)."""
+        self.raise_on_status()
         headers = self.all[:, -HEADER:].cpu().tolist()
-        want = headers[self.rank][1]
+        want = float(self.mine[-2].item())
         for r, (rank, epoch, rows) in enumerate(headers):
             if rank != float(r) or epoch != want or rows != float(self.rows) or not all(map(math.isfinite, (rank, epoch, rows))):
                 raise RuntimeError(f"rank {self.rank}: the partial of rank {r} is missing or stale (header rank {rank}, "

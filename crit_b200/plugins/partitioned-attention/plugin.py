@@ -17,5 +17,5 @@ def create(context, options, parts):
                            device=getattr(context, "device", None), kernels_mib=options.get("workspace_mib", 128),
                            prompt_reader="prefill" if reader == "auto" else reader,
                            scratch=getattr(context, "scratch", None),
-                           window_engine=options.get("window_engine", "mma.sync"))
+                           window_engine=options.get("window_engine", "auto"))
     return PartitionedAttention(parts["kv_cache"], options, form)

@@ -112,7 +112,8 @@ class KVPool:
         self.row_of, self._free_rows = {}, list(range(int(sequences)))
         self.block_tables = torch.full((int(sequences), self.table_pages), self.dump, dtype=torch.int32,
                                        device=self.device)
-        self._updates = []          # (flat index, page id) entries of the block table not yet on the device
+        self._updates = {}          # flat index -> page id: block-table entries not yet on the device (the last write of
+                                    # an entry wins: a scatter with one index twice has no defined order on the device)
         self.device_tables = _Tables(self)
         self.window, self.step_rows, self.step_tokens = int(window), int(step_rows), int(step_tokens)
         self.windows, self.window_tokens = [], 0
@@ -155,7 +156,7 @@ class KVPool:
             self._drop(page)
         self.lengths.pop(sequence, None)
         row = self.row_of.pop(sequence)
-        self._updates += [(row * self.table_pages + p, self.dump) for p in range(len(table))]
+        self._updates.update((row * self.table_pages + p, self.dump) for p in range(len(table)))
         heapq.heappush(self._free_rows, row)
 
     def fork(self, sequence, new):
@@ -193,7 +194,7 @@ class KVPool:
         row = self.row_of[sequence]
         for p in range(needed, len(table)):
             self._drop(table[p])
-            self._updates.append((row * self.table_pages + p, self.dump))
+            self._updates[row * self.table_pages + p] = self.dump
         del table[needed:]
 
     def set_scales(self, layer, key_scale, value_scale):
@@ -504,7 +505,7 @@ class KVPool:
     # -- the block table on the device -----------------------------------------------------------------------------------
     def _note(self, sequence, indices):
         row, table = self.row_of[sequence], self.tables[sequence]
-        self._updates += [(row * self.table_pages + p, table[p]) for p in indices]
+        self._updates.update((row * self.table_pages + p, table[p]) for p in indices)
 
     def _upload(self, values, dtype):
         torch = self.torch
@@ -518,9 +519,9 @@ class KVPool:
         if not self._updates:
             return
         torch = self.torch
-        packed = self._upload([x for pair in self._updates for x in pair], torch.int64).view(-1, 2)
+        packed = self._upload([x for pair in self._updates.items() for x in pair], torch.int64).view(-1, 2)
         self.block_tables.view(-1).index_copy_(0, packed[:, 0], packed[:, 1].to(torch.int32))
-        self._updates = []
+        self._updates = {}
 
     def _more_rows(self):
         torch = self.torch

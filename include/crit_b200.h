@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define CRIT_B200_ABI_VERSION 1
+#define CRIT_B200_ABI_VERSION 2
 
 /* Page kinds (the reference's KINDS, paged_kv_attention/__init__.py:78, plus the per-page FP8 scale). */
 #define CRIT_B200_KIND_16BIT    0   /* bf16 or fp16 pages (page_dtype says which) */
@@ -40,6 +40,15 @@ extern "C" {
 #define CRIT_B200_EALIGN      (-4)  /* a pointer or stride is not aligned as the kernels read it */
 #define CRIT_B200_ESTATIC     (-5)  /* the launch needs more partials than crit_b200_attend_static's built-in scratch holds */
 
+/* What a kernel leaves in a `status` word (it sets, never clears): a launch whose word is not 0 afterwards has skipped
+ * the work concerned and written nothing for it. */
+#define CRIT_B200_STATUS_TMA    1      /* a TMA copy of the m16n8k16 decode kernel never landed (bounded wait) */
+#define CRIT_B200_STATUS_PLAN   2      /* a row took more splits or partial rows than max_splits / partial_rows allow */
+#define CRIT_B200_STATUS_BOUNDS 3      /* a slot or page id lay outside the page tensor (slots_total / slots given) */
+                                       /* 0x110..0x1ff: the tcgen05 prefill kernel's waits; 0x410..0x440: the tcgen05 decode
+                                          kernel's; 0x800 + rank: the peer exchange waited in vain; 0x900 + rank: that
+                                          rank's message carried another step's or shape's header */
+
 /* -- KV append ---------------------------------------------------------------------------------------------------
  * Replaces paged_kv_attention.write (paged_kv_attention/__init__.py:289-324, kernel _kernels.py:112-150) and the torch
  * path of KVPool.write (inference/attention-state/code/pages.py:420-453 with fp8_rows/int8_rows :872-895).
@@ -54,7 +63,10 @@ typedef struct crit_b200_append_params {
     void* value_pages;
     float* key_scales;           /* kinds 2, 3: [slots][kv_heads]; kind 4: [pages][kv_heads]; else NULL */
     float* value_scales;
+    int32_t* status;             /* or NULL: set to CRIT_B200_STATUS_BOUNDS when a slot lay outside [0, slots_total) */
     int64_t tokens;
+    int64_t slots_total;         /* slots each page tensor stores; a slot at or past it is skipped and reported.  0: unknown,
+                                    nothing is checked */
     int64_t key_stride_token, key_stride_head, value_stride_token, value_stride_head;
     int32_t kv_heads, head_dim, value_dim, page;
     int32_t kind, in_dtype, page_dtype;
@@ -73,7 +85,9 @@ typedef struct crit_b200_gather_params {
     const int32_t* table;
     const int64_t* slots;
     void* out;
+    int32_t* status;             /* or NULL: set to CRIT_B200_STATUS_BOUNDS when a slot lay outside [0, slots_total) */
     int64_t count;
+    int64_t slots_total;         /* slots the page tensor stores; a row whose slot is outside reads as zeros.  0: unchecked */
     int32_t kv_heads, dim, page;
     int32_t kind, page_dtype, out_dtype;
     float multiplier;
@@ -109,6 +123,9 @@ int crit_b200_slots(const crit_b200_slots_params* params, void* stream);
                                        probabilities as two E4M3 terms each) or CRIT_B200_EUNSUPPORTED: E4M3 pages of
                                        128-wide heads, columns x group heads <= 32, chunk a multiple of 128, slots set */
 #define CRIT_B200_ATTEND_MMA_SYNC 16 /* the m16n8k16 kernel even where the tcgen05 kernel serves the launch */
+#define CRIT_B200_ATTEND_PARTIALS 32 /* every row's split states go to the workspace, a row of one split too (the first launch
+                                        writes nothing to out / lse): what crit_b200_merge_push sends, or what
+                                        crit_b200_merge folds */
 
 /* -- split-K decode / speculative-verify attention ------------------------------------------------------------------
  * Replaces paged_kv_attention.attend (paged_kv_attention/__init__.py:396-576; kernels _kernels.py:263-478 and :558-604,
@@ -136,7 +153,7 @@ typedef struct crit_b200_attend_params {
     int32_t* status;             /* or NULL: a device word a kernel sets (never clears) when a bounded wait gave up */
     int64_t workspace_floats;
     int64_t slots;               /* slots each page tensor stores ((pages + 1) * page): the bound of the TMA tensor maps;
-                                    0: unknown, pages are staged with cp.async */
+                                    0: unknown, pages are staged with cp.async and page ids are not range-checked */
     int64_t q_stride_token, q_stride_head, out_stride_token, out_stride_head, table_stride;
     int32_t n_rows, columns, partial_rows;
     int32_t q_heads, kv_heads, head_dim, value_dim, page;
@@ -218,6 +235,18 @@ typedef struct crit_b200_exchange_params {
 int crit_b200_shard_push(const crit_b200_exchange_params* params, void* stream);
 int crit_b200_shard_wait(const crit_b200_exchange_params* params, void* stream);
 int64_t crit_b200_exchange_bytes(int32_t world, int64_t floats);
+
+/* The same exchange with the arithmetic either side of it in the same two launches (what one decode step of a context
+ * sharded by KV range runs after crit_b200_decode with CRIT_B200_ATTEND_PARTIALS): crit_b200_merge_push folds this
+ * rank's splits (the fold of crit_b200_merge) and stores each (token, head)'s normalised output and log-sum-exp as FP32
+ * straight into every rank's buffer, then the header and the flag; crit_b200_wait_merge waits (bounded) for the `world`
+ * messages in this rank's own buffer, checks their headers (sender, step, shape) and writes the merge of shards to
+ * merge->out / merge->lse (merge->outs and ->lses are not read; parts = world).  A message is tokens x q_heads x
+ * (value_dim + 1) floats + 3: exchange->floats says so, and the attend rows' tokens cover 0 .. tokens - 1.
+ * exchange->mine and ->gathered are not used.  A wait that runs out (status 0x800 + rank) or a foreign header
+ * (0x900 + sender) writes nothing: the step's output is then not published. */
+int crit_b200_merge_push(const crit_b200_attend_params* attend, const crit_b200_exchange_params* exchange, void* stream);
+int crit_b200_wait_merge(const crit_b200_exchange_params* exchange, const crit_b200_merge_shards_params* merge, void* stream);
 
 /* -- chunked prefill ---------------------------------------------------------------------------------------------
  * Replaces paged_kv_attention.prefill (paged_kv_attention/__init__.py:1245-1332; kernel _kernels.py:610-726) behind

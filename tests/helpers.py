@@ -15,7 +15,10 @@ STORE = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp8": torch.float8_e4m3
 class Cache:
     """Pages of several sequences, each over shuffled pages (the last page index is left unused, as a dump page)."""
 
-    def __init__(self, kind, hkv, d, dv, page, lengths, seed=0, multipliers=(0.02, 0.03), spare=1, outliers=False):
+    def __init__(self, kind, hkv, d, dv, page, lengths, seed=0, multipliers=(0.02, 0.03), spare=1, outliers=False,
+                 poison=False):
+        """poison: every byte of the pages and scales is 0xFF (NaN codes, NaN scales) before the sequences are written,
+        so whatever a kernel reads past a row's last position is a NaN."""
         self.dev = torch.device("cuda")
         g = torch.Generator().manual_seed(seed)
         self.kind, self.hkv, self.d, self.dv, self.page = kind, hkv, d, dv, page
@@ -31,6 +34,10 @@ class Cache:
         elif kind == "fp8:page":
             self.ks = torch.zeros(n_pages, hkv, dtype=torch.float32, device=self.dev)
             self.vs = torch.zeros_like(self.ks)
+        if poison:
+            for t in (self.k, self.v, self.ks, self.vs):
+                if t is not None:
+                    t.view(torch.uint8).fill_(0xFF)
         order = torch.randperm(n_pages - 1, generator=g)
         self.tables = order[:width * len(lengths)].view(len(lengths), width).to(torch.int32).to(self.dev)
         self.lengths = list(lengths)
@@ -96,3 +103,108 @@ def assert_attention_close(out, lse, want, want_lse, rows_tokens, max_abs=2e-2, 
     if lse is not None:
         gl, wl = lse.cpu().numpy()[rows_tokens], want_lse[rows_tokens]
         assert np.abs(gl - wl).max() <= lse_abs, f"lse {np.abs(gl - wl).max():.4g}"
+
+
+def attend_params(cache, q, out, lse, rows, starts, firsts, columns, chunk, workspace=None, counts=None, flags=0,
+                  partial_rows=None, offsets=None, status=None):
+    """The parameter block of include/crit_b200.h for one launch over a Cache, filled as crit_b200.attend fills it: for
+    tests that call the C ABI themselves.  Returns (params, the tensors the block points at: keep them alive)."""
+    from crit_b200 import _lib
+    dev = q.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    held = dict(rows=torch.tensor(rows, **i32), starts=torch.tensor(starts, **i32),
+                firsts=torch.tensor(firsts, dtype=torch.int64, device=dev))
+    T, hq, d = q.shape
+    positions = cache.tables.shape[1] * cache.page
+    p = _lib.AttendParams()
+    p.q, p.out = q.data_ptr(), out.data_ptr()
+    p.lse = lse.data_ptr() if lse is not None else None
+    p.key_pages, p.value_pages = cache.k.data_ptr(), cache.v.data_ptr()
+    if cache.ks is not None:
+        p.key_scales, p.value_scales = cache.ks.data_ptr(), cache.vs.data_ptr()
+    p.tables, p.rows, p.starts, p.firsts = (cache.tables.data_ptr(), held["rows"].data_ptr(), held["starts"].data_ptr(),
+                                            held["firsts"].data_ptr())
+    if counts is not None:
+        held["counts"] = torch.tensor(counts, **i32)
+        p.counts = held["counts"].data_ptr()
+    if offsets is not None:
+        held["offsets"] = torch.tensor(offsets, **i32)
+        p.offsets = held["offsets"].data_ptr()
+    if status is not None:
+        p.status = status.data_ptr()
+    p.q_stride_token, p.q_stride_head = q.stride(0), q.stride(1)
+    p.out_stride_token, p.out_stride_head = out.stride(0), out.stride(1)
+    p.table_stride = cache.tables.stride(0)
+    p.n_rows, p.columns = len(rows), columns
+    p.partial_rows = len(rows) * columns if partial_rows is None else partial_rows
+    p.q_heads, p.kv_heads, p.head_dim, p.value_dim, p.page = hq, cache.hkv, d, cache.dv, cache.page
+    p.kind, p.page_dtype = pk.KINDS[cache.kind], _lib.DTYPE_FP16 if cache.kind == "fp16" else _lib.DTYPE_BF16
+    p.q_dtype = _lib.DTYPE_FP16 if q.dtype == torch.float16 else _lib.DTYPE_BF16
+    p.chunk, p.max_splits = chunk, -(-positions // chunk)
+    p.slots = cache.k.numel() // (cache.hkv * d)
+    p.flags = flags
+    p.scale = d ** -0.5
+    p.key_multiplier, p.value_multiplier = cache.multipliers
+    if workspace is not None:
+        p.workspace, p.workspace_floats = workspace.data_ptr(), workspace.numel()
+    return p, held
+
+
+class Guarded:
+    """A CUDA buffer between two guard regions filled with 0xFF bytes: a kernel that writes outside what it was given
+    leaves a mark that intact() finds."""
+
+    def __init__(self, nbytes, guard=4096, fill=0):
+        self.nbytes, self.guard = int(nbytes), guard
+        padded = -(-self.nbytes // 256) * 256
+        self.raw = torch.full((padded + 2 * guard,), 0xFF, dtype=torch.uint8, device="cuda")
+        self.bytes = self.raw[guard:guard + self.nbytes]
+        self.bytes.fill_(fill)
+
+    def view(self, dtype, *shape):
+        return self.bytes.view(dtype).view(*shape)
+
+    def intact(self):
+        front, back = self.raw[:self.guard], self.raw[self.guard + self.nbytes:]
+        return bool((front == 0xFF).all()) and bool((back == 0xFF).all())
+
+
+class EmulatedRanks:
+    """The peer exchange of `world` ranks on ONE GPU: every rank's exchange buffer lives on this device and the ranks'
+    launches run one after another on one stream (a push never waits, so this order cannot block; a wait runs after the
+    pushes it needs).  What two or more GPUs do with peer stores, minus the wire."""
+
+    def __init__(self, world, tokens, heads, dim, wait_ms=50):
+        import ctypes
+        from crit_b200 import _lib
+        self.ctypes, self.lib, self._lib = ctypes, _lib.load(), _lib
+        self.world, self.n, self.dim = world, tokens * heads, dim
+        self.floats = self.n * (dim + 1) + 3
+        size = self.lib.crit_b200_exchange_bytes(world, self.floats)
+        dev = torch.device("cuda")
+        self.buffers = [torch.zeros(size // 4, dtype=torch.float32, device=dev) for _ in range(world)]
+        self.peers = torch.tensor([b.data_ptr() for b in self.buffers], dtype=torch.int64, device=dev)
+        self.steps = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(world)]
+        self.status = [torch.zeros(1, dtype=torch.int32, device=dev) for _ in range(world)]
+        self.params = []
+        for r in range(world):
+            x = _lib.ExchangeParams()
+            x.peers, x.step, x.status = self.peers.data_ptr(), self.steps[r].data_ptr(), self.status[r].data_ptr()
+            x.floats, x.wait_ns, x.world, x.rank = self.floats, int(wait_ms) * 1000000, world, r
+            self.params.append(x)
+
+    def _stream(self):
+        return self.ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def push(self, rank, attend_params):
+        """Rank `rank` folds the split states its decode launch left and stores the result into every rank's buffer."""
+        code = self.lib.crit_b200_merge_push(self.ctypes.byref(attend_params), self.ctypes.byref(self.params[rank]), self._stream())
+        assert code == 0, self.lib.crit_b200_error(code)
+
+    def wait_merge(self, rank, out, lse):
+        m = self._lib.MergeShardsParams()
+        m.out, m.lse, m.n, m.parts, m.dim = out.data_ptr(), lse.data_ptr(), self.n, self.world, self.dim
+        m.in_dtype = self._lib.DTYPE_FP32
+        m.out_dtype = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out.dtype]
+        code = self.lib.crit_b200_wait_merge(self.ctypes.byref(self.params[rank]), self.ctypes.byref(m), self._stream())
+        assert code == 0, self.lib.crit_b200_error(code)

@@ -1,6 +1,7 @@
 """Two GPUs, one process each: a context sharded by KV range, each rank's split-K decode over its own pages, the
-(out, lse) partials exchanged (NCCL all-gather, and the library's own stores into peer memory) and merged, against the
-CPU oracle over the whole context; the two exchanges give the same bits, step after step and from a CUDA graph.
+(out, lse) partials exchanged (NCCL all-gather; and the library's own exchange, the fold of a rank's splits stored
+straight into every rank's memory and the merge of shards read out of a rank's own) and merged, against the CPU oracle
+over the whole context; the fused exchange gives the same bits step after step and from a CUDA graph.
 Skipped with fewer than two GPUs."""
 import os
 import socket
@@ -43,23 +44,40 @@ def _rank(rank, world, port, queue):
                       torch.tensor([mine - 1], device=dev), 1, page, out=out, lse=lse, chunk=256)
         merger = ShardMerge(1, hq, d, dev, exchange="nccl")
         merged, merged_lse = merger.merge(out, lse, check=True)
-        # the peer-memory exchange: the same bits, over several steps (the slots alternate) and replayed from a graph
+        # the peer-memory exchange, fused with the fold and the merge (decode, fold + push, wait + merge of shards): within
+        # the bounds of the NCCL road (FP32 partials cross the wire here, the output's dtype there), the same bits step
+        # after step (the slots alternate) and replayed from a graph
         peer = ShardMerge(1, hq, d, dev, exchange="auto", wait_ms=500)
         same = peer.peer is not None
         if same:
+            i32 = dict(dtype=torch.int32, device=dev)
+            fused, fused_lse = torch.zeros_like(out), torch.zeros_like(lse)
+            count, zero = torch.tensor([1 if mine else 0], **i32), torch.zeros(1, **i32)
+            last, q_dev = torch.tensor([max(mine - 1, 0)], device=dev), q.to(dev)
+
+            def fused_step():
+                return pk.attend(q_dev, k, v, "bf16", table, zero, zero, last, 1, page, counts=count, out=fused,
+                                 lse=fused_lse, chunk=256, shards=peer)
+            fused_step()
+            first, first_lse = fused.clone(), fused_lse.clone()
+            same = same and bool((first.float() - merged.float()).abs().max() <= 2e-2)
+            same = same and bool((first_lse - merged_lse).abs().max() <= 2e-3)
             for _ in range(3):
-                again, again_lse = peer.merge(out, lse, check=True)
-                same = same and torch.equal(again, merged) and torch.equal(again_lse, merged_lse)
+                fused.zero_()
+                fused_step()
+                same = same and torch.equal(fused, first) and torch.equal(fused_lse, first_lse)
             stream = torch.cuda.Stream(dev)
             with torch.cuda.stream(stream):
                 graph = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(graph, stream=stream):
-                    captured, captured_lse = peer.merge(out, lse)
+                    fused_step()
                 for _ in range(3):
+                    fused.zero_()
                     graph.replay()
                 stream.synchronize()
-            peer.verify()
-            same = same and torch.equal(captured, merged) and torch.equal(captured_lse, merged_lse) and pk.status(dev) == 0
+            peer.raise_on_status()
+            same = same and torch.equal(fused, first) and torch.equal(fused_lse, first_lse) and pk.status(dev) == 0
+            merged, merged_lse = fused, fused_lse
         whole_table = np.arange(-(-n // page), dtype=np.int32)
         kf = np.zeros((len(whole_table) * page, hkv, d), np.float32)
         vf = np.zeros_like(kf)

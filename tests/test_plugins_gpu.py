@@ -12,12 +12,14 @@ import oracle
 pytestmark = pytest.mark.gpu
 
 
-def parts(page=16, **kw):
+def parts(page=16, window_engine="mma.sync", **kw):
+    """The two plugin objects; window_engine "mma.sync" unless a test asks otherwise: the tests of row-exact bits hold
+    that engine to them (the default, "auto", sends verify windows over E4M3 pages to the tcgen05 kernel)."""
     from crit_b200.attention import DeviceAttention, PartitionedAttention
     from crit_b200.kv_state import KVStateCache
     import crit_b200
     kv = KVStateCache(page=page, kernels=crit_b200, **kw)
-    return kv, PartitionedAttention(kv, {"world": 2, "page_size": 256}, DeviceAttention(device="cuda"))
+    return kv, PartitionedAttention(kv, {"world": 2, "page_size": 256}, DeviceAttention(device="cuda", window_engine=window_engine))
 
 
 def rows_of(n, hkv, d, seed):
@@ -112,6 +114,41 @@ def test_keep_rolls_a_verify_window_back_and_a_fork_copies_on_write():
     assert pool.free_pages() == 16
 
 
+def test_the_device_block_table_follows_the_host_when_one_flush_holds_an_entry_twice():
+    """An entry of the block table can be queued twice before one upload: a closed sequence's row taken by the next
+    open(), a page rolled back by keep() and grown again, the shared and then the copied tail of a bound sequence's
+    fork.  The device table must end with the last value of each (a scatter with one index twice has no order)."""
+    kv, _ = parts(round_rows=4)
+    pool = kv.pool([0], 2, 64, 16 * 32, "cuda", "bf16")
+
+    def mirrors():
+        pool._flush()
+        torch.cuda.synchronize()
+        for s, table in pool.tables.items():
+            row = pool.block_tables[pool.row_of[s]].tolist()
+            assert row[:len(table)] == table and set(row[len(table):]) <= {pool.dump}, s
+    for turn in range(20):                      # many turns: a lost race shows up in some of them
+        pool.open("a")
+        step(pool, [("a", 0, 40)])
+        pool.keep("a", 40)
+        pool.close("a")
+        pool.open("b")                          # takes a's row; its reserve flushes a's entries and its own together
+        step(pool, [("b", 0, 20)])
+        mirrors()
+        pool.keep("b", 10)                      # page 1 back to the pool ...
+        step(pool, [("b", 10, 10)])             # ... and grown again before any flush
+        mirrors()
+        pool.keep("b", 20)
+        pool.bind(0, "b", 64)
+        pool.fork("b", "c")                     # the tail page: shared, then copied, in one flush
+        mirrors()
+        assert pool.table("b")[1] != pool.table("c")[1]
+        pool.unbind(0)
+        pool.close("b")
+        pool.close("c")
+        assert pool.free_pages() == 32
+
+
 @pytest.mark.parametrize("dtype", ["bf16", "fp8:page"])
 def test_a_decode_step_and_a_verify_window_match_the_oracle(dtype):
     from crit_b200.batch import StepBatch
@@ -146,6 +183,7 @@ def test_verify_windows_through_the_tcgen05_engine_match_the_oracle():
     kv, plain = parts()
     fast = PartitionedAttention(kv, {"world": 2, "page_size": 256}, DeviceAttention(device="cuda", window_engine="tcgen05"))
     assert fast.exactness()["decode"] == "repeatable" and plain.exactness()["decode"] == "row-exact"
+    assert DeviceAttention(device="cuda").exactness()["decode"] == "repeatable"        # the default, "auto"
     pool = kv.pool([0], 4, 128, 16 * 400, "cuda", "fp8:page")
     for s, n in {"a": 700, "b": 64, "d": 2100}.items():
         pool.open(s)

@@ -12,35 +12,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _params(pk, cache, q, out, lse, rows, starts, firsts, columns, chunk, workspace=None):
-    """The parameter block of include/crit_b200.h for one launch, filled as crit_b200.attend fills it."""
-    from crit_b200 import _lib
-    dev = q.device
-    i32 = dict(dtype=torch.int32, device=dev)
-    held = dict(rows=torch.tensor(rows, **i32), starts=torch.tensor(starts, **i32),
-                firsts=torch.tensor(firsts, dtype=torch.int64, device=dev))
-    T, hq, d = q.shape
-    positions = cache.tables.shape[1] * cache.page
-    p = _lib.AttendParams()
-    p.q, p.out, p.lse = q.data_ptr(), out.data_ptr(), lse.data_ptr()
-    p.key_pages, p.value_pages = cache.k.data_ptr(), cache.v.data_ptr()
-    if cache.ks is not None:
-        p.key_scales, p.value_scales = cache.ks.data_ptr(), cache.vs.data_ptr()
-    p.tables, p.rows, p.starts, p.firsts = (cache.tables.data_ptr(), held["rows"].data_ptr(), held["starts"].data_ptr(),
-                                            held["firsts"].data_ptr())
-    p.q_stride_token, p.q_stride_head = q.stride(0), q.stride(1)
-    p.out_stride_token, p.out_stride_head = out.stride(0), out.stride(1)
-    p.table_stride = cache.tables.stride(0)
-    p.n_rows, p.columns, p.partial_rows = len(rows), columns, len(rows) * columns
-    p.q_heads, p.kv_heads, p.head_dim, p.value_dim, p.page = hq, cache.hkv, d, cache.dv, cache.page
-    p.kind, p.page_dtype, p.q_dtype = pk.KINDS[cache.kind], _lib.DTYPE_BF16, _lib.DTYPE_BF16
-    p.chunk, p.max_splits = chunk, -(-positions // chunk)
-    p.slots = cache.k.numel() // (cache.hkv * d)
-    p.scale = d ** -0.5
-    p.key_multiplier, p.value_multiplier = cache.multipliers
-    if workspace is not None:
-        p.workspace, p.workspace_floats = workspace.data_ptr(), workspace.numel()
-    return p, held
+def _params(pk, cache, q, out, lse, rows, starts, firsts, columns, chunk, workspace=None, **more):
+    from helpers import attend_params
+    return attend_params(cache, q, out, lse, rows, starts, firsts, columns, chunk, workspace=workspace, **more)
 
 
 @pytest.mark.parametrize("kind", ["bf16", "fp8:page"])
@@ -74,3 +48,61 @@ def test_the_static_scratch_entry_point_gives_the_ordinary_ones_bits_twice_in_a_
     p.partial_rows = 1 << 20
     code = lib.crit_b200_attend_static(ctypes.byref(p), stream)
     assert code == -5 and b"16 MiB" in lib.crit_b200_error(code)
+    # sizes whose product passes 64 bits are refused too, not wrapped under the limit
+    p.partial_rows, p.max_splits = (1 << 31) - 1, (1 << 31) - 1
+    assert lib.crit_b200_attend_static(ctypes.byref(p), stream) == -5
+
+
+def test_the_static_scratch_holds_exactly_its_stated_floats():
+    """The last launch that fits (its partials packed by offsets, so the count of partial rows is the caller's to
+    state) passes with the ordinary entry point's bits; one partial row more is refused."""
+    import crit_b200 as pk
+    from crit_b200 import _lib
+    from helpers import Cache, queries
+    lib = _lib.load()
+    cache = Cache("bf16", 4, 128, 128, 16, [700, 300, 2100, 40], spare=8)
+    rows, starts, columns, chunk = [0, 1, 2, 3], [0, 4, 8, 12], 4, 256
+    firsts = [690, 290, 2090, 30]
+    splits = -(-cache.tables.shape[1] * 16 // chunk)
+    per_row = 24 * splits * 130
+    most = (4 * 1024 * 1024) // per_row                  # partial rows the array holds at this geometry
+    assert most >= 16
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    q = queries(16, 24, 128, 8)
+    want, want_lse = torch.zeros(16, 24, 128, dtype=torch.bfloat16, device="cuda"), torch.zeros(16, 24, device="cuda")
+    got, got_lse = torch.zeros_like(want), torch.zeros_like(want_lse)
+    space = torch.empty(most * per_row, device="cuda")
+    p, held = _params(pk, cache, q, want, want_lse, rows, starts, firsts, columns, chunk, workspace=space,
+                      offsets=[0, 4, 8, 12], partial_rows=most)
+    assert lib.crit_b200_attend(ctypes.byref(p), stream) == 0
+    p, held2 = _params(pk, cache, q, got, got_lse, rows, starts, firsts, columns, chunk, offsets=[0, 4, 8, 12], partial_rows=most)
+    assert lib.crit_b200_attend_static(ctypes.byref(p), stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and torch.equal(got_lse, want_lse) and want.float().abs().sum() > 0
+    p.partial_rows = most + 1
+    assert lib.crit_b200_attend_static(ctypes.byref(p), stream) == -5
+
+
+def test_the_static_scratch_entry_point_on_one_split_and_on_tcgen05_tiles():
+    """Rows of one split never touch the scratch; with CRIT_B200_ATTEND_TCGEN05 the tcgen05 kernel's partials go
+    through it: both give the ordinary entry point's bits."""
+    import crit_b200 as pk
+    from crit_b200 import _lib
+    from helpers import Cache, queries
+    lib = _lib.load()
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    cache = Cache("fp8:page", 4, 128, 128, 16, [700, 300, 2100, 40], spare=8)
+    rows, starts, columns, firsts = [0, 1, 2, 3], [0, 4, 8, 12], 4, [690, 290, 2090, 30]
+    q = queries(16, 24, 128, 6)
+    for chunk, flags in ((cache.tables.shape[1] * 16, 0), (256, 8)):       # one split a row; the tcgen05 kernel's flag
+        want, want_lse = torch.zeros(16, 24, 128, dtype=torch.bfloat16, device="cuda"), torch.zeros(16, 24, device="cuda")
+        got, got_lse = torch.zeros_like(want), torch.zeros_like(want_lse)
+        splits = -(-cache.tables.shape[1] * 16 // chunk)
+        space = torch.empty(max(pk.workspace_floats(16, 24, splits, 128), 4), device="cuda")
+        p, held = _params(pk, cache, q, want, want_lse, rows, starts, firsts, columns, chunk, workspace=space, flags=flags)
+        assert lib.crit_b200_attend(ctypes.byref(p), stream) == 0
+        p, held2 = _params(pk, cache, q, got, got_lse, rows, starts, firsts, columns, chunk, flags=flags)
+        assert lib.crit_b200_attend_static(ctypes.byref(p), stream) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(got, want) and torch.equal(got_lse, want_lse) and want.float().abs().sum() > 0, (chunk, flags)
+    assert pk.status() == 0
