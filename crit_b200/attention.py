@@ -14,20 +14,32 @@ and the step's metadata is one small upload of five numbers a row.  Any pool wit
 builds them.
 """
 import math
+from dataclasses import dataclass
 
-from . import partition
+from . import host_form
 
 TABLE_WIDTH = 16      # a generic pool's per-step tables are this many pages wide or a multiple (reference :1079)
 PIECE_COLUMNS = 64    # columns of a prompt row's piece when it is read by the decode kernel
 
 
+@dataclass
 class Windows:
-    """Window rows of one launch as device tensors: tables, each row's table row, first token, column count (None:
-    `columns` each), column 0's position, and with `offsets` its first partial row."""
+    """The window rows of one launch, on the device.  Row r reads the page table tables[rows[r]]; its tokens are
+    starts[r] .. starts[r] + counts[r] - 1 of the step's queries (counts None: `columns` each) and its column 0 sits at
+    position firsts[r].  offsets[r] (optional) is its first partial row when the rows' partials are packed by their
+    tokens; packed[r] is then the host's copy of its token count and total the tokens of all rows."""
+    tables: object
+    rows: object
+    starts: object
+    counts: object
+    firsts: object
+    columns: int
+    offsets: object = None
+    packed: object = None
+    total: object = None
 
-    def __init__(self, tables, rows, starts, counts, firsts, columns, offsets=None, bounds=None, total=None):
-        self.tables, self.rows, self.starts, self.counts, self.firsts = tables, rows, starts, counts, firsts
-        self.columns, self.offsets, self.bounds, self.total = int(columns), offsets, bounds, total
+    def __len__(self):
+        return int(self.starts.shape[0])
 
 
 class DeviceAttention:
@@ -106,7 +118,7 @@ class DeviceAttention:
             if n:
                 bounds = [batch.row(r)[2] for r in pool.windows]
                 meta = Windows(pool.d_tables, pool.d_rows[:n], pool.d_starts[:n], pool.d_counts[:n], pool.d_firsts[:n],
-                               pool.window, offsets=pool.d_offsets[:n], bounds=bounds, total=q.shape[0])
+                               pool.window, offsets=pool.d_offsets[:n], packed=bounds, total=q.shape[0])
                 self._windows(layer, q, pool, meta, scale, out, found)
             chosen = set(pool.windows)
             self._prompts(layer, q, pool, batch, [r for r in range(batch.rows) if r not in chosen], scale, out, found)
@@ -146,12 +158,11 @@ class DeviceAttention:
             chunk = max(chunk, -(-positions // self.partitions))
         chunk = -(-chunk // 16) * 16
         parts = kernels.parts_for(positions, chunk)
-        count = int(meta.starts.shape[0])
-        launches, workspace = [(slice(0, count), meta.total)], None
+        launches, workspace = [(slice(0, len(meta)), meta.total)], None
         if self.partial_bytes and parts > 1:
+            # the partials come from the engine's scratch: as many rows a launch as its share of the scratch holds
             per = kernels.workspace_floats(1, q.shape[1], parts, pool.value_dim)
-            capacity = self.partial_bytes // 4 // per
-            launches = _launches(meta, capacity)
+            launches = launch_cuts(meta, self.partial_bytes // 4 // per)
             most = max((cut.stop - cut.start) * meta.columns if tokens is None else tokens for cut, tokens in launches)
             import torch
             workspace = self.scratch.take(min(self.partial_bytes, 4 * per * most)).view(torch.float32)
@@ -220,24 +231,27 @@ class DeviceAttention:
         self._windows(layer, q, pool, meta, scale, out, found)
 
 
-def _launches(meta, capacity):
-    """[(rows, partial rows)]: consecutive rows whose partials fit `capacity` partial rows."""
-    count = int(meta.starts.shape[0])
-    if meta.offsets is None or meta.bounds is None:
+def launch_cuts(meta, capacity):
+    """Consecutive runs of window rows whose partial rows fit a workspace of `capacity` partial rows:
+    [(slice of rows, partial rows of the run or None)].  Rows without packed partials take `columns` partial rows each
+    (None: the launch counts them itself); packed rows take their own token counts, found by one cumulative sum and a
+    search per run.  A row that alone passes the capacity is refused."""
+    import numpy as np
+    n = len(meta)
+    if meta.offsets is None or meta.packed is None:
         step = capacity // meta.columns
         if step < 1:
             raise _too_small(meta.columns)
-        return [(slice(a, min(count, a + step)), None) for a in range(0, count, step)]
-    found, first, used = [], 0, 0
-    for r, bound in enumerate(meta.bounds):
-        if min(used + bound, meta.total) > capacity:
-            if r == first:
-                raise _too_small(bound)
-            found.append((slice(first, r), min(used, meta.total)))
-            first, used = r, 0
-        used += bound
-    found.append((slice(first, count), min(used, meta.total)))
-    return found
+        return [(slice(a, min(n, a + step)), None) for a in range(0, n, step)]
+    upto = np.cumsum(np.asarray(meta.packed, dtype=np.int64))
+    cuts, first, before = [], 0, 0
+    while first < n:
+        end = int(np.searchsorted(upto, before + capacity, side="right"))
+        if end <= first:
+            raise _too_small(int(meta.packed[first]))
+        cuts.append((slice(first, end), int(upto[end - 1] - before)))
+        first, before = end, int(upto[end - 1])
+    return cuts
 
 
 def _too_small(tokens):
@@ -267,31 +281,27 @@ def windows_of(pool, rows, device):
                          in zip(rows, offsets, ids)], dtype=torch.int64)
     meta = (meta.pin_memory() if torch.device(device).type == "cuda" else meta).to(device, non_blocking=True)
     return Windows(tables, meta[:, 4].to(torch.int32), meta[:, 0].to(torch.int32), meta[:, 1].to(torch.int32),
-                   meta[:, 2].contiguous(), max(counts), offsets=meta[:, 3].to(torch.int32), bounds=counts,
+                   meta[:, 2].contiguous(), max(counts), offsets=meta[:, 3].to(torch.int32), packed=counts,
                    total=sum(counts))
 
 
 class PartitionedAttention:
-    """The attention slot's plugin object: the host form (partials of interleaved ownership, merged) and the device
-    form above.  Reference: inference/partitioned-attention/plugin.py:15-64."""
+    """The attention slot's plugin object: the host form (every query's softmax taken shard by shard over interleaved
+    ownership and merged by the shards' log-sum-exps: host_form) and the device form above.  The plugin it stands in
+    for: inference/partitioned-attention/plugin.py:15-64."""
 
     def __init__(self, kv, options, device_form):
-        self.kv, self.device_form = kv, device_form
-        self.ranks = [partition.SequencePartition(options["world"], rank, options["page_size"])
-                      for rank in range(options["world"])]
+        self.kv, self.device_form, self.world = kv, device_form, int(options["world"])
 
     def attend(self, sequence, queries, positions, scale=None, pending=False):
-        rows = self.kv.rows(sequence, pending)
-        if not rows:
+        """Each query over the sequence's rows at positions up to its own -> [output row] (lists of floats)."""
+        keys, values = self.kv.arrays(sequence, pending) if hasattr(self.kv, "arrays") else _matrices(self.kv.rows(sequence, pending))
+        if not len(keys):
             raise ValueError("no rows to attend")
-        width = len(rows[0][2])
-        out = []
-        for query, position in zip(queries, positions):
-            partials = [partition.attention_partial(query, [row for row in rows if rank.owner(row[0]) == rank.rank],
-                                                    value_width=width, query_position=position, scale=scale)
-                        for rank in self.ranks]
-            out.append(list(partition.merge_partials(partials).output))
-        return out
+        if len(queries) != len(positions):
+            raise ValueError("one position per query")
+        return [host_form.attend(query, keys, values, position, self.world, scale).tolist()
+                for query, position in zip(queries, positions)]
 
     def forward(self, layer, queries, pool, batch, scale=None, blocks=None, block_size=None, parents=None, lse=False):
         return self.device_form.forward(layer, queries, pool, batch, scale, blocks, block_size, parents, lse)
@@ -307,3 +317,11 @@ class PartitionedAttention:
 
     def close(self):
         self.device_form.close()
+
+
+def _matrices(rows):
+    """[(position, key, value)] in position order -> (keys, values) matrices (another plugin's kv_cache host form)."""
+    import numpy as np
+    if not rows:
+        return np.empty((0, 0)), np.empty((0, 0))
+    return np.array([key for _, key, _ in rows], dtype=np.float64), np.array([value for _, _, value in rows], dtype=np.float64)

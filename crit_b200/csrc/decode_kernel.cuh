@@ -35,6 +35,13 @@
 
 namespace crit_b200 {
 
+#ifndef CRIT_DECODE_STAGES_SMALL
+#define CRIT_DECODE_STAGES_SMALL 4          // stages of a warp's ring where an iteration takes two tiles
+#endif
+#ifndef CRIT_DECODE_MIN_BLOCKS
+#define CRIT_DECODE_MIN_BLOCKS 0            // blocks an SM the registers are budgeted for (0: what the shared memory allows)
+#endif
+
 constexpr int DECODE_WARPS = 4;
 constexpr int DECODE_THREADS = DECODE_WARPS * 32;
 constexpr float LAZY = 8.f;
@@ -50,7 +57,7 @@ struct DecodeCfg {
     static constexpr int KTILE = 16 * KROW, VTILE = 16 * VROW;
     static constexpr int TILES = KTILE + VTILE;
     static constexpr int TPI = TILES <= 4096 ? 2 : 1;          // tiles an iteration consumes
-    static constexpr int STAGES = TPI == 2 ? 4 : 3;         // (3 stages and 4 blocks an SM measured 124 us against 112)
+    static constexpr int STAGES = TPI == 2 ? CRIT_DECODE_STAGES_SMALL : 3;
     static constexpr int ROWS = 8 * NT;
     static constexpr int QROW = D * 2 + 16;                    // padded: rows 8 apart fall in different banks
     static constexpr int QBYTES = ROWS * QROW;
@@ -60,6 +67,12 @@ struct DecodeCfg {
     __host__ __device__ static constexpr int ring_bytes(int scb) { return DECODE_WARPS * STAGES * (TILES + scb); }
     __host__ __device__ static constexpr int region(int scb) { return ((ring_bytes(scb) > FOLD ? ring_bytes(scb) : FOLD) + 127) / 128 * 128; }
     __host__ __device__ static constexpr int smem_bytes(int scb) { return 1024 + region(scb) + QBYTES + DECODE_WARPS * STAGES * 8; }
+    // blocks an SM holds by its 227 KB of shared memory (the scales' stage at its cp.async size).  A decode tile (8 query
+    // rows) budgets its registers for as many, up to 3, so the compiler never trades a resident block for registers;
+    // the wider tiles hold 2 or 4 times the accumulators and take what they need
+    static constexpr int BY_SMEM = 232448 / (smem_bytes(128) + 1024);
+    static constexpr int MIN_BLOCKS = CRIT_DECODE_MIN_BLOCKS ? CRIT_DECODE_MIN_BLOCKS
+                                                             : (NT > 1 || BY_SMEM < 1 ? 1 : (BY_SMEM > 3 ? 3 : BY_SMEM));
 };
 
 __device__ __forceinline__ int swz16(int c, int row) { return (c & ~7) | ((c ^ row) & 7); }
@@ -94,7 +107,7 @@ __device__ __forceinline__ int tile_off(int row, int c) {
 }
 
 template <int D, int DV, int PK, int NT, bool TMA>
-__global__ void __launch_bounds__(DECODE_THREADS)
+__global__ void __launch_bounds__(DECODE_THREADS, DecodeCfg<D, DV, PK, NT, TMA>::MIN_BLOCKS)
 decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode, const int scb, const int persistent,
               const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
     using C = DecodeCfg<D, DV, PK, NT, TMA>;
@@ -284,19 +297,55 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     const int64_t krow_stride = (int64_t)p.kv_heads * C::KROW, vrow_stride = (int64_t)p.kv_heads * C::VROW;
     const uint32_t scale_bytes = smode == 2 ? (uint32_t)p.kv_heads * 4u : (smode == 1 ? (uint32_t)p.kv_heads * 64u : 0u);
     const uint32_t tiles_per_page = (uint32_t)p.page >> 4;
-    const uint32_t pages_total = p.slots > 0 ? (uint32_t)(p.slots / p.page) : 0u;      // 0: the tensor's size is not known
+    // a page id at or past this lies outside the page tensor (the tensor's size unknown: no page id does)
+    const uint32_t pages_total = p.slots > 0 ? (uint32_t)(p.slots / p.page) : 0x7fffffffu;
+    const int tshift = (tiles_per_page & (tiles_per_page - 1)) == 0 ? __ffs((int)tiles_per_page) - 1 : -1;
     const int Lr = (int)L;
 
+    // The page ids of this warp's tiles, 32 tiles at a time: lane j holds the page of tile i0 + j of the warp's tiles (one
+    // load a lane per 32 tiles, made 32 tiles ahead), and a tile's id reaches every lane by a shuffle.  So no tile waits
+    // for a table read on its way to the copies.
+    auto page_ids = [&](int i0) {
+        const int k = i0 + lane;
+        if (k >= mine) return 0;
+        const uint32_t tile = (uint32_t)(tile0 + warp + k * DECODE_WARPS);
+        return table[tshift >= 0 ? tile >> tshift : tile / tiles_per_page];
+    };
+    int pgs = 0, pgs_next = page_ids(0);
+    bool outside = false;
+
+    // cp.async staging of small tiles (four copies a lane for the keys, four for the values): each lane's source and
+    // destination offsets inside a tile are fixed, so they are made once
+    constexpr bool FIXED = !TMA && 16 * KC / 32 <= 4 && 16 * VC / 32 <= 4;
+    constexpr int KU = FIXED ? 16 * KC / 32 : 1, VU = FIXED ? 16 * VC / 32 : 1;
+    int ksrc[KU], kdst[KU], vsrc[VU], vdst[VU];
+    if constexpr (FIXED) {
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            const int id = lane + 32 * u, row = id / KC, c = id - row * KC;
+            ksrc[u] = row * (int)krow_stride + c * 16;
+            kdst[u] = tile_off<false, C::KROW, ES, D, false>(row, c);
+        }
+#pragma unroll
+        for (int u = 0; u < VU; ++u) {
+            const int id = lane + 32 * u, row = id / VC, c = id - row * VC;
+            vsrc[u] = row * (int)vrow_stride + c * 16;
+            vdst[u] = C::KTILE + tile_off<false, C::VROW, ES, DV, true>(row, c);
+        }
+    }
+
     auto issue = [&](int i) {
+        if ((i & 31) == 0) {
+            pgs = pgs_next;
+            pgs_next = page_ids(i + 32);
+        }
         if (i < mine) {
             const uint32_t tile = (uint32_t)(tile0 + warp + i * DECODE_WARPS);
-            const uint32_t pidx = tile / tiles_per_page;
+            const uint32_t pidx = tshift >= 0 ? tile >> tshift : tile / tiles_per_page;
             const int off = (int)(tile - pidx * tiles_per_page) << 4;
-            int pg = table[pidx];
-            if (pages_total && (uint32_t)pg >= pages_total) {     // a page id outside the page tensor: the last page is read
-                pg = (int)pages_total - 1;                        // instead and the launch reports it
-                if (lane == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_BOUNDS);
-            }
+            const uint32_t listed = (uint32_t)__shfl_sync(0xffffffffu, pgs, i & 31);
+            outside |= listed >= pages_total;           // read the tensor's last page instead; reported at the unit's end
+            const int pg = (int)(listed < pages_total ? listed : pages_total - 1);
             const int64_t slot0 = (int64_t)pg * p.page + off;
             const int stage = (tbase + i) % C::STAGES;
             const uint32_t ks = smem_addr(tiles + stage * C::TILES), vs = ks + C::KTILE;
@@ -318,19 +367,28 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
                 }
             } else {
                 const int live = Lr - (int)(tile << 4);          // rows past it are zero-filled
+                if (FIXED && live >= 16) {
+                    const char* ksrc0 = kbase + slot0 * krow_stride;
+                    const char* vsrc0 = vbase + slot0 * vrow_stride;
 #pragma unroll
-                for (int u = 0; u < 16 * KC / 32; ++u) {
-                    const int id = lane + 32 * u, row = id / KC, c = id - row * KC;
-                    const bool ok = row < live;
-                    cp_async16(ks + tile_off<false, C::KROW, ES, D, false>(row, c),
-                               kbase + (slot0 + (ok ? row : 0)) * krow_stride + c * 16, ok);
-                }
+                    for (int u = 0; u < KU; ++u) cp_async16(ks + kdst[u], ksrc0 + ksrc[u], true);
 #pragma unroll
-                for (int u = 0; u < 16 * VC / 32; ++u) {
-                    const int id = lane + 32 * u, row = id / VC, c = id - row * VC;
-                    const bool ok = row < live;
-                    cp_async16(vs + tile_off<false, C::VROW, ES, DV, true>(row, c),
-                               vbase + (slot0 + (ok ? row : 0)) * vrow_stride + c * 16, ok);
+                    for (int u = 0; u < VU; ++u) cp_async16(ks + vdst[u], vsrc0 + vsrc[u], true);
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 16 * KC / 32; ++u) {
+                        const int id = lane + 32 * u, row = id / KC, c = id - row * KC;
+                        const bool ok = row < live;
+                        cp_async16(ks + tile_off<false, C::KROW, ES, D, false>(row, c),
+                                   kbase + (slot0 + (ok ? row : 0)) * krow_stride + c * 16, ok);
+                    }
+#pragma unroll
+                    for (int u = 0; u < 16 * VC / 32; ++u) {
+                        const int id = lane + 32 * u, row = id / VC, c = id - row * VC;
+                        const bool ok = row < live;
+                        cp_async16(vs + tile_off<false, C::VROW, ES, DV, true>(row, c),
+                                   vbase + (slot0 + (ok ? row : 0)) * vrow_stride + c * 16, ok);
+                    }
                 }
                 if (PK >= 2 && smode) {
                     const int row = lane & 15;
@@ -556,6 +614,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
         }
         __syncwarp();
     }
+    if (__any_sync(0xffffffffu, outside) && lane == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_BOUNDS);
     if constexpr (TMA) {
         if (__any_sync(0xffffffffu, dead)) {
             // Give every copy this warp still has in flight a last bounded chance to land before the block leaves.

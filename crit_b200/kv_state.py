@@ -1,86 +1,54 @@
 """The kv_cache slot's plugin object: the host form (rows staged after the committed ones stay pending until a commit
-keeps the accepted prefix) and the device form pool().  Reference: inference/attention-state/plugin.py:14-117 and
-code/implementation.py:5-50 (KVState)."""
-import math
-
+keeps the accepted prefix; host_form.Rows) and the device form pool().  The slot's interface:
+core/python/crit_plugins/slots.py:62-70; the plugin it stands in for: inference/attention-state/plugin.py."""
+from . import host_form
 from . import pool as pages
-
-
-class HostState:
-    """One sequence's rows on the host: committed, and pending until commit(count) keeps a prefix of them."""
-
-    def __init__(self, capacity, key_width, value_width):
-        for x in (capacity, key_width, value_width):
-            if type(x) is not int or x <= 0:
-                raise ValueError("positive integer state geometry required")
-        self.capacity, self.key_width, self.value_width = capacity, key_width, value_width
-        self.committed, self.pending = [], []
-
-    def stage(self, key, value):
-        key, value = tuple(key), tuple(value)
-        if len(key) != self.key_width or len(value) != self.value_width:
-            raise ValueError("KV geometry differs")
-        if not all(math.isfinite(x) for x in key + value):
-            raise ValueError("finite KV values required")
-        if len(self.committed) + len(self.pending) >= self.capacity:
-            raise ValueError("KV capacity exhausted")
-        self.pending.append((key, value))
-
-    def commit(self, count=None):
-        count = len(self.pending) if count is None else count
-        if type(count) is not int or not 0 <= count <= len(self.pending):
-            raise ValueError("commit exceeds staged state")
-        self.committed += self.pending[:count]
-        self.pending.clear()
-
-    def rollback(self):
-        self.pending.clear()
 
 
 class KVStateCache:
     def __init__(self, page=16, step_rows=0, step_tokens=0, window=16, round_rows=8, kernels=None, sequences=64):
-        self.states, self.page = {}, page
-        self.step_rows, self.step_tokens, self.window = step_rows, step_tokens, window
-        self.round_rows, self.kernels, self.sequences = round_rows, kernels, sequences
+        self.page, self.kernels, self.sequences = page, kernels, sequences
+        self.step_rows, self.step_tokens, self.window, self.round_rows = step_rows, step_tokens, window, round_rows
+        self.held = {}              # sequence -> host_form.Rows
         self.pools = []
 
-    def _state(self, sequence):
-        try:
-            return self.states[sequence]
-        except KeyError:
-            raise ValueError(f"sequence {sequence!r} is not open") from None
-
     # -- the host form ---------------------------------------------------------------------------------------------------
+    def _rows(self, sequence):
+        found = self.held.get(sequence)
+        if found is None:
+            raise ValueError(f"sequence {sequence!r} is not open")
+        return found
+
     def open(self, sequence, key_width, value_width, capacity):
-        if sequence in self.states:
+        if sequence in self.held:
             raise ValueError(f"sequence {sequence!r} is open already")
-        self.states[sequence] = HostState(capacity, key_width, value_width)
+        self.held[sequence] = host_form.Rows(key_width, value_width, capacity)
 
     def stage(self, sequence, keys, values):
-        if len(keys) != len(values):
-            raise ValueError("one value row per key row")
-        state = self._state(sequence)
-        for key, value in zip(keys, values):
-            state.stage(key, value)
+        self._rows(sequence).append(keys, values)
 
     def commit(self, sequence, count=None):
-        self._state(sequence).commit(count)
+        self._rows(sequence).settle(count)
 
     def rollback(self, sequence):
-        self._state(sequence).rollback()
+        self._rows(sequence).drop()
 
     def rows(self, sequence, pending=False):
-        state = self._state(sequence)
-        held = state.committed + (state.pending if pending else [])
-        return [(position, list(key), list(value)) for position, (key, value) in enumerate(held)]
+        keys, values = self._rows(sequence).view(staged=pending)
+        return [(position, key, value) for position, (key, value) in enumerate(zip(keys.tolist(), values.tolist()))]
+
+    def arrays(self, sequence, pending=False):
+        """The same rows as two float64 matrices (keys [n][key width], values [n][value width]): what the attention
+        slot's host form reads."""
+        return self._rows(sequence).view(staged=pending)
 
     def fork(self, sequence, new):
-        state = self._state(sequence)
-        self.open(new, state.key_width, state.value_width, state.capacity)
-        self.states[new].committed = list(state.committed)
+        if new in self.held:
+            raise ValueError(f"sequence {new!r} is open already")
+        self.held[new] = self._rows(sequence).fork()
 
     def release(self, sequence):
-        self.states.pop(sequence, None)
+        self.held.pop(sequence, None)
 
     # -- the device form -------------------------------------------------------------------------------------------------
     def pool(self, layers, kv_heads, head_dim, tokens, device, dtype="bf16", *, page=None, value_dim=None, spare=0,
