@@ -270,7 +270,7 @@ def build_state(w, device, rank, world):
         # one long row read alone: the split size that fills the device's resident blocks in whole waves
         from crit_b200.dist import chunk_to_fill
         found = pk.plan(hq, hkv, d, d, page, w["kind"], 1, device)
-        state["chunk"] = chunk_to_fill(lens[0], hkv, found["sms"] * max(found["per_sm"], 1))
+        state["chunk"] = chunk_to_fill(lens[0], hkv, found["sms"] * max(found["per_sm"], 1), waves=1 if sharded else None)
     return state
 
 
@@ -475,8 +475,19 @@ def measure(name, w, args, device, rank, world, local, primary):
         barrier()
         with Clocks(local) as clocks:
             seconds, fastest, slowest = timed(runs[0], steps, args.warmup, stream, samples)
-            # the dominant kernel alone (same stream, CUDA events)
-            decode_s, _, _ = timed(lambda: step(state, launch="decode", append=False), max(20, steps), 3, stream, 5)
+            # the dominant kernel alone (same stream, CUDA events): five launches back to back from a graph, so that the
+            # launches' host cost is not what is timed
+            decode_fn, reps = (lambda: step(state, launch="decode", append=False)), 1
+            if not args.no_graph and state["live"]:
+                try:
+                    decode_graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(decode_graph, stream=stream):
+                        for _ in range(5):
+                            step(state, launch="decode", append=False)
+                    decode_fn, reps = decode_graph.replay, 5
+                except Exception:
+                    torch.cuda.synchronize()
+            decode_s = timed(decode_fn, max(4, steps // 2), 3, stream, 7)[0] / reps
         barrier()
         # the fold of the splits (a few microseconds): ten launches back to back from a graph, so that the launches' host
         # cost is not what is timed

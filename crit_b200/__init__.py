@@ -417,10 +417,12 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
         if lse is None:
             raise ValueError("a sharded context's merge writes lse too: pass lse")
         with torch.cuda.device(device):
-            if launch in ("both", "decode"):
+            if launch in ("both", "decode", "push"):
                 _lib.check(lib.crit_b200_decode(ctypes.byref(p), _stream(device)), "crit_b200.attend")
             if launch in ("both", "merge"):
                 shards.attend(p, out, lse)
+            elif launch == "push":             # decode and fold + push, no wait: a measurement's
+                shards.attend(p, out, lse, wait=False)
         return out
     call = {"both": lib.crit_b200_attend, "decode": lib.crit_b200_decode, "merge": lib.crit_b200_merge}[launch]
     with torch.cuda.device(device):

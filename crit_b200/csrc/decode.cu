@@ -146,85 +146,113 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
 }
 
 
-// The fold of a rank's splits, sent: what merge_warp_kernel computes for a (token, head), normalised, goes as FP32 into
-// slot [step & 1][rank] of EVERY rank's exchange buffer (peer stores over NVLink; this rank's own buffer too) instead of
-// into `out`: a message is [tokens x heads][DV] outputs, [tokens x heads] log-sum-exps (natural log), then (rank, step,
-// tokens x heads) as int32 bits.  A column past its row's count, and a row that holds no position, send zeros and -inf.
-// The blocks count themselves on a ticket in this rank's buffer; the last one stores the header, raises this rank's
-// flag in every buffer (system-scope release) and moves the step counter on.  Nothing here waits.
+// The fold of a rank's splits, sent: what merge_kernel computes for a (token, head), normalised, goes as FP32 into slot
+// [step & 1][rank] of EVERY rank's exchange buffer (peer stores over NVLink; this rank's own buffer too) instead of into
+// `out`: a message is [tokens x heads][DV] outputs, [tokens x heads] log-sum-exps (natural log), then (rank, step,
+// tokens x heads) as int32 bits.  Block = (window token, query head); warp w folds splits w, w + 8, ... and the eight
+// warps' states are folded in warp order, so a row of a hundred splits costs a dozen dependent loads, not a hundred.  A
+// column past its row's count, and a row that holds no position, send zeros and -inf.  The blocks count themselves on a
+// ticket in this rank's buffer; the last one stores the header, raises this rank's flag in every buffer (system-scope
+// release) and moves the step counter on.  Nothing here waits.
 template <int DV>
-__global__ void __launch_bounds__(128) merge_push_kernel(const crit_b200_attend_params p, const crit_b200_exchange_params x) {
+__global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit_b200_attend_params p, const crit_b200_exchange_params x) {
     constexpr int PER = DV / 32;
-    const int lane = threadIdx.x & 31;
+    __shared__ float sm[MERGE_WARPS], sl[MERGE_WARPS];
+    __shared__ float so[MERGE_WARPS][DV];
+    __shared__ float* slots[EX_MAX_WORLD];          // this rank's slot of the step in every rank's buffer
+    __shared__ uint64_t bases[EX_MAX_WORLD];        // every rank's buffer (read once: the array lives in global memory)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int32_t step = *x.step + 1;
-    const int64_t item = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
-    const int64_t items = (int64_t)p.n_rows * p.columns * p.q_heads;
     const int64_t stride = ex_stride(x.floats);
+    if (threadIdx.x < x.world) {
+        bases[threadIdx.x] = x.peers[threadIdx.x];
+        slots[threadIdx.x] = ex_slot(bases[threadIdx.x], step, x.world, x.rank, stride);
+    }
     const int64_t n = (x.floats - EX_HEADER) / (DV + 1);           // (token, head) pairs of a message
-    if (item < items) {
-        const int head = (int)(item % p.q_heads);
-        const int rc = (int)(item / p.q_heads);
-        const int r = rc / p.columns, col = rc - r * p.columns;
-        int count = p.counts ? p.counts[r] : p.columns;
-        count = count > p.columns ? p.columns : count;
-        const int64_t L = p.firsts[r] + (count > 0 ? count : 0);
-        const int nsplit = count > 0 ? (int)((L + p.chunk - 1) / p.chunk) : 0;
-        const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
-        const int64_t entry = (int64_t)(p.starts[r] + col) * p.q_heads + head;
-        float total = 0.f, top = -INFINITY, acc[PER];
+    const int head = blockIdx.x;
+    const int r = blockIdx.y / p.columns, col = blockIdx.y - r * p.columns;
+    int count = p.counts ? p.counts[r] : p.columns;
+    count = count > p.columns ? p.columns : count;
+    const int64_t L = p.firsts[r] + (count > 0 ? count : 0);
+    const int nsplit = count > 0 ? (int)((L + p.chunk - 1) / p.chunk) : 0;
+    const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
+    const int64_t entry = (int64_t)(p.starts[r] + col) * p.q_heads + head;
+    const bool listed = entry >= 0 && entry < n;
+    const bool fits = nsplit <= p.max_splits && prow >= 0 && prow < p.partial_rows;
+    float m = -INFINITY, l = 0.f, acc[PER];
 #pragma unroll
-        for (int i = 0; i < PER; ++i) acc[i] = 0.f;
-        bool fits = entry >= 0 && entry < n;
-        if (col < count && nsplit > 0 && fits) {
-            fits = nsplit <= p.max_splits && prow >= 0 && prow < p.partial_rows;
-            if (fits) {
-                const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
-                const int64_t base = ((int64_t)prow * p.q_heads + head) * p.max_splits;
-                const float* pm = p.workspace + states * DV;
-                const float* pl = p.workspace + states * (DV + 1);
-                for (int s = lane; s < nsplit; s += 32) top = fmaxf(top, pm[base + s]);
-                top = warp_max(top);
-                const float sub = top == -INFINITY ? 0.f : top;
+    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+    if (listed && fits && col < count) {
+        const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
+        const int64_t base = ((int64_t)prow * p.q_heads + head) * p.max_splits;
+        const float* pm = p.workspace + states * DV;
+        const float* pl = p.workspace + states * (DV + 1);
 #pragma unroll 4
-                for (int s = 0; s < nsplit; ++s) {
-                    const float w = ex2(pm[base + s] - sub);
-                    total += pl[base + s] * w;
-                    const float* o = p.workspace + (base + s) * DV + lane * PER;
+        for (int s = warp; s < nsplit; s += MERGE_WARPS) {
+            const float ms = pm[base + s], ls = pl[base + s];
+            const float* o = p.workspace + (base + s) * DV + lane * PER;
+            float v[PER];
 #pragma unroll
-                    for (int i = 0; i < PER; i += 2) {
-                        const float2 v = *reinterpret_cast<const float2*>(o + i);
-                        acc[i] += v.x * w, acc[i + 1] += v.y * w;
-                    }
-                }
+            for (int i = 0; i < PER; i += 2) {
+                const float2 pair = *reinterpret_cast<const float2*>(o + i);
+                v[i] = pair.x, v[i + 1] = pair.y;
             }
-        }
-        if (!fits && lane == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
-        if (entry >= 0 && entry < n) {
-            const float inv = total > 0.f ? 1.f / total : 0.f;
-            const float lse = total > 0.f ? top * LN2 + logf(total) : -INFINITY;
-            for (int peer = 0; peer < x.world; ++peer) {
-                float* slot = ex_slot(x.peers[peer], step, x.world, x.rank, stride);
-                float* dst = slot + entry * DV + lane * PER;
+            const float top = fmaxf(m, ms);
+            const float sub = top == -INFINITY ? 0.f : top;
+            const float keep = ex2(m - sub), take = ex2(ms - sub);
+            l = l * keep + ls * take;
 #pragma unroll
-                for (int i = 0; i < PER; i += 2) *reinterpret_cast<float2*>(dst + i) = make_float2(acc[i] * inv, acc[i + 1] * inv);
-                if (lane == 0) slot[n * DV + entry] = lse;
-            }
+            for (int i = 0; i < PER; ++i) acc[i] = acc[i] * keep + v[i] * take;
+            m = top;
         }
     }
-    __threadfence_system();
+    if (listed && !fits && col < count && threadIdx.x == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
+    if (lane == 0) sm[warp] = m, sl[warp] = l;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) so[warp][lane * PER + i] = acc[i];
+    __syncthreads();
+    if (listed) {
+        float top = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < MERGE_WARPS; ++w) top = fmaxf(top, sm[w]);
+        const float sub = top == -INFINITY ? 0.f : top;
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < MERGE_WARPS; ++w) total += sl[w] * ex2(sm[w] - sub);
+        const float inv = total > 0.f ? 1.f / total : 0.f;
+        for (int c = threadIdx.x; c < DV; c += MERGE_WARPS * 32) {
+            float o = 0.f;
+#pragma unroll
+            for (int w = 0; w < MERGE_WARPS; ++w) o += so[w][c] * ex2(sm[w] - sub);
+            o *= inv;
+            for (int peer = 0; peer < x.world; ++peer) slots[peer][entry * DV + c] = o;
+        }
+        if (threadIdx.x == 0) {
+            const float lse = total > 0.f ? top * LN2 + logf(total) : -INFINITY;
+            for (int peer = 0; peer < x.world; ++peer) slots[peer][n * DV + entry] = lse;
+        }
+    }
+    // The block's stores are ordered before its ticket by ONE system-scope fence: the barrier makes them visible to
+    // thread 0 and its fence is cumulative (a fence per thread would drain the NVLink writes hundreds of times).
     __syncthreads();
     if (threadIdx.x == 0) {
-        int32_t* mine = reinterpret_cast<int32_t*>(x.peers[x.rank]);
+        __threadfence_system();
+        int32_t* mine = reinterpret_cast<int32_t*>(bases[x.rank]);
         const int done = atomicAdd(mine + EX_TICKET, 1);
-        if (done == (int)gridDim.x - 1) {
+        if (done == (int)(gridDim.x * gridDim.y) - 1) {
+            __threadfence();                    // the other blocks' stores, seen through their tickets
             mine[EX_TICKET] = 0;
-            __threadfence_system();
             for (int peer = 0; peer < x.world; ++peer) {
-                float* header = ex_slot(x.peers[peer], step, x.world, x.rank, stride) + n * (DV + 1);
+                float* header = slots[peer] + n * (DV + 1);
                 header[0] = __int_as_float(x.rank), header[1] = __int_as_float(step), header[2] = __int_as_float((int)n);
             }
+            // the headers, and everything seen above, before the flags: one fence, then plain system-scope stores (a
+            // release store per rank would drain the writes once per rank)
             __threadfence_system();
-            for (int peer = 0; peer < x.world; ++peer) st_release_sys(reinterpret_cast<int32_t*>(x.peers[peer]) + x.rank, step);
+            for (int peer = 0; peer < x.world; ++peer) {
+                int32_t* flag = reinterpret_cast<int32_t*>(bases[peer]) + x.rank;
+                asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
+            }
             *x.step = step;
         }
     }
@@ -536,12 +564,11 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_merge_push(const
     if (!e) e = check_exchange(x, false);
     if (e) return e;
     if (x.floats < EX_HEADER + p.value_dim + 1 || (x.floats - EX_HEADER) % (p.value_dim + 1)) return CRIT_B200_EINVAL;
-    const int64_t items = (int64_t)p.n_rows * p.columns * p.q_heads;
-    const unsigned blocks = (unsigned)((items + 3) / 4);
+    const dim3 blocks((unsigned)p.q_heads, (unsigned)(p.n_rows * p.columns));
     cudaStream_t s = (cudaStream_t)stream;
-    if (p.value_dim == 128) merge_push_kernel<128><<<blocks, 128, 0, s>>>(p, x);
-    else if (p.value_dim == 256) merge_push_kernel<256><<<blocks, 128, 0, s>>>(p, x);
-    else if (p.value_dim == 64) merge_push_kernel<64><<<blocks, 128, 0, s>>>(p, x);
+    if (p.value_dim == 128) merge_push_kernel<128><<<blocks, MERGE_WARPS * 32, 0, s>>>(p, x);
+    else if (p.value_dim == 256) merge_push_kernel<256><<<blocks, MERGE_WARPS * 32, 0, s>>>(p, x);
+    else if (p.value_dim == 64) merge_push_kernel<64><<<blocks, MERGE_WARPS * 32, 0, s>>>(p, x);
     else return CRIT_B200_EUNSUPPORTED;
     CRIT_CHECK_LAUNCH();
     return 0;

@@ -54,19 +54,19 @@ __global__ void __launch_bounds__(1024) shard_push_kernel(const crit_b200_exchan
     if (threadIdx.x < p.world) st_release_sys(reinterpret_cast<int32_t*>(p.peers[threadIdx.x]) + p.rank, step);
 }
 
-// One block: its first thread waits, then every thread copies.  (Several blocks, each with its own wait, could disagree
-// near the limit and leave `gathered` half written beside the status word.)
+// One block: its first `world` threads wait, one rank each, then every thread copies.  (Several blocks, each with its own
+// wait, could disagree near the limit and leave `gathered` half written beside the status word.)
 __global__ void __launch_bounds__(1024) shard_wait_kernel(const crit_b200_exchange_params p) {
-    __shared__ int landed;
     const int32_t step = *p.step;
-    if (threadIdx.x == 0) {
-        landed = ex_wait_flags(reinterpret_cast<const int32_t*>(p.peers[p.rank]), p.world, step, (uint64_t)p.wait_ns) ? 1 : 0;
-        if (!landed && p.status) atomicExch(p.status, 0x800 + p.rank);
+    const uint64_t own = p.peers[p.rank];
+    bool ok = true;
+    if (threadIdx.x < p.world) {            // thread r waits for rank r
+        ok = ex_wait_flag(reinterpret_cast<const int32_t*>(own) + threadIdx.x, step, (uint64_t)p.wait_ns);
+        if (!ok && p.status) atomicExch(p.status, 0x800 + p.rank);
     }
-    __syncthreads();
-    if (!landed) return;
+    if (!__syncthreads_and(ok ? 1 : 0)) return;
     const int64_t stride = ex_stride(p.floats);
-    const float* slot = ex_slot(p.peers[p.rank], step, p.world, 0, stride);
+    const float* slot = ex_slot(own, step, p.world, 0, stride);
     const int64_t total = (int64_t)p.world * p.floats;
     for (int64_t i = threadIdx.x; i < total; i += blockDim.x) {
         const int64_t r = i / p.floats, at = i - r * p.floats;
@@ -75,35 +75,33 @@ __global__ void __launch_bounds__(1024) shard_wait_kernel(const crit_b200_exchan
 }
 
 // The merge of the ranks' partials, read where the peers stored them.  A message is [n][dim] outputs, [n] log-sum-exps,
-// then (rank, step, n) as the bits of three int32.  One block: thread 0 waits for the flags and checks the headers; then thread t takes
+// then (rank, step, n) as the bits of three int32.  One block: thread r < world waits for rank r's flag and checks its header; then thread t takes
 // 4-float pieces t, t + 1024, ... of the n x dim outputs: top = max lse over the ranks, w = exp(lse - top) (0 for -inf),
 // out = sum w o / sum w in rank order, lse = top + log(sum w); a (token, head) no rank saw gets zeros and -inf.
 // Reference: inference/partitioned-attention/plugin.py:52-64.
 template <typename TOUT>
 __global__ void __launch_bounds__(1024) wait_merge_kernel(const crit_b200_exchange_params p, const crit_b200_merge_shards_params m) {
-    __shared__ int landed;
     const int32_t step = *p.step;
     const int64_t stride = ex_stride(p.floats);
-    const float* slot = ex_slot(p.peers[p.rank], step, p.world, 0, stride);
+    const uint64_t own = p.peers[p.rank];
+    const float* slot = ex_slot(own, step, p.world, 0, stride);
     const int64_t n = m.n;
     const int dim = m.dim;
-    if (threadIdx.x == 0) {
-        int ok = ex_wait_flags(reinterpret_cast<const int32_t*>(p.peers[p.rank]), p.world, step, (uint64_t)p.wait_ns) ? 1 : 0;
+    bool ok = true;
+    if (threadIdx.x < p.world) {            // thread r waits for rank r's flag, then checks rank r's header
+        const int r = threadIdx.x;
+        ok = ex_wait_flag(reinterpret_cast<const int32_t*>(own) + r, step, (uint64_t)p.wait_ns);
         if (!ok) {
             if (p.status) atomicExch(p.status, 0x800 + p.rank);
         } else {
-            for (int r = 0; r < p.world && ok; ++r) {
-                const float* header = slot + r * stride + n * (dim + 1);
-                if (__float_as_int(header[0]) != r || __float_as_int(header[1]) != step || __float_as_int(header[2]) != (int)n) {
-                    if (p.status) atomicExch(p.status, 0x900 + r);
-                    ok = 0;
-                }
+            const float* header = slot + r * stride + n * (dim + 1);
+            if (__float_as_int(header[0]) != r || __float_as_int(header[1]) != step || __float_as_int(header[2]) != (int)n) {
+                if (p.status) atomicExch(p.status, 0x900 + r);
+                ok = false;
             }
         }
-        landed = ok;
     }
-    __syncthreads();
-    if (!landed) return;
+    if (!__syncthreads_and(ok ? 1 : 0)) return;
     const int quads = dim >> 2;
     for (int64_t idx = threadIdx.x; idx < n * quads; idx += blockDim.x) {
         const int64_t i = idx / quads;

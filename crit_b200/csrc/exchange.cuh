@@ -27,16 +27,20 @@ __host__ __device__ __forceinline__ int64_t ex_stride(int64_t floats) { return (
 __device__ __forceinline__ float* ex_slot(uint64_t buffer, int32_t step, int world, int rank, int64_t stride) {
     return reinterpret_cast<float*>(buffer) + EX_FLAG_WORDS + ((int64_t)(step & 1) * world + rank) * stride;
 }
-// Waits (at most wait_ns) until every rank's flag in this rank's own buffer is at `step`; one thread calls it.
-__device__ __forceinline__ bool ex_wait_flags(const int32_t* flags, int world, int32_t step, uint64_t wait_ns) {
+__device__ __forceinline__ int32_t ld_relaxed_sys(const int32_t* p) {
+    int32_t v;
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Waits (at most wait_ns) until ONE rank's flag is at `step`, then fences (acquire, system scope): the threads of a block
+// each wait for one rank, so the flags are polled side by side (acquire loads one after another, by one thread, cost a
+// memory round trip per rank).
+__device__ __forceinline__ bool ex_wait_flag(const int32_t* flag, int32_t step, uint64_t wait_ns) {
     const uint64_t t0 = global_ns();
-    do {
-        bool ok = true;
-        for (int r = 0; r < world; ++r)
-            if (ld_acquire_sys(flags + r) - step < 0) ok = false;
-        if (ok) return true;
-    } while (global_ns() - t0 < wait_ns);
-    return false;
+    bool ok = ld_relaxed_sys(flag) - step >= 0;
+    while (!ok && global_ns() - t0 < wait_ns) ok = ld_relaxed_sys(flag) - step >= 0;
+    __threadfence_system();
+    return ok;
 }
 
 }  // namespace crit_b200

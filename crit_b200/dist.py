@@ -57,15 +57,15 @@ def kv_ranges(context, world, partition=4096):
             for r in range(world)]
 
 
-def chunk_to_fill(positions, kv_heads, blocks, chunk=1024, tile=16):
+def chunk_to_fill(positions, kv_heads, blocks, chunk=1024, tile=16, waves=None):
     """Positions per split for ONE long row of `positions` so that its launch's blocks (splits x kv_heads) fill the
-    device's `blocks` resident blocks in whole waves: the default chunk where the row gives several waves anyway, else
-    the chunk whose splits come to the largest whole number of waves not above what the default gives (at least one).
+    device's `blocks` resident blocks in whole waves: as many waves as the default chunk comes nearest to (at least
+    one), or `waves` when given (a shard of a context takes one: fewer splits to fold before its partial can leave).
     A row's own choice: it changes the split boundaries, so only a caller that always reads the row alone (one long
     context over a KV range) uses it."""
     positions, blocks = max(int(positions), 1), max(int(blocks), 1)
     units = -(-positions // chunk) * kv_heads
-    waves = max(1, round(units / blocks))
+    waves = max(1, round(units / blocks)) if waves is None else max(1, int(waves))
     splits = max(1, waves * blocks // kv_heads)
     return max(tile, -(-(-(-positions // splits)) // tile) * tile)
 
@@ -160,11 +160,11 @@ class ShardMerge:
             return None
         return found
 
-    def attend(self, params, out, lse):
+    def attend(self, params, out, lse, wait=True):
         """The fused step after a decode launch that left every split state in its workspace (crit_b200.attend with
         shards=self passes its parameter block here): fold + push, wait + merge of shards into out [tokens][heads][dim]
-        and lse [tokens][heads].  Device work only, capturable.  Without the peer exchange: the fold into out / lse and
-        merge() over NCCL."""
+        and lse [tokens][heads].  Device work only, capturable.  wait=False: the fold + push alone (a measurement's).
+        Without the peer exchange: the fold into out / lse and merge() over NCCL."""
         import ctypes
         torch = self.torch
         from . import _lib
@@ -185,7 +185,8 @@ class ShardMerge:
         x = self.peer.params
         with torch.cuda.device(out.device):
             _lib.check(lib.crit_b200_merge_push(ctypes.byref(params), ctypes.byref(x), stream), "crit_b200.dist.ShardMerge.attend (push)")
-            _lib.check(lib.crit_b200_wait_merge(ctypes.byref(x), ctypes.byref(m), stream), "crit_b200.dist.ShardMerge.attend (wait)")
+            if wait:
+                _lib.check(lib.crit_b200_wait_merge(ctypes.byref(x), ctypes.byref(m), stream), "crit_b200.dist.ShardMerge.attend (wait)")
         return out, lse
 
     def raise_on_status(self):
