@@ -466,7 +466,7 @@ def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scale
             multipliers=(1.0, 1.0), scale=None, out=None, lse=None, int8_qk=False, fresh=None, flash=False,
             sinks=None, sliding=0, splits=None, workspace=None, derive=None, engine=None):
     """A prompt chunk of one sequence: q [T][heads][dim] at positions position.. (their keys and values written),
-    table [pages] int32 -> out [T][heads][dim] in q's dtype (and lse [T][heads] FP32 when given), causal.  position: an
+    table [pages] int32 (or int64) -> out [T][heads][dim] in q's dtype (and lse [T][heads] FP32 when given), causal.  position: an
     int, or a one-element int64 device tensor read on the device.  engine: None (tcgen05.mma tiles with TMEM accumulators
     for 16-bit pages of 128-wide heads, m16n8k16 tiles otherwise), "mma.sync" or "tcgen05" (refused where not served).
     Reference: paged_kv_attention/__init__.py:1245-1332."""
@@ -480,8 +480,12 @@ def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scale
     if not key_pages.is_contiguous() or not value_pages.is_contiguous():
         raise ValueError("pages are contiguous [slots][kv_heads][dim] storage")
     out = torch.empty_like(q) if out is None else out
-    if q.stride(-1) != 1 or out.stride(-1) != 1 or table.dtype != torch.int32 or not table.is_contiguous():
-        raise ValueError("q and out have contiguous last dimensions, table is contiguous int32")
+    if table.dtype not in (torch.int32, torch.int64) or table.dim() != 1:
+        raise ValueError("table is the sequence's page ids, int32 (read in place) or int64 (converted)")
+    if table.dtype != torch.int32 or not table.is_contiguous():
+        table = table.to(torch.int32).contiguous()       # (the reference's pool hands its tables over as int64 slices)
+    if q.stride(-1) != 1 or out.stride(-1) != 1:
+        raise ValueError("q and out have contiguous last dimensions")
     if torch.is_tensor(position) and (position.dtype != torch.int64 or position.numel() != 1 or not position.is_cuda):
         raise ValueError("a position read on the device is a one-element int64 tensor there")
     p = _lib.PrefillParams()

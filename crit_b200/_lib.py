@@ -86,6 +86,7 @@ SYMBOLS = {
     "crit_b200_shard_wait": (c_int, [POINTER(ExchangeParams), c_void_p]),
     "crit_b200_merge_push": (c_int, [POINTER(AttendParams), POINTER(ExchangeParams), c_void_p]),
     "crit_b200_wait_merge": (c_int, [POINTER(ExchangeParams), POINTER(MergeShardsParams), c_void_p]),
+    "crit_b200_exchange_merge": (c_int, [POINTER(AttendParams), POINTER(ExchangeParams), POINTER(MergeShardsParams), c_void_p]),
     "crit_b200_exchange_bytes": (c_int64, [c_int32, c_int64]),
     "crit_b200_abi_version": (c_int, []),
     "crit_b200_params_size": (c_int, [c_int32]),

@@ -154,8 +154,9 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
 // column past its row's count, and a row that holds no position, send zeros and -inf.  The blocks count themselves on a
 // ticket in this rank's buffer; the last one stores the header, raises this rank's flag in every buffer (system-scope
 // release) and moves the step counter on.  Nothing here waits.
-template <int DV>
-__global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit_b200_attend_params p, const crit_b200_exchange_params x) {
+template <int DV, bool FUSED>
+__global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit_b200_attend_params p, const crit_b200_exchange_params x,
+                                                                      const crit_b200_merge_shards_params shards) {
     constexpr int PER = DV / 32;
     __shared__ float sm[MERGE_WARPS], sl[MERGE_WARPS];
     __shared__ float so[MERGE_WARPS][DV];
@@ -232,6 +233,13 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit
             for (int peer = 0; peer < x.world; ++peer) slots[peer][n * DV + entry] = lse;
         }
     }
+    // the message's header goes with the first block's data
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 32) {
+        for (int peer = 0; peer < x.world; ++peer) {
+            float* header = slots[peer] + n * (DV + 1);
+            header[0] = __int_as_float(x.rank), header[1] = __int_as_float(step), header[2] = __int_as_float((int)n);
+        }
+    }
     // The block's stores are ordered before its ticket by ONE system-scope fence: the barrier makes them visible to
     // thread 0 and its fence is cumulative (a fence per thread would drain the NVLink writes hundreds of times).
     __syncthreads();
@@ -240,14 +248,9 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit
         int32_t* mine = reinterpret_cast<int32_t*>(bases[x.rank]);
         const int done = atomicAdd(mine + EX_TICKET, 1);
         if (done == (int)(gridDim.x * gridDim.y) - 1) {
-            __threadfence();                    // the other blocks' stores, seen through their tickets
+            // every block's stores, seen through its ticket, before the flags: one fence (this thread has no write of its
+            // own in flight), then plain system-scope stores
             mine[EX_TICKET] = 0;
-            for (int peer = 0; peer < x.world; ++peer) {
-                float* header = slots[peer] + n * (DV + 1);
-                header[0] = __int_as_float(x.rank), header[1] = __int_as_float(step), header[2] = __int_as_float((int)n);
-            }
-            // the headers, and everything seen above, before the flags: one fence, then plain system-scope stores (a
-            // release store per rank would drain the writes once per rank)
             __threadfence_system();
             for (int peer = 0; peer < x.world; ++peer) {
                 int32_t* flag = reinterpret_cast<int32_t*>(bases[peer]) + x.rank;
@@ -255,6 +258,50 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit
             }
             *x.step = step;
         }
+    }
+    if constexpr (FUSED) {
+        // The same launch waits for the ranks' messages and merges them: every block takes its own (token, head) out of
+        // this rank's own buffer.  (Only launched where every block is resident at once: a block waits for a flag that
+        // this rank's LAST block raises.)  Thread r waits, bounded, for rank r's flag and checks rank r's header.
+        bool ok = true;
+        const float* own = ex_slot(bases[x.rank], step, x.world, 0, stride);
+        if (threadIdx.x < x.world) {
+            const int rr = threadIdx.x;
+            ok = ex_wait_flag(reinterpret_cast<const int32_t*>(bases[x.rank]) + rr, step, (uint64_t)x.wait_ns);
+            if (!ok) {
+                if (x.status) atomicExch(x.status, 0x800 + x.rank);
+            } else {
+                const float* header = own + rr * stride + n * (DV + 1);
+                if (__float_as_int(header[0]) != rr || __float_as_int(header[1]) != step || __float_as_int(header[2]) != (int)n) {
+                    if (x.status) atomicExch(x.status, 0x900 + rr);
+                    ok = false;
+                }
+            }
+        }
+        if (!__syncthreads_and(ok ? 1 : 0) || !listed) return;
+        float top = -INFINITY;
+        for (int rr = 0; rr < x.world; ++rr) top = fmaxf(top, own[rr * stride + n * DV + entry]);
+        const float sub = top == -INFINITY ? 0.f : top;
+        float total = 0.f;
+        for (int rr = 0; rr < x.world; ++rr) {
+            const float lse = own[rr * stride + n * DV + entry];
+            total += lse == -INFINITY ? 0.f : expf(lse - sub);
+        }
+        const float denom = fmaxf(total, 1e-30f);
+        const float inv = total > 0.f ? 1.f / denom : 0.f;
+        for (int c = threadIdx.x; c < DV; c += MERGE_WARPS * 32) {
+            float o = 0.f;
+            for (int rr = 0; rr < x.world; ++rr) {
+                const float lse = own[rr * stride + n * DV + entry];
+                const float w = lse == -INFINITY ? 0.f : expf(lse - sub);
+                o += w * own[rr * stride + entry * DV + c];
+            }
+            o *= inv;
+            if (shards.out_dtype == CRIT_B200_DTYPE_BF16) ((__nv_bfloat16*)shards.out)[entry * DV + c] = __float2bfloat16_rn(o);
+            else if (shards.out_dtype == CRIT_B200_DTYPE_FP16) ((__half*)shards.out)[entry * DV + c] = __float2half_rn(o);
+            else ((float*)shards.out)[entry * DV + c] = o;
+        }
+        if (threadIdx.x == 0 && shards.lse) shards.lse[entry] = total > 0.f ? sub + logf(denom) : -INFINITY;
     }
 }
 
@@ -554,24 +601,62 @@ namespace crit_b200 {
 int check_exchange(const crit_b200_exchange_params& p, bool with_message);      // exchange.cu
 }
 
-extern "C" __attribute__((visibility("default"))) int crit_b200_merge_push(const crit_b200_attend_params* attend,
-                                                                           const crit_b200_exchange_params* exchange, void* stream) {
-    if (!attend || !exchange) return CRIT_B200_EINVAL;
-    const crit_b200_attend_params p = *attend;
-    const crit_b200_exchange_params x = *exchange;
+template <bool FUSED>
+static int launch_merge_push(const crit_b200_attend_params& p, const crit_b200_exchange_params& x, const crit_b200_merge_shards_params& m,
+                             cudaStream_t s) {
+    const dim3 blocks((unsigned)p.q_heads, (unsigned)(p.n_rows * p.columns));
+    if (p.value_dim == 128) merge_push_kernel<128, FUSED><<<blocks, MERGE_WARPS * 32, 0, s>>>(p, x, m);
+    else if (p.value_dim == 256) merge_push_kernel<256, FUSED><<<blocks, MERGE_WARPS * 32, 0, s>>>(p, x, m);
+    else if (p.value_dim == 64) merge_push_kernel<64, FUSED><<<blocks, MERGE_WARPS * 32, 0, s>>>(p, x, m);
+    else return CRIT_B200_EUNSUPPORTED;
+    CRIT_CHECK_LAUNCH();
+    return 0;
+}
+
+static int check_merge_push(const crit_b200_attend_params& p, const crit_b200_exchange_params& x) {
     if (!(p.flags & CRIT_B200_ATTEND_PARTIALS)) return CRIT_B200_EINVAL;
     int e = check(p);
     if (!e) e = check_exchange(x, false);
     if (e) return e;
     if (x.floats < EX_HEADER + p.value_dim + 1 || (x.floats - EX_HEADER) % (p.value_dim + 1)) return CRIT_B200_EINVAL;
-    const dim3 blocks((unsigned)p.q_heads, (unsigned)(p.n_rows * p.columns));
-    cudaStream_t s = (cudaStream_t)stream;
-    if (p.value_dim == 128) merge_push_kernel<128><<<blocks, MERGE_WARPS * 32, 0, s>>>(p, x);
-    else if (p.value_dim == 256) merge_push_kernel<256><<<blocks, MERGE_WARPS * 32, 0, s>>>(p, x);
-    else if (p.value_dim == 64) merge_push_kernel<64><<<blocks, MERGE_WARPS * 32, 0, s>>>(p, x);
-    else return CRIT_B200_EUNSUPPORTED;
-    CRIT_CHECK_LAUNCH();
     return 0;
+}
+
+extern "C" __attribute__((visibility("default"))) int crit_b200_merge_push(const crit_b200_attend_params* attend,
+                                                                           const crit_b200_exchange_params* exchange, void* stream) {
+    if (!attend || !exchange) return CRIT_B200_EINVAL;
+    const crit_b200_attend_params p = *attend;
+    const crit_b200_exchange_params x = *exchange;
+    if (int e = check_merge_push(p, x)) return e;
+    crit_b200_merge_shards_params none;
+    memset(&none, 0, sizeof none);
+    return launch_merge_push<false>(p, x, none, (cudaStream_t)stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int crit_b200_wait_merge(const crit_b200_exchange_params* exchange,
+                                                                           const crit_b200_merge_shards_params* merge, void* stream);
+
+// Fold + push and wait + merge of shards: one launch where every block of it is resident at once (a block per (token,
+// head) of the step, up to the device's SM count: a block waits for the flag this rank's last block raises), else the two
+// launches crit_b200_merge_push and crit_b200_wait_merge.
+extern "C" __attribute__((visibility("default"))) int crit_b200_exchange_merge(const crit_b200_attend_params* attend,
+                                                                               const crit_b200_exchange_params* exchange,
+                                                                               const crit_b200_merge_shards_params* merge, void* stream) {
+    if (!attend || !exchange || !merge) return CRIT_B200_EINVAL;
+    const crit_b200_attend_params p = *attend;
+    const crit_b200_exchange_params x = *exchange;
+    const crit_b200_merge_shards_params m = *merge;
+    if (int e = check_merge_push(p, x)) return e;
+    if (m.n < 1 || m.dim != p.value_dim || !m.out || m.parts != x.world || x.floats != m.n * (m.dim + 1) + EX_HEADER) return CRIT_B200_EINVAL;
+    if (m.out_dtype != CRIT_B200_DTYPE_BF16 && m.out_dtype != CRIT_B200_DTYPE_FP16 && m.out_dtype != CRIT_B200_DTYPE_FP32) return CRIT_B200_EINVAL;
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 0;
+    const int64_t blocks = (int64_t)p.q_heads * p.n_rows * p.columns;
+    if (blocks <= sms) return launch_merge_push<true>(p, x, m, (cudaStream_t)stream);
+    crit_b200_merge_shards_params none;
+    memset(&none, 0, sizeof none);
+    if (int e = launch_merge_push<false>(p, x, none, (cudaStream_t)stream)) return e;
+    return crit_b200_wait_merge(exchange, merge, stream);
 }
 
 extern "C" __attribute__((visibility("default"))) int crit_b200_attend_plan(int32_t q_heads, int32_t kv_heads, int32_t head_dim,

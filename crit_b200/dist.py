@@ -184,9 +184,11 @@ class ShardMerge:
         m.out_dtype = {torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_FP16, torch.float32: _lib.DTYPE_FP32}[out.dtype]
         x = self.peer.params
         with torch.cuda.device(out.device):
-            _lib.check(lib.crit_b200_merge_push(ctypes.byref(params), ctypes.byref(x), stream), "crit_b200.dist.ShardMerge.attend (push)")
             if wait:
-                _lib.check(lib.crit_b200_wait_merge(ctypes.byref(x), ctypes.byref(m), stream), "crit_b200.dist.ShardMerge.attend (wait)")
+                _lib.check(lib.crit_b200_exchange_merge(ctypes.byref(params), ctypes.byref(x), ctypes.byref(m), stream),
+                           "crit_b200.dist.ShardMerge.attend")
+            else:
+                _lib.check(lib.crit_b200_merge_push(ctypes.byref(params), ctypes.byref(x), stream), "crit_b200.dist.ShardMerge.attend (push)")
         return out, lse
 
     def raise_on_status(self):

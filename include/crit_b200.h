@@ -247,6 +247,11 @@ int64_t crit_b200_exchange_bytes(int32_t world, int64_t floats);
  * (0x900 + sender) writes nothing: the step's output is then not published. */
 int crit_b200_merge_push(const crit_b200_attend_params* attend, const crit_b200_exchange_params* exchange, void* stream);
 int crit_b200_wait_merge(const crit_b200_exchange_params* exchange, const crit_b200_merge_shards_params* merge, void* stream);
+/* Both in one launch where the step is small enough that every block of the launch is resident at once (a block per
+ * (token, head), up to the device's SM count: each block folds and pushes its own pair, waits for the ranks' flags and
+ * merges its own pair out of this rank's buffer), else the two launches above, one after the other. */
+int crit_b200_exchange_merge(const crit_b200_attend_params* attend, const crit_b200_exchange_params* exchange,
+                             const crit_b200_merge_shards_params* merge, void* stream);
 
 /* -- chunked prefill ---------------------------------------------------------------------------------------------
  * Replaces paged_kv_attention.prefill (paged_kv_attention/__init__.py:1245-1332; kernel _kernels.py:610-726) behind

@@ -201,6 +201,20 @@ class EmulatedRanks:
         code = self.lib.crit_b200_merge_push(self.ctypes.byref(attend_params), self.ctypes.byref(self.params[rank]), self._stream())
         assert code == 0, self.lib.crit_b200_error(code)
 
+    def exchange_merge(self, rank, attend_params, out, lse):
+        """Fold + push and wait + merge in one call (one launch where the step's blocks are all resident): only a world
+        of one rank can run it on one GPU, since the wait needs every rank's push."""
+        code = self.lib.crit_b200_exchange_merge(self.ctypes.byref(attend_params), self.ctypes.byref(self.params[rank]),
+                                                 self.ctypes.byref(self._merge_params(out, lse)), self._stream())
+        assert code == 0, self.lib.crit_b200_error(code)
+
+    def _merge_params(self, out, lse):
+        m = self._lib.MergeShardsParams()
+        m.out, m.lse, m.n, m.parts, m.dim = out.data_ptr(), lse.data_ptr(), self.n, self.world, self.dim
+        m.in_dtype = self._lib.DTYPE_FP32
+        m.out_dtype = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[out.dtype]
+        return m
+
     def wait_merge(self, rank, out, lse):
         m = self._lib.MergeShardsParams()
         m.out, m.lse, m.n, m.parts, m.dim = out.data_ptr(), lse.data_ptr(), self.n, self.world, self.dim

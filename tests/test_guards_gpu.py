@@ -261,3 +261,32 @@ def test_the_fused_exchange_merges_two_ranks_and_refuses_missing_and_stale_messa
     ranks.wait_merge(0, *merged[0])
     torch.cuda.synchronize()
     assert int(ranks.status[0].item()) == 0x900 + 1 and bool((merged[0][0] == 7.0).all())
+
+
+@pytest.mark.parametrize("tokens,columns", [(1, 1), (3, 3), (40, 1)])
+def test_the_one_launch_exchange_of_a_single_rank_equals_the_plain_attention(pk, tokens, columns):
+    """crit_b200_exchange_merge with a world of one rank: the launch folds and stores into its own buffer, waits for its own
+    flag (raised by its last block) and merges the one part: the output is the ordinary launch pair's within FP32 rounding.
+    3 tokens x 8 heads run as one launch (24 blocks), 40 x 8 = 320 blocks pass the SM count and run as the two launches."""
+    from helpers import Cache, EmulatedRanks, attend_params, queries
+    binding, lib = _lib()
+    rows_n = tokens // columns
+    cache = Cache("bf16", 2, 128, 128, 16, [700 + 13 * r for r in range(rows_n)], spare=4, seed=3)
+    q = queries(tokens, 8, 128, 2)
+    rows, starts = list(range(rows_n)), [r * columns for r in range(rows_n)]
+    firsts = [700 + 13 * r - columns for r in range(rows_n)]
+    want_lse = torch.empty(tokens, 8, device="cuda")
+    want = cache.attend(q, rows, starts, firsts, columns, lse=want_lse, chunk=128)
+    ranks = EmulatedRanks(1, tokens, 8, 128, wait_ms=50)
+    splits = pk.parts_for(cache.tables.shape[1] * 16, 128)
+    space = torch.empty(pk.workspace_floats(tokens, 8, splits, 128), device="cuda")
+    scratch = torch.zeros(tokens, 8, 128, dtype=torch.bfloat16, device="cuda")
+    p, held = attend_params(cache, q, scratch, None, rows, starts, firsts, columns, 128, workspace=space, flags=32)
+    for _ in range(3):                       # step after step: the slots alternate, the ticket comes back to zero
+        got, got_lse = torch.full_like(want, 7.0), torch.full_like(want_lse, 7.0)
+        assert lib.crit_b200_decode(ctypes.byref(p), _stream()) == 0
+        ranks.exchange_merge(0, p, got, got_lse)
+        torch.cuda.synchronize()
+        assert int(ranks.status[0].item()) == 0
+        torch.testing.assert_close(got.float(), want.float(), atol=1e-2, rtol=1e-2)
+        torch.testing.assert_close(got_lse, want_lse, atol=1e-4, rtol=1e-5)
