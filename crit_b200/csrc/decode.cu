@@ -148,12 +148,13 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
 
 // The fold of a rank's splits, sent: what merge_kernel computes for a (token, head), normalised, goes as FP32 into slot
 // [step & 1][rank] of EVERY rank's exchange buffer (peer stores over NVLink; this rank's own buffer too) instead of into
-// `out`: a message is [tokens x heads][DV] outputs, [tokens x heads] log-sum-exps (natural log), then (rank, step,
-// tokens x heads) as int32 bits.  Block = (window token, query head); warp w folds splits w, w + 8, ... and the eight
-// warps' states are folded in warp order, so a row of a hundred splits costs a dozen dependent loads, not a hundred.  A
-// column past its row's count, and a row that holds no position, send zeros and -inf.  The blocks count themselves on a
-// ticket in this rank's buffer; the last one stores the header, raises this rank's flag in every buffer (system-scope
-// release) and moves the step counter on.  Nothing here waits.
+// `out`: a message is [tokens x heads][DV] outputs then [tokens x heads] log-sum-exps (natural log), every float stored
+// with the step beside it (exchange.cuh).  Block = (window token, query head); warp w folds splits w, w + 8, ... and the
+// eight warps' states are folded in warp order, so a row of a hundred splits costs a dozen dependent loads, not a
+// hundred.  A column past its row's count, and a row that holds no position, send zeros and -inf.  Nothing waits for a
+// peer here.  FUSED: the same block then gathers its own (token, head) from every rank's message in this rank's own buffer
+// (a bounded wait per float) and writes the merge of shards: the whole exchange in one launch, its latency one NVLink
+// write.  The blocks count themselves out on a ticket in this rank's buffer; the last one moves the step counter on.
 template <int DV, bool FUSED>
 __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit_b200_attend_params p, const crit_b200_exchange_params x,
                                                                       const crit_b200_merge_shards_params shards) {
@@ -161,14 +162,12 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit
     __shared__ float sm[MERGE_WARPS], sl[MERGE_WARPS];
     __shared__ float so[MERGE_WARPS][DV];
     __shared__ float* slots[EX_MAX_WORLD];          // this rank's slot of the step in every rank's buffer
-    __shared__ uint64_t bases[EX_MAX_WORLD];        // every rank's buffer (read once: the array lives in global memory)
+    __shared__ float parts_lse[EX_MAX_WORLD];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int32_t step = *x.step + 1;
-    const int64_t stride = ex_stride(x.floats);
-    if (threadIdx.x < x.world) {
-        bases[threadIdx.x] = x.peers[threadIdx.x];
-        slots[threadIdx.x] = ex_slot(bases[threadIdx.x], step, x.world, x.rank, stride);
-    }
+    const int64_t stride = 2 * ex_stride(x.floats);
+    const uint64_t own_base = x.peers[x.rank];
+    if (threadIdx.x < x.world) slots[threadIdx.x] = ex_slot(x.peers[threadIdx.x], step, x.world, x.rank, stride);
     const int64_t n = (x.floats - EX_HEADER) / (DV + 1);           // (token, head) pairs of a message
     const int head = blockIdx.x;
     const int r = blockIdx.y / p.columns, col = blockIdx.y - r * p.columns;
@@ -226,82 +225,69 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit
 #pragma unroll
             for (int w = 0; w < MERGE_WARPS; ++w) o += so[w][c] * ex2(sm[w] - sub);
             o *= inv;
-            for (int peer = 0; peer < x.world; ++peer) slots[peer][entry * DV + c] = o;
+            for (int peer = 0; peer < x.world; ++peer) ll_store(slots[peer], entry * DV + c, o, step);
         }
         if (threadIdx.x == 0) {
             const float lse = total > 0.f ? top * LN2 + logf(total) : -INFINITY;
-            for (int peer = 0; peer < x.world; ++peer) slots[peer][n * DV + entry] = lse;
-        }
-    }
-    // the message's header goes with the first block's data
-    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 32) {
-        for (int peer = 0; peer < x.world; ++peer) {
-            float* header = slots[peer] + n * (DV + 1);
-            header[0] = __int_as_float(x.rank), header[1] = __int_as_float(step), header[2] = __int_as_float((int)n);
-        }
-    }
-    // The block's stores are ordered before its ticket by ONE system-scope fence: the barrier makes them visible to
-    // thread 0 and its fence is cumulative (a fence per thread would drain the NVLink writes hundreds of times).
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        int32_t* mine = reinterpret_cast<int32_t*>(bases[x.rank]);
-        const int done = atomicAdd(mine + EX_TICKET, 1);
-        if (done == (int)(gridDim.x * gridDim.y) - 1) {
-            // every block's stores, seen through its ticket, before the flags: one fence (this thread has no write of its
-            // own in flight), then plain system-scope stores
-            mine[EX_TICKET] = 0;
-            __threadfence_system();
-            for (int peer = 0; peer < x.world; ++peer) {
-                int32_t* flag = reinterpret_cast<int32_t*>(bases[peer]) + x.rank;
-                asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
-            }
-            *x.step = step;
+            for (int peer = 0; peer < x.world; ++peer) ll_store(slots[peer], n * DV + entry, lse, step);
         }
     }
     if constexpr (FUSED) {
-        // The same launch waits for the ranks' messages and merges them: every block takes its own (token, head) out of
-        // this rank's own buffer.  (Only launched where every block is resident at once: a block waits for a flag that
-        // this rank's LAST block raises.)  Thread r waits, bounded, for rank r's flag and checks rank r's header.
+        // this block's (token, head) out of every rank's message in this rank's own buffer: the log-sum-exps first (one
+        // thread), then thread c takes column c of every rank; nothing of the pair is written unless all of it arrived
+        constexpr int MINE = (DV + MERGE_WARPS * 32 - 1) / (MERGE_WARPS * 32);
+        const float* own = ex_slot(own_base, step, x.world, 0, stride);
         bool ok = true;
-        const float* own = ex_slot(bases[x.rank], step, x.world, 0, stride);
-        if (threadIdx.x < x.world) {
-            const int rr = threadIdx.x;
-            ok = ex_wait_flag(reinterpret_cast<const int32_t*>(bases[x.rank]) + rr, step, (uint64_t)x.wait_ns);
-            if (!ok) {
-                if (x.status) atomicExch(x.status, 0x800 + x.rank);
-            } else {
-                const float* header = own + rr * stride + n * (DV + 1);
-                if (__float_as_int(header[0]) != rr || __float_as_int(header[1]) != step || __float_as_int(header[2]) != (int)n) {
-                    if (x.status) atomicExch(x.status, 0x900 + rr);
-                    ok = false;
+        if (listed && threadIdx.x == 0) {
+            float found[EX_MAX_WORLD];
+            ok = ll_gather(own, stride, x.world, n * DV + entry, step, (uint64_t)x.wait_ns, found);
+            for (int rr = 0; rr < x.world; ++rr) parts_lse[rr] = ok ? found[rr] : -INFINITY;
+        }
+        ok = __syncthreads_and(ok ? 1 : 0) != 0;
+        float mine[MINE], total = 0.f, sub = 0.f, denom = 1.f;
+        if (ok && listed) {
+            float top = -INFINITY;
+            for (int rr = 0; rr < x.world; ++rr) top = fmaxf(top, parts_lse[rr]);
+            sub = top == -INFINITY ? 0.f : top;
+            for (int rr = 0; rr < x.world; ++rr) total += parts_lse[rr] == -INFINITY ? 0.f : expf(parts_lse[rr] - sub);
+            denom = fmaxf(total, 1e-30f);
+            const float inv = total > 0.f ? 1.f / denom : 0.f;
+#pragma unroll
+            for (int k = 0; k < MINE; ++k) {
+                const int c = threadIdx.x + k * MERGE_WARPS * 32;
+                mine[k] = 0.f;
+                if (c < DV) {
+                    float found[EX_MAX_WORLD];
+                    ok = ll_gather(own, stride, x.world, entry * DV + c, step, (uint64_t)x.wait_ns, found) && ok;
+                    float sum = 0.f;
+                    for (int rr = 0; rr < x.world; ++rr)
+                        sum += (parts_lse[rr] == -INFINITY ? 0.f : expf(parts_lse[rr] - sub)) * (ok ? found[rr] : 0.f);
+                    mine[k] = sum * inv;
                 }
             }
         }
-        if (!__syncthreads_and(ok ? 1 : 0) || !listed) return;
-        float top = -INFINITY;
-        for (int rr = 0; rr < x.world; ++rr) top = fmaxf(top, own[rr * stride + n * DV + entry]);
-        const float sub = top == -INFINITY ? 0.f : top;
-        float total = 0.f;
-        for (int rr = 0; rr < x.world; ++rr) {
-            const float lse = own[rr * stride + n * DV + entry];
-            total += lse == -INFINITY ? 0.f : expf(lse - sub);
-        }
-        const float denom = fmaxf(total, 1e-30f);
-        const float inv = total > 0.f ? 1.f / denom : 0.f;
-        for (int c = threadIdx.x; c < DV; c += MERGE_WARPS * 32) {
-            float o = 0.f;
-            for (int rr = 0; rr < x.world; ++rr) {
-                const float lse = own[rr * stride + n * DV + entry];
-                const float w = lse == -INFINITY ? 0.f : expf(lse - sub);
-                o += w * own[rr * stride + entry * DV + c];
+        ok = __syncthreads_and(ok ? 1 : 0) != 0;
+        if (ok && listed) {
+#pragma unroll
+            for (int k = 0; k < MINE; ++k) {
+                const int c = threadIdx.x + k * MERGE_WARPS * 32;
+                if (c >= DV) continue;
+                if (shards.out_dtype == CRIT_B200_DTYPE_BF16) ((__nv_bfloat16*)shards.out)[entry * DV + c] = __float2bfloat16_rn(mine[k]);
+                else if (shards.out_dtype == CRIT_B200_DTYPE_FP16) ((__half*)shards.out)[entry * DV + c] = __float2half_rn(mine[k]);
+                else ((float*)shards.out)[entry * DV + c] = mine[k];
             }
-            o *= inv;
-            if (shards.out_dtype == CRIT_B200_DTYPE_BF16) ((__nv_bfloat16*)shards.out)[entry * DV + c] = __float2bfloat16_rn(o);
-            else if (shards.out_dtype == CRIT_B200_DTYPE_FP16) ((__half*)shards.out)[entry * DV + c] = __float2half_rn(o);
-            else ((float*)shards.out)[entry * DV + c] = o;
+            if (threadIdx.x == 0 && shards.lse) shards.lse[entry] = total > 0.f ? sub + logf(denom) : -INFINITY;
         }
-        if (threadIdx.x == 0 && shards.lse) shards.lse[entry] = total > 0.f ? sub + logf(denom) : -INFINITY;
+        if (!ok && threadIdx.x == 0 && x.status) atomicExch(x.status, 0x800 + x.rank);
+    }
+    // the step counter moves on when every block has read it: the last block out does it
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int32_t* ticket = reinterpret_cast<int32_t*>(own_base) + EX_TICKET;
+        if (atomicAdd(ticket, 1) == (int)(gridDim.x * gridDim.y) - 1) {
+            *ticket = 0;
+            *x.step = step;
+        }
     }
 }
 
@@ -651,8 +637,10 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_exchange_merge(c
     if (m.out_dtype != CRIT_B200_DTYPE_BF16 && m.out_dtype != CRIT_B200_DTYPE_FP16 && m.out_dtype != CRIT_B200_DTYPE_FP32) return CRIT_B200_EINVAL;
     int device = 0, sms = 0;
     if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess) sms = 0;
+    // one launch while every block of it is resident at once (4 blocks of 256 threads an SM at the least): a block
+    // waits for the same block of the other ranks, which must not sit behind blocks that wait themselves
     const int64_t blocks = (int64_t)p.q_heads * p.n_rows * p.columns;
-    if (blocks <= sms) return launch_merge_push<true>(p, x, m, (cudaStream_t)stream);
+    if (blocks <= 4 * (int64_t)sms) return launch_merge_push<true>(p, x, m, (cudaStream_t)stream);
     crit_b200_merge_shards_params none;
     memset(&none, 0, sizeof none);
     if (int e = launch_merge_push<false>(p, x, none, (cudaStream_t)stream)) return e;

@@ -13,9 +13,11 @@
 // the wire in the same launches: crit_b200_merge_push (decode.cu) folds this rank's split-K partials and stores each
 // (token, head)'s result straight into the peers' slots, and crit_b200_wait_merge here merges the ranks' partials out
 // of this rank's own buffer into the step's output as soon as the flags are up.
+// The fused pair stores every float with its step beside it in one 8-byte store (exchange.cuh): a float is valid when its
+// step is the reader's, so its exchange needs no flag, no fence and no header, and costs one NVLink write.
 // A push never waits, so no rank's progress depends on another rank's kernel having started; a wait that runs out sets
-// the status word (0x800 + rank) and writes nothing, and so does a message whose header is not the step's (0x900 + the
-// sender): the host reads the status and does not publish.  After either, the exchange is out of step: the buffers are
+// the status word (0x800 + rank) and writes nothing of the pair concerned (the plain wait also refuses a message whose
+// header is not the step's: 0x900 + the sender): the host reads the status and does not publish.  After either, the exchange is out of step: the buffers are
 // zeroed and the ranks synchronised again before the next step (slot [step & 1] of rank y is written again at step + 2,
 // which rank x starts only after its own wait of step + 1 saw y's push of step + 1, which y launched after its wait of
 // `step` had read the slot; that chain holds only while every wait succeeds).
@@ -74,56 +76,58 @@ __global__ void __launch_bounds__(1024) shard_wait_kernel(const crit_b200_exchan
     }
 }
 
-// The merge of the ranks' partials, read where the peers stored them.  A message is [n][dim] outputs, [n] log-sum-exps,
-// then (rank, step, n) as the bits of three int32.  One block: thread r < world waits for rank r's flag and checks its header; then thread t takes
-// 4-float pieces t, t + 1024, ... of the n x dim outputs: top = max lse over the ranks, w = exp(lse - top) (0 for -inf),
-// out = sum w o / sum w in rank order, lse = top + log(sum w); a (token, head) no rank saw gets zeros and -inf.
+// The merge of the ranks' partials, read where the peers stored them (the second launch of the fused exchange where one
+// launch does not hold the step: crit_b200_exchange_merge).  A message is [n][dim] outputs then [n] log-sum-exps, every
+// float with its step beside it (exchange.cuh).  Block = one (token, head): thread 0 gathers the ranks' log-sum-exps
+// (a bounded wait per float), thread c column c of every rank: top = max lse over the ranks, w = exp(lse - top) (0 for
+// -inf), out = sum w o / sum w in rank order, lse = top + log(sum w); a (token, head) no rank saw gets zeros and -inf.
+// A float that never arrives: the status word (0x800 + rank), and nothing of its pair is written.
 // Reference: inference/partitioned-attention/plugin.py:52-64.
 template <typename TOUT>
-__global__ void __launch_bounds__(1024) wait_merge_kernel(const crit_b200_exchange_params p, const crit_b200_merge_shards_params m) {
+__global__ void __launch_bounds__(256) wait_merge_kernel(const crit_b200_exchange_params p, const crit_b200_merge_shards_params m) {
+    __shared__ float parts_lse[EX_MAX_WORLD];
     const int32_t step = *p.step;
-    const int64_t stride = ex_stride(p.floats);
-    const uint64_t own = p.peers[p.rank];
-    const float* slot = ex_slot(own, step, p.world, 0, stride);
-    const int64_t n = m.n;
+    const int64_t stride = 2 * ex_stride(p.floats);
+    const float* own = ex_slot(p.peers[p.rank], step, p.world, 0, stride);
+    const int64_t n = m.n, entry = blockIdx.x;
     const int dim = m.dim;
     bool ok = true;
-    if (threadIdx.x < p.world) {            // thread r waits for rank r's flag, then checks rank r's header
-        const int r = threadIdx.x;
-        ok = ex_wait_flag(reinterpret_cast<const int32_t*>(own) + r, step, (uint64_t)p.wait_ns);
-        if (!ok) {
-            if (p.status) atomicExch(p.status, 0x800 + p.rank);
-        } else {
-            const float* header = slot + r * stride + n * (dim + 1);
-            if (__float_as_int(header[0]) != r || __float_as_int(header[1]) != step || __float_as_int(header[2]) != (int)n) {
-                if (p.status) atomicExch(p.status, 0x900 + r);
-                ok = false;
+    if (threadIdx.x == 0) {
+        float found[EX_MAX_WORLD];
+        ok = ll_gather(own, stride, p.world, n * dim + entry, step, (uint64_t)p.wait_ns, found);
+        for (int r = 0; r < p.world; ++r) parts_lse[r] = ok ? found[r] : -INFINITY;
+    }
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    float mine[4] = {0.f, 0.f, 0.f, 0.f}, total = 0.f, sub = 0.f, denom = 1.f;
+    if (ok) {
+        float top = -INFINITY;
+        for (int r = 0; r < p.world; ++r) top = fmaxf(top, parts_lse[r]);
+        sub = top == -INFINITY ? 0.f : top;
+        for (int r = 0; r < p.world; ++r) total += parts_lse[r] == -INFINITY ? 0.f : expf(parts_lse[r] - sub);
+        denom = fmaxf(total, 1e-30f);
+        const float inv = total > 0.f ? 1.f / denom : 0.f;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = threadIdx.x + 256 * k;
+            if (c < dim) {
+                float found[EX_MAX_WORLD];
+                ok = ll_gather(own, stride, p.world, entry * dim + c, step, (uint64_t)p.wait_ns, found) && ok;
+                float sum = 0.f;
+                for (int r = 0; r < p.world; ++r) sum += (parts_lse[r] == -INFINITY ? 0.f : expf(parts_lse[r] - sub)) * (ok ? found[r] : 0.f);
+                mine[k] = sum * inv;
             }
         }
     }
-    if (!__syncthreads_and(ok ? 1 : 0)) return;
-    const int quads = dim >> 2;
-    for (int64_t idx = threadIdx.x; idx < n * quads; idx += blockDim.x) {
-        const int64_t i = idx / quads;
-        const int c4 = (int)(idx - i * quads);
-        float top = -INFINITY;
-        for (int r = 0; r < p.world; ++r) top = fmaxf(top, slot[r * stride + n * dim + i]);
-        const float sub = top == -INFINITY ? 0.f : top;
-        float total = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < p.world; ++r) {
-            const float l = slot[r * stride + n * dim + i];
-            const float w = l == -INFINITY ? 0.f : expf(l - sub);
-            total += w;
-            const float4 v = *reinterpret_cast<const float4*>(slot + r * stride + i * dim + c4 * 4);
-            acc.x += w * v.x, acc.y += w * v.y, acc.z += w * v.z, acc.w += w * v.w;
+    ok = __syncthreads_and(ok ? 1 : 0) != 0;
+    if (ok) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = threadIdx.x + 256 * k;
+            if (c < dim) ((TOUT*)m.out)[entry * dim + c] = from_float<TOUT>(mine[k]);
         }
-        const float denom = fmaxf(total, 1e-30f);
-        const float inv = total > 0.f ? 1.f / denom : 0.f;
-        TOUT* dst = (TOUT*)m.out + i * dim + c4 * 4;
-        dst[0] = from_float<TOUT>(acc.x * inv), dst[1] = from_float<TOUT>(acc.y * inv);
-        dst[2] = from_float<TOUT>(acc.z * inv), dst[3] = from_float<TOUT>(acc.w * inv);
-        if (c4 == 0 && m.lse) m.lse[i] = total > 0.f ? sub + logf(denom) : -INFINITY;
+        if (threadIdx.x == 0 && m.lse) m.lse[entry] = total > 0.f ? sub + logf(denom) : -INFINITY;
+    } else if (threadIdx.x == 0 && p.status) {
+        atomicExch(p.status, 0x800 + p.rank);
     }
 }
 
@@ -165,13 +169,14 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_wait_merge(const
     const crit_b200_exchange_params p = *exchange;
     const crit_b200_merge_shards_params m = *merge;
     if (int e = check_exchange(p, false)) return e;
-    if (m.n < 1 || m.dim < 4 || m.dim % 4 || !m.out || m.parts != p.world) return CRIT_B200_EINVAL;
+    if (m.n < 1 || m.n > 0x7fffffff || m.dim < 1 || m.dim > 1024 || !m.out || m.parts != p.world) return CRIT_B200_EINVAL;
     if (p.floats != m.n * (m.dim + 1) + EX_HEADER) return CRIT_B200_EINVAL;
     cudaStream_t s = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)m.n;
     switch (m.out_dtype) {
-        case CRIT_B200_DTYPE_BF16: wait_merge_kernel<__nv_bfloat16><<<1, 1024, 0, s>>>(p, m); break;
-        case CRIT_B200_DTYPE_FP16: wait_merge_kernel<__half><<<1, 1024, 0, s>>>(p, m); break;
-        case CRIT_B200_DTYPE_FP32: wait_merge_kernel<float><<<1, 1024, 0, s>>>(p, m); break;
+        case CRIT_B200_DTYPE_BF16: wait_merge_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(p, m); break;
+        case CRIT_B200_DTYPE_FP16: wait_merge_kernel<__half><<<blocks, 256, 0, s>>>(p, m); break;
+        case CRIT_B200_DTYPE_FP32: wait_merge_kernel<float><<<blocks, 256, 0, s>>>(p, m); break;
         default: return CRIT_B200_EINVAL;
     }
     CRIT_CHECK_LAUNCH();
@@ -180,5 +185,6 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_wait_merge(const
 
 extern "C" __attribute__((visibility("default"))) int64_t crit_b200_exchange_bytes(int32_t world, int64_t floats) {
     if (world < 1 || floats < 1) return CRIT_B200_EINVAL;
-    return (EX_FLAG_WORDS + 2 * (int64_t)world * ex_stride(floats)) * 4;
+    // two alternating slots a rank, each wide enough for the fused exchange's {value, step} pairs (twice the floats)
+    return (EX_FLAG_WORDS + 2 * (int64_t)world * 2 * ex_stride(floats)) * 4;
 }

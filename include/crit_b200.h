@@ -236,15 +236,18 @@ int crit_b200_shard_push(const crit_b200_exchange_params* params, void* stream);
 int crit_b200_shard_wait(const crit_b200_exchange_params* params, void* stream);
 int64_t crit_b200_exchange_bytes(int32_t world, int64_t floats);
 
-/* The same exchange with the arithmetic either side of it in the same two launches (what one decode step of a context
- * sharded by KV range runs after crit_b200_decode with CRIT_B200_ATTEND_PARTIALS): crit_b200_merge_push folds this
- * rank's splits (the fold of crit_b200_merge) and stores each (token, head)'s normalised output and log-sum-exp as FP32
- * straight into every rank's buffer, then the header and the flag; crit_b200_wait_merge waits (bounded) for the `world`
- * messages in this rank's own buffer, checks their headers (sender, step, shape) and writes the merge of shards to
- * merge->out / merge->lse (merge->outs and ->lses are not read; parts = world).  A message is tokens x q_heads x
- * (value_dim + 1) floats + 3: exchange->floats says so, and the attend rows' tokens cover 0 .. tokens - 1.
- * exchange->mine and ->gathered are not used.  A wait that runs out (status 0x800 + rank) or a foreign header
- * (0x900 + sender) writes nothing: the step's output is then not published. */
+/* The same exchange with the arithmetic either side of it (what one decode step of a context sharded by KV range runs
+ * after crit_b200_decode with CRIT_B200_ATTEND_PARTIALS): crit_b200_merge_push folds this rank's splits (the fold of
+ * crit_b200_merge) and stores each (token, head)'s normalised output and log-sum-exp as FP32 straight into every rank's
+ * buffer, every float in one 8-byte store with the step beside it, so a reader that finds its step has the value: no
+ * flag, fence or header is involved and the exchange costs one NVLink write.  crit_b200_wait_merge gathers, for every
+ * (token, head), the `world` ranks' floats from this rank's own buffer (a wait of at most wait_ns per float) and writes
+ * the merge of shards to merge->out / merge->lse (merge->outs and ->lses are not read; parts = world).  A message is
+ * tokens x q_heads x (value_dim + 1) floats + 3: exchange->floats says so, and the attend rows' tokens cover
+ * 0 .. tokens - 1.  exchange->mine and ->gathered are not used; the buffers are crit_b200_exchange_bytes(world, floats)
+ * bytes as for the plain pair.  A float that never arrives (a rank that stayed away, or one that ran a step ahead and
+ * stored over the slot) sets the status word (0x800 + rank) and nothing of its (token, head) is written: the step's
+ * output is then not published. */
 int crit_b200_merge_push(const crit_b200_attend_params* attend, const crit_b200_exchange_params* exchange, void* stream);
 int crit_b200_wait_merge(const crit_b200_exchange_params* exchange, const crit_b200_merge_shards_params* merge, void* stream);
 /* Both in one launch where the step is small enough that every block of the launch is resident at once (a block per

@@ -201,7 +201,8 @@ def test_split_states_kept_in_the_workspace_fold_to_the_ordinary_bits(pk, kind, 
 def test_the_fused_exchange_merges_two_ranks_and_refuses_missing_and_stale_messages(pk):
     """Two ranks on one GPU, each over its half of one context: fold + push (crit_b200_merge_push), wait + merge
     (crit_b200_wait_merge).  The merged attention equals the attention over the whole; a rank whose partner never pushed
-    gets 0x800 after its bounded wait and its output untouched; a message carrying another step's header gets 0x900."""
+    gets 0x800 after its bounded wait and its output untouched; so does a rank that finds a later step's floats where it
+    waits for its own step's (every float carries its step)."""
     from helpers import Cache, EmulatedRanks, assert_attention_close, attend_params, queries
     binding, lib = _lib()
     whole = Cache("bf16", 2, 128, 128, 16, [1000], seed=7)
@@ -253,14 +254,14 @@ def test_the_fused_exchange_merges_two_ranks_and_refuses_missing_and_stale_messa
         assert all(int(s.item()) == 0 for s in ranks.status) and torch.equal(merged[0][0], merged[1][0])
         torch.testing.assert_close(merged[0][0].float(), want.float(), atol=2e-2, rtol=2e-2)
     # a message of another step: rank 1 pushes three times (its counter runs ahead and comes round to the same slot),
-    # rank 0 once; rank 0 finds rank 1's flag high enough but, in the slot of its own step, the header of step + 2
+    # rank 0 once; in the slot of its own step rank 0 finds floats stamped step + 2: not its step's, so they never "arrive"
     for _ in range(3):
         decode_and_push(1)
     decode_and_push(0)
     merged[0][0].fill_(7.0)
     ranks.wait_merge(0, *merged[0])
     torch.cuda.synchronize()
-    assert int(ranks.status[0].item()) == 0x900 + 1 and bool((merged[0][0] == 7.0).all())
+    assert int(ranks.status[0].item()) == 0x800 and bool((merged[0][0] == 7.0).all())
 
 
 @pytest.mark.parametrize("tokens,columns", [(1, 1), (3, 3), (40, 1)])
