@@ -39,8 +39,7 @@ def build(force=False, verbose=False):
     procs = []
     for name in SOURCES:
         obj = LIBRARY.parent / (name + ".o")
-        extra = os.environ.get("CRIT_B200_NVCC_FLAGS", "").split()        # e.g. -DCRIT_DT_PROFILE
-        cmd = [nvcc(), *FLAGS, *extra, *(["-Xptxas", "-v"] if verbose else []), "-c", str(HERE / "csrc" / name), "-o", str(obj)]
+        cmd = [nvcc(), *FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-c", str(HERE / "csrc" / name), "-o", str(obj)]
         procs.append((name, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
         objects.append(str(obj))
     for name, proc in procs:

@@ -6,6 +6,7 @@
 
 #include "decode_kernel.cuh"
 #include "decode_tc.cuh"
+#include "decode_sw.cuh"
 #include "exchange.cuh"
 #include "tensor_map.cuh"
 
@@ -334,7 +335,7 @@ static int page_class(int kind, int page_dtype) {
 // 8-row tiles of query rows a block holds: as many as a row's columns times the group's heads need, up to 4 (32 rows),
 // 2 where the value accumulators of more would not fit the registers (256-wide values).
 static int row_tiles(int rows, int dv) {
-    const int most = dv <= 128 ? 4 : 2;         // (two 16-row tiles instead of one of 32 measured 519 us against 502)
+    const int most = dv <= 128 ? 4 : 2;
     const int need = rows <= 8 ? 1 : (rows <= 16 ? 2 : 4);
     return need < most ? need : most;
 }
@@ -476,7 +477,35 @@ static int launch_decode_tc(const crit_b200_attend_params& p, cudaStream_t s) {
     return 0;
 }
 
+static int launch_decode_sw(const crit_b200_attend_params& p, cudaStream_t s) {
+    CUtensorMap kmap, vmap;
+    if (!page_map(&kmap, p.key_pages, 2, p.head_dim, p.kv_heads, p.slots) ||
+        !page_map(&vmap, p.value_pages, 2, p.value_dim, p.kv_heads, p.slots))
+        return CRIT_B200_EUNSUPPORTED;
+    const int rows = p.columns * (p.q_heads / p.kv_heads);
+    typedef void (*sw_fn)(const crit_b200_attend_params, const CUtensorMap, const CUtensorMap);
+    const int nrg = rows <= 8 ? 0 : (rows <= 16 ? 1 : 2);
+    static const sw_fn fns[3][3] = {
+        {decode_sw_kernel<8, 0>, decode_sw_kernel<8, 1>, decode_sw_kernel<8, 2>},
+        {decode_sw_kernel<16, 0>, decode_sw_kernel<16, 1>, decode_sw_kernel<16, 2>},
+        {decode_sw_kernel<32, 0>, decode_sw_kernel<32, 1>, decode_sw_kernel<32, 2>}};
+    const sw_fn fn = fns[nrg][scale_mode(p.kind)];
+    const int smem = nrg == 0 ? SwCfg<8>::SMEM : (nrg == 1 ? SwCfg<16>::SMEM : SwCfg<32>::SMEM);
+    cudaError_t ce = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (ce != cudaSuccess) return (int)ce;
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
+        return CRIT_B200_EUNSUPPORTED;
+    const int64_t most = (int64_t)p.max_splits * p.kv_heads * p.n_rows;        // units the launch can have
+    const unsigned blocks = (unsigned)(most < 2 * sms ? most : 2 * sms);       // two persistent blocks per SM
+    fn<<<blocks, SW_THREADS, smem, s>>>(p, kmap, vmap);
+    CRIT_CHECK_LAUNCH();
+    return 0;
+}
+
 static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
+    if (p.flags & CRIT_B200_ATTEND_TCGEN05T) return tc_serves(p) && p.n_rows <= SW_MAX_LIST ? launch_decode_sw(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05) return tc_serves(p) ? launch_decode_tc(p, s) : CRIT_B200_EUNSUPPORTED;
     // The library's choice: windows of several columns over E4M3 pages go to the tcgen05 kernel where it serves them
     // (the page bytes feed the tensor cores as they are; the m16n8k16 kernel converts every byte in registers and holds

@@ -38,9 +38,6 @@
 
 #include <cuda.h>
 #include <cuda_fp16.h>
-#ifdef CRIT_DT_PROFILE
-#include <cstdio>
-#endif
 
 #include "tcgen05.cuh"
 
@@ -124,21 +121,6 @@ __device__ __forceinline__ void split_e4m3x2(float a, float b, uint32_t& hi, uin
     if (LOSCALE != 1) rest = __hmul2(rest, __float2half2_rn((float)LOSCALE));
     lo = f16x2_to_e4m3x2(*reinterpret_cast<uint32_t*>(&rest));
 }
-
-// With CRIT_DT_PROFILE defined, block 0 prints the cycles each role spent in each kind of wait (a tuning aid).
-#ifdef CRIT_DT_PROFILE
-#define DT_TIMED(slot, expr) ([&] { const long long t0_ = clock64(); const bool r_ = (expr); prof[slot] += clock64() - t0_; return r_; }())
-#define DT_PROF_BEGIN long long prof[16] = {0}; const long long prof_t0 = clock64(); long long prof_mark = prof_t0;
-#define DT_PHASE(slot) { const long long now_ = clock64(); prof[slot] += now_ - prof_mark; prof_mark = now_; }
-#define DT_COUNT(slot) prof[slot] += 1;
-#define DT_PROF_END(name) if (blockIdx.x == 0 && lane == 0) printf("%s warp %d: total %lld waits %lld %lld %lld %lld %lld %lld %lld phases %lld %lld %lld %lld %lld %lld %lld count %lld\n", name, warp, clock64() - prof_t0, prof[0], prof[1], prof[2], prof[3], prof[4], prof[5], prof[6], prof[7], prof[8], prof[9], prof[10], prof[11], prof[12], prof[13], prof[15]);
-#else
-#define DT_TIMED(slot, expr) (expr)
-#define DT_PROF_BEGIN
-#define DT_PHASE(slot)
-#define DT_COUNT(slot)
-#define DT_PROF_END(name)
-#endif
 
 // A bounded wait that also gives up when another thread of the block already did.  BACKOFF: nanoseconds to sleep
 // between polls (the roles that wait long share their issue slots with the softmax warps; those poll without a pause).
@@ -365,7 +347,6 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
         fetch_pages(w1, pg1);
         int t = 0;
         bool ok = true;
-        DT_PROF_BEGIN
         while (w0.live && ok) {
             fetch_scales(w1, pg1, ks1, vs1);
             fetch_pages(w2, pg2);
@@ -383,14 +364,14 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 const int stage = t % DT_STAGES;
                 const uint32_t free_parity = (uint32_t)((t / DT_STAGES) & 1) ^ 1u;
                 unsigned char* st = stages + stage * DT_STAGE;
-                ok = DT_TIMED(0, dt_wait<100>(bar(DT_KEMPTY + stage), free_parity, abort_flag));
+                ok = (dt_wait<100>(bar(DT_KEMPTY + stage), free_parity, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 if (lane == 0) mbar_expect_tx(bar(DT_KFULL + stage), (uint32_t)DT_KV_BYTES);
                 __syncwarp();
                 if (lane < 8) tma_load_3d(smem_addr(st) + lane * 2048, &kmap, 0, w0.u.h, slot0, bar(DT_KFULL + stage));
                 // the values, and with them the tile's scales (read by the softmax, which ends before the values are free)
-                ok = DT_TIMED(1, dt_wait<100>(bar(DT_VEMPTY + stage), free_parity, abort_flag));
+                ok = (dt_wait<100>(bar(DT_VEMPTY + stage), free_parity, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 float* scs = reinterpret_cast<float*>(st + 2 * DT_KV_BYTES);
@@ -407,7 +388,6 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
             for (int j = 0; j < DT_NB; ++j) pg0[j] = pg1[j], ks0[j] = ks1[j], vs0[j] = vs1[j], pg1[j] = pg2[j];
             w0 = w1, w1 = w2, w2.next_unit(p, rows);
         }
-        DT_PROF_END("producer")
         if (!ok) {              // leaving early: the copies in flight land first (bounded)
             where = 0x410;
             for (int tt = t > DT_STAGES ? t - DT_STAGES : 0; tt <= t; ++tt) {
@@ -423,10 +403,9 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
         const int qt = lane & 3;
         bool ok = true, have_prev = false, prev_acc = false;
         int prev_t = 0;
-        DT_PROF_BEGIN
         auto issue_pv = [&]() {             // O (+)= P V of tile prev_t
             const int pstage = prev_t % DT_STAGES;
-            ok = DT_TIMED(3, dt_wait<32>(bar(DT_PFULL), (uint32_t)prev_t & 1u, abort_flag)) &&
+            ok = (dt_wait<32>(bar(DT_PFULL), (uint32_t)prev_t & 1u, abort_flag)) &&
                  dt_wait<32>(bar(DT_VFULL + pstage), (uint32_t)(prev_t / DT_STAGES) & 1u, abort_flag);
             ok = __all_sync(FULLMASK, ok);
             if (!ok) return;
@@ -532,7 +511,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                     if (!ok) break;
                 }
                 if (t > 0) {
-                    ok = DT_TIMED(0, dt_wait<32>(bar(DT_SFULL), (uint32_t)(t - 1) & 1u, abort_flag) &&
+                    ok = (dt_wait<32>(bar(DT_SFULL), (uint32_t)(t - 1) & 1u, abort_flag) &&
                                          dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag));
                     ok = __all_sync(FULLMASK, ok);
                     if (!ok) break;
@@ -543,14 +522,12 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                     after.next_unit(p, rows);
                     load_q(after);
                 }
-                DT_PHASE(7)
             }
-            ok = DT_TIMED(1, dt_wait<32>(bar(DT_KFULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
-            ok = ok && DT_TIMED(2, dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag));
+            ok = (dt_wait<32>(bar(DT_KFULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
+            ok = ok && (dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag));
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             tc_fence_after();
-            DT_PHASE(8)
             if (lane == 0) {
                 const uint32_t qa = smem_addr(qbuf), ka = smem_addr(stages + stage * DT_STAGE);
 #pragma unroll
@@ -560,15 +537,12 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 umma_commit(bar(DT_KEMPTY + stage));
             }
             __syncwarp();
-            DT_PHASE(9)
             if (have_prev) issue_pv();
-            DT_PHASE(10)
             have_prev = true, prev_t = t, prev_acc = w.i > 0;
             w.next(p, rows);
             ++t;
         }
         if (ok && have_prev) issue_pv();
-        DT_PROF_END("mma")
         if (!ok) where = 0x420;
     } else {
         // -- softmax: thread = TMEM lane 32 * warp + lane.  A lane group is 16 lanes: lanes 0-7 hold the hi terms of 8
@@ -594,12 +568,11 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
         DtWalk w;
         w.begin(p, rows);
         int t = 0;
-        DT_PROF_BEGIN
         while (w.live && ok) {
             const int k = w.k;
             DtWalk after = w;                   // the unit after this one, found while this one's first scores are on their way
             after.next_unit(p, rows);
-            ok = DT_TIMED(0, dt_wait(bar(DT_QFULL), (uint32_t)k & 1u, abort_flag));
+            ok = (dt_wait(bar(DT_QFULL), (uint32_t)k & 1u, abort_flag));
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             const float a_r = qfac[(k & 1) * 32 + r];
@@ -610,7 +583,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
             for (int i = 0; i < w.u.ntiles; ++i, ++t) {
                 const int stage = t % DT_STAGES;
                 const int tile_pos = (int)w.u.begin + i * DT_N;
-                ok = DT_TIMED(1, dt_wait(bar(DT_SFULL), (uint32_t)t & 1u, abort_flag) &&
+                ok = (dt_wait(bar(DT_SFULL), (uint32_t)t & 1u, abort_flag) &&
                                      dt_wait(bar(DT_VFULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
@@ -694,7 +667,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 m_run = top;
 
                 // the P tile is free (and the outputs settled) once the second product of the tile before has landed
-                ok = DT_TIMED(2, dt_wait(bar(DT_PVDONE), (uint32_t)(t & 1) ^ 1u, abort_flag));
+                ok = (dt_wait(bar(DT_PVDONE), (uint32_t)(t & 1) ^ 1u, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 float l_tile = 0.f;
@@ -737,7 +710,6 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
 
                 if (__any_sync(FULLMASK, rescale)) {
                     // a maximum moved: the warp brings its output lanes to the new reference
-                    DT_COUNT(15)
                     tc_fence_after();
                     dt_rescale(tmem + lane_base + DT_O, alpha);
                 }
@@ -746,11 +718,10 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 mbar_arrive(bar(DT_PFULL));
             }
             if (!ok) break;
-            DT_PHASE(7)
 
             // -- the unit's result: wait for its last second product, fold the replicas, write ------------------------------
             const int tl = t - 1;
-            ok = DT_TIMED(4, dt_wait(bar(DT_PVDONE), (uint32_t)tl & 1u, abort_flag));
+            ok = (dt_wait(bar(DT_PVDONE), (uint32_t)tl & 1u, abort_flag));
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             tc_fence_after();
@@ -774,7 +745,6 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 const float l_row = l_run + __shfl_xor_sync(FULLMASK, l_run, 8);
                 if (!second) fm[entry] = m_run, fl[entry] = l_row;
             }
-            DT_PHASE(8)
             const bool whole = w.u.nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS);
             const int prow_first = p.offsets ? p.offsets[w.u.r] - p.offsets[0] : w.u.r * p.columns;
             const bool fits = whole || (p.workspace && w.u.split < p.max_splits && prow_first >= 0 && prow_first + w.u.count <= p.partial_rows);
@@ -788,7 +758,7 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                             make_float4(keep[4 * f4], keep[4 * f4 + 1], keep[4 * f4 + 2], keep[4 * f4 + 3]);
                 }
                 mbar_arrive(bar(DT_FOLD_A));
-                ok = DT_TIMED(5, dt_wait(bar(DT_FOLD_A), (uint32_t)pass, abort_flag));
+                ok = (dt_wait(bar(DT_FOLD_A), (uint32_t)pass, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
 #pragma unroll
@@ -837,20 +807,17 @@ decode_tc_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                     }
                 }
                 mbar_arrive(bar(DT_FOLD_B));
-                ok = DT_TIMED(6, dt_wait(bar(DT_FOLD_B), (uint32_t)pass, abort_flag));
+                ok = (dt_wait(bar(DT_FOLD_B), (uint32_t)pass, abort_flag));
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
             }
             if (!ok) break;
-            DT_PHASE(9)
             // the fold used the P tile: this thread's row back to zeros (the columns it never writes stay zero)
 #pragma unroll
             for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(pbuf + prow * 128 + c * 16) = make_uint4(0, 0, 0, 0);
             __syncwarp();               // a row's other lane writes into this row too
             w = after;
-            DT_PHASE(10)
         }
-        DT_PROF_END("softmax")
         if (!ok) where = 0x440;
     }
 

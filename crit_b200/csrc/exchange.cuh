@@ -27,7 +27,7 @@ __host__ __device__ __forceinline__ int64_t ex_stride(int64_t floats) { return (
 // The fused exchange sends every float with its step beside it, as one 8-byte store: {value, step}.  An 8-byte store
 // reaches a peer's memory whole, so a reader that finds the step it waits for has the value too: no fence orders data
 // before a flag, and nothing waits for a write to be acknowledged across NVLink (a system-scope fence behind peer stores
-// measured 5 us).  A slot of the fused exchange is therefore twice a message's floats; the flags and headers of the plain
+// waits for exactly that, for microseconds).  A slot of the fused exchange is therefore twice a message's floats; the flags and headers of the plain
 // exchange are not used by it.
 __device__ __forceinline__ void ll_store(float* slot, int64_t idx, float v, int32_t step) {
     asm volatile("st.volatile.global.v2.b32 [%0], {%1, %2};" ::"l"(slot + 2 * idx), "r"(__float_as_uint(v)), "r"(step) : "memory");

@@ -123,6 +123,9 @@ int crit_b200_slots(const crit_b200_slots_params* params, void* stream);
                                        probabilities as two E4M3 terms each) or CRIT_B200_EUNSUPPORTED: E4M3 pages of
                                        128-wide heads, columns x group heads <= 32, chunk a multiple of 128, slots set */
 #define CRIT_B200_ATTEND_MMA_SYNC 16 /* the m16n8k16 kernel even where the tcgen05 kernel serves the launch */
+#define CRIT_B200_ATTEND_TCGEN05T 64 /* the tcgen05 kernel with the operands swapped (the key and value tiles on the MMA's 128
+                                        rows, the query rows on its columns) or CRIT_B200_EUNSUPPORTED: the same launches
+                                        CRIT_B200_ATTEND_TCGEN05 takes */
 #define CRIT_B200_ATTEND_PARTIALS 32 /* every row's split states go to the workspace, a row of one split too (the first launch
                                         writes nothing to out / lse): what crit_b200_merge_push sends, or what
                                         crit_b200_merge folds */

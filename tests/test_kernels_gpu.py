@@ -151,10 +151,14 @@ def test_windows_match_the_oracle(pk, kind, hq, hkv, d, dv, page):
 
 # The tcgen05 engine: E4M3 page bytes straight into the tensor cores; the queries and probabilities enter as two E4M3
 # terms each (an error below 2^-8 of each value, like bf16's own rounding), so the same bounds hold.
+TC_ENGINES = ["tcgen05", "tcgen05t"]       # the query rows on the MMA's rows (replicated), or on its columns (operands swapped)
+
+
+@pytest.mark.parametrize("engine", TC_ENGINES)
 @pytest.mark.parametrize("kind", ["fp8", "fp8:row", "fp8:page"])
 @pytest.mark.parametrize("hq,hkv", [(8, 2), (56, 8), (40, 8), (4, 4), (16, 1)])
 @pytest.mark.parametrize("page,chunk", [(16, 128), (48, 256), (16, 1024)])
-def test_windows_on_tcgen05_tiles_match_the_oracle(pk, kind, hq, hkv, page, chunk):
+def test_windows_on_tcgen05_tiles_match_the_oracle(pk, kind, hq, hkv, page, chunk, engine):
     from helpers import Cache, assert_attention_close, queries
     cache = Cache(kind, hkv, 128, 128, page, [130, 64, 1, 517, 1300])
     G = hq // hkv
@@ -164,63 +168,65 @@ def test_windows_on_tcgen05_tiles_match_the_oracle(pk, kind, hq, hkv, page, chun
     rows, starts = [0, 1, 2, 3, 4], [0, 5, 10, 15, 20]
     q = queries(25, hq, 128, 3)
     lse = torch.full((25, hq), 7.0, device="cuda")
-    out = cache.attend(q, rows, starts, firsts, cols, counts=counts, lse=lse, chunk=chunk, engine="tcgen05")
+    out = cache.attend(q, rows, starts, firsts, cols, counts=counts, lse=lse, chunk=chunk, engine=engine)
     assert pk.status() == 0
     want, want_lse = cache.oracle(q, rows, starts, firsts, cols, counts=counts)
     tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
     assert_attention_close(out, lse, want, want_lse, tokens)
 
 
+@pytest.mark.parametrize("engine", TC_ENGINES)
 @pytest.mark.parametrize("kind", ["fp8:page", "fp8:row"])
-def test_tcgen05_tiles_with_outliers_and_long_rows(pk, kind):
+def test_tcgen05_tiles_with_outliers_and_long_rows(pk, kind, engine):
     from helpers import Cache, assert_attention_close, queries
     cache = Cache(kind, 2, 128, 128, 16, [1000, 37, 16, 2049, 5000], outliers=True)
     q = queries(5, 16, 128, 9)      # bf16 queries split into two E4M3 terms exactly; fp16 ones keep 8 of their 11 bits
     rows, starts, firsts = [0, 1, 2, 3, 4], [0, 1, 2, 3, 4], [999, 36, 15, 2048, 4999]
     lse = torch.empty(5, 16, device="cuda")
-    out = cache.attend(q, rows, starts, firsts, 1, lse=lse, chunk=1024, engine="tcgen05")
+    out = cache.attend(q, rows, starts, firsts, 1, lse=lse, chunk=1024, engine=engine)
     assert pk.status() == 0
     want, want_lse = cache.oracle(q, rows, starts, firsts, 1)
     assert_attention_close(out, lse, want, want_lse, [0, 1, 2, 3, 4], rel=2.0 ** -7)
 
 
-def test_tcgen05_tiles_edge_cases(pk):
+@pytest.mark.parametrize("engine", TC_ENGINES)
+def test_tcgen05_tiles_edge_cases(pk, engine):
     """The tcgen05 engine on the edges the m16n8k16 engine is held to: a NaN query stays in its own token, rows with no
     columns and counts past the columns, FP16 queries, packed partial rows, and a row alone against the row in a batch."""
     from helpers import Cache, assert_attention_close, queries
     cache = Cache("fp8:page", 2, 128, 128, 16, [200, 1300, 40], spare=8)
     q = queries(12, 8, 128, 2)
     rows, starts, firsts = [0, 1, 2], [0, 4, 8], [196, 1296, 36]
-    clean = cache.attend(q, rows, starts, firsts, 4, engine="tcgen05")
+    clean = cache.attend(q, rows, starts, firsts, 4, engine=engine)
     q2 = q.clone()
     q2[5, 3, 7] = float("nan")
-    got = cache.attend(q2, rows, starts, firsts, 4, engine="tcgen05")
+    got = cache.attend(q2, rows, starts, firsts, 4, engine=engine)
     assert torch.isnan(got[5, 3]).all()
     keep = torch.ones(12, 8, dtype=torch.bool)
     keep[5, 3] = False
     assert torch.equal(got.cpu()[keep], clean.cpu()[keep])
     # a row without columns writes nothing; a count past the columns reads as the columns
     marked = torch.full_like(clean, 7.0)
-    some = cache.attend(q, rows, starts, firsts, 4, counts=[4, 0, 9], out=marked, engine="tcgen05")
+    some = cache.attend(q, rows, starts, firsts, 4, counts=[4, 0, 9], out=marked, engine=engine)
     assert torch.equal(some[0:4], clean[0:4]) and torch.equal(some[8:12], clean[8:12]) and bool((some[4:8] == 7.0).all())
     # FP16 queries keep 8 of their 11 significant bits in the split: inside the bounds
     qh = queries(12, 8, 128, 4, torch.float16)
     cache16 = Cache("fp8:row", 2, 128, 128, 16, [200, 1300, 40], spare=8)
     lse = torch.empty(12, 8, device="cuda")
-    out = cache16.attend(qh, rows, starts, firsts, 4, lse=lse, engine="tcgen05")
+    out = cache16.attend(qh, rows, starts, firsts, 4, lse=lse, engine=engine)
     want, want_lse = cache16.oracle(qh, rows, starts, firsts, 4)
     assert_attention_close(out, lse, want, want_lse, list(range(12)))
     # packed partial rows (offsets) fold to the same bits as padded ones
     offsets = torch.tensor([0, 2, 3], dtype=torch.int32, device="cuda")
     splits = pk.parts_for(cache.tables.shape[1] * 16, 256)
     space = torch.empty(pk.workspace_floats(7, 8, splits, 128), device="cuda")
-    padded = cache.attend(q, rows, starts, firsts, 4, counts=[2, 1, 4], chunk=256, engine="tcgen05")
+    padded = cache.attend(q, rows, starts, firsts, 4, counts=[2, 1, 4], chunk=256, engine=engine)
     packed = cache.attend(q, rows, starts, firsts, 4, counts=[2, 1, 4], offsets=offsets, tokens=7, workspace=space, chunk=256,
-                          engine="tcgen05")
+                          engine=engine)
     for start, count in zip(starts, [2, 1, 4]):
         assert torch.equal(packed[start:start + count], padded[start:start + count])
     # a row alone and in a batch of the same columns: the same unit, the same bits
-    alone = cache.attend(q[4:8], [1], [0], [1296], 4, engine="tcgen05")
+    alone = cache.attend(q[4:8], [1], [0], [1296], 4, engine=engine)
     assert torch.equal(alone, clean[4:8])
     assert pk.status() == 0
 
