@@ -141,7 +141,7 @@ def chunk_for(head_dim, value_dim, heads, kv_heads, page, kind="bf16", engine=No
     m16n8k16 kernel, never by the batch, so a column's bits are the same alone and in any window.  Launches the tcgen05
     kernel takes (engine "tcgen05", or the library's choice for windows of several columns over E4M3 pages) use splits
     of 2,048: a unit's fold of its lane replicas is paid once per split."""
-    if engine in ("tcgen05", "tcgen05t") or (engine is None and columns > 1 and
+    if engine in ("tcgen05", "tcgen05t", "tcgen05p") or (engine is None and columns > 1 and
                                tcgen05_serves(kind, head_dim, value_dim, heads, kv_heads, columns, 2 * DEFAULT_CHUNK)):
         return 2 * DEFAULT_CHUNK
     return DEFAULT_CHUNK
@@ -380,7 +380,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     if partitions:
         chunk = max(chunk, -(-positions // int(partitions)))
     chunk = -(-chunk // TILE) * TILE
-    splits = parts_for(positions, chunk)
+    splits = parts_for(positions, chunk) * (2 if engine == "tcgen05p" else 1)       # that engine: a split's head and tail
     partial_rows = R * columns if offsets is None else int(tokens)
     out = torch.empty(T, hq, dv, dtype=q.dtype, device=device) if out is None else out
     if out.dtype != q.dtype or out.stride(-1) != 1:
@@ -408,7 +408,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     if staging not in (None, "tma", "cp.async"):
         raise ValueError("staging is None, tma or cp.async")
     p.flags = ({None: 0, "cp.async": 1, "tma": 2}[staging] | (4 if persistent else 0) |
-               {None: 0, "tcgen05": 8, "mma.sync": 16, "tcgen05t": 64}[engine] | (32 if shards is not None else 0))
+               {None: 0, "tcgen05": 8, "mma.sync": 16, "tcgen05t": 64, "tcgen05p": 128}[engine] | (32 if shards is not None else 0))
     p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])

@@ -7,12 +7,20 @@
 #include "decode_kernel.cuh"
 #include "decode_tc.cuh"
 #include "decode_sw.cuh"
+#include "decode_ph.cuh"
 #include "exchange.cuh"
 #include "tensor_map.cuh"
 
 namespace crit_b200 {
 
 constexpr int MERGE_WARPS = 8;
+
+// States a row of L positions has in the workspace: one a split, or two (a split's head and tail; m = -inf marks one
+// that holds nothing, and the folds pass it over) after a launch that deals tiles out evenly.
+__device__ __forceinline__ int states_of(const crit_b200_attend_params& p, int64_t L) {
+    const int n = (int)((L + p.chunk - 1) / p.chunk);
+    return (p.flags & CRIT_B200_ATTEND_TCGEN05P) ? 2 * n : n;
+}
 
 // The fold of a row's splits in split order (warp w takes splits w, w + 8, ...; the eight warps' states are folded in
 // warp order).  Block = (window token, query head).  m is in base-2 units, o and l are relative to it.
@@ -25,7 +33,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     count = count > p.columns ? p.columns : count;
     if (col >= count) return;
     const int64_t L = p.firsts[r] + count;
-    const int nsplit = (int)((L + p.chunk - 1) / p.chunk);
+    const int nsplit = states_of(p, L);
     if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS))) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int DV = p.value_dim, per = DV >> 5;
@@ -43,6 +51,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     for (int s = warp; s < nsplit; s += MERGE_WARPS) {
         const float ms = pm[base + s], ls = pl[base + s];
+        if (ms == -INFINITY) continue;
         const float* o = p.workspace + (base + s) * DV + lane * per;
         float v[8];
 #pragma unroll
@@ -98,7 +107,7 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
     count = count > p.columns ? p.columns : count;
     if (col >= count) return;
     const int64_t L = p.firsts[r] + count;
-    const int nsplit = (int)((L + p.chunk - 1) / p.chunk);
+    const int nsplit = states_of(p, L);
     if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS))) return;
     const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
     if (nsplit > p.max_splits || prow < 0 || prow >= p.partial_rows) {      // a plan too small for this row: nothing is read
@@ -119,6 +128,7 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
     for (int i = 0; i < PER; ++i) acc[i] = 0.f;
 #pragma unroll 4
     for (int s = 0; s < nsplit; ++s) {
+        if (pm[base + s] == -INFINITY) continue;
         const float w = ex2(pm[base + s] - sub);
         total += pl[base + s] * w;
         const float* o = p.workspace + (base + s) * DV + lane * PER;
@@ -175,7 +185,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit
     int count = p.counts ? p.counts[r] : p.columns;
     count = count > p.columns ? p.columns : count;
     const int64_t L = p.firsts[r] + (count > 0 ? count : 0);
-    const int nsplit = count > 0 ? (int)((L + p.chunk - 1) / p.chunk) : 0;
+    const int nsplit = count > 0 ? states_of(p, L) : 0;
     const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
     const int64_t entry = (int64_t)(p.starts[r] + col) * p.q_heads + head;
     const bool listed = entry >= 0 && entry < n;
@@ -191,6 +201,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit
 #pragma unroll 4
         for (int s = warp; s < nsplit; s += MERGE_WARPS) {
             const float ms = pm[base + s], ls = pl[base + s];
+            if (ms == -INFINITY) continue;
             const float* o = p.workspace + (base + s) * DV + lane * PER;
             float v[PER];
 #pragma unroll
@@ -504,7 +515,42 @@ static int launch_decode_sw(const crit_b200_attend_params& p, cudaStream_t s) {
     return 0;
 }
 
+// Whether the whole-page-rows tcgen05 kernel serves a launch: E4M3 pages of 128-wide heads, 8 kv heads, at most 8 query
+// rows a kv head (columns x heads of a group), splits of whole 16-position tiles, scales the bulk copies can take.
+static bool ph_serves(const crit_b200_attend_params& p) {
+    if (page_class(p.kind, p.page_dtype) != 2) return false;
+    if (p.head_dim != DT_D || p.value_dim != DT_D || p.kv_heads != PH_HEADS) return false;
+    if (p.columns * (p.q_heads / p.kv_heads) > 8) return false;
+    if (p.chunk % PH_TILE || p.chunk > DT_MAX_CHUNK) return false;
+    if (p.slots < 16 || p.slots > 0x7fffffffLL) return false;
+    if (p.n_rows > PH_MAX_LIST || !p.workspace || p.max_splits < 2) return false;
+    if (scale_mode(p.kind) != 0 && (!aligned(p.key_scales, 16) || !aligned(p.value_scales, 16))) return false;
+    return true;
+}
+
+static int launch_decode_ph(const crit_b200_attend_params& p, cudaStream_t s) {
+    CUtensorMap kmap, vmap;
+    if (!page_rows_map(&kmap, p.key_pages, p.head_dim, p.kv_heads, p.slots) ||
+        !page_rows_map(&vmap, p.value_pages, p.value_dim, p.kv_heads, p.slots))
+        return CRIT_B200_EUNSUPPORTED;
+    typedef void (*ph_fn)(const crit_b200_attend_params, const CUtensorMap, const CUtensorMap);
+    static const ph_fn fns[3] = {decode_ph_kernel<0>, decode_ph_kernel<1>, decode_ph_kernel<2>};
+    const ph_fn fn = fns[scale_mode(p.kind)];
+    cudaError_t ce = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, PH_SMEM);
+    if (ce != cudaSuccess) return (int)ce;
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
+        return CRIT_B200_EUNSUPPORTED;
+    const int64_t most = (int64_t)((p.max_splits + 1) / 2) * p.n_rows;         // splits the launch can have: a block holds one at least
+    const unsigned blocks = (unsigned)(most < 2 * sms ? most : 2 * sms);       // two persistent blocks per SM
+    fn<<<blocks, PH_THREADS, PH_SMEM, s>>>(p, kmap, vmap);
+    CRIT_CHECK_LAUNCH();
+    return 0;
+}
+
 static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
+    if (p.flags & CRIT_B200_ATTEND_TCGEN05P) return ph_serves(p) ? launch_decode_ph(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05T) return tc_serves(p) && p.n_rows <= SW_MAX_LIST ? launch_decode_sw(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05) return tc_serves(p) ? launch_decode_tc(p, s) : CRIT_B200_EUNSUPPORTED;
     // The library's choice: windows of several columns over E4M3 pages go to the tcgen05 kernel where it serves them

@@ -35,23 +35,24 @@ constexpr int SW_MAX_LIST = 128;            // window rows a launch lists its wo
 constexpr uint32_t SW_COLUMNS = 256;        // TMEM: scores buffer 0 at 0, buffer 1 at 64, outputs at 128 (up to 64 each)
 constexpr uint32_t SW_S1 = 64, SW_O = 128;
 
-// shared memory (after the 1 KB alignment): Q^T (N rows of 128 bytes) | P^T x 2 (the same, two buffers) | stages | small.
+// shared memory (after the 1 KB alignment): Q^T x 2 (N rows of 128 bytes, by the unit's parity) | P^T x 2 (the same, by the
+// tile's parity) | stages | small.
 // A decode unit (8 rows) has small operands and takes three stages; the wider ones two: two blocks an SM either way.
 template <int NR>
 struct SwCfg {
     static constexpr int N = 2 * NR;
     static constexpr int OPER = N * 128;
     static constexpr int STAGES = NR == 8 ? 3 : 2;
-    static constexpr int OFF_Q = 0, OFF_P = OPER, OFF_STAGES = 3 * OPER;
+    static constexpr int OFF_Q = 0, OFF_P = 2 * OPER, OFF_STAGES = 4 * OPER;
     static constexpr int OFF_SMALL = OFF_STAGES + STAGES * DT_STAGE;
     static constexpr int SMALL_QFAC = 0;                             // [2][32] floats: the rows' score factors, by the unit's parity
-    static constexpr int SMALL_MREF = 256;                           // [32] floats: the rows' references (the same in every thread)
-    static constexpr int SMALL_ROWMAX = 384;                         // [4 warps][32] floats: a tile's row maxima; the unit's row sums
-    static constexpr int SMALL_BARS = 896;                           // 24 mbarriers
+    static constexpr int SMALL_MREF = 256;                           // [2][32] floats: the rows' references, current and last
+    static constexpr int SMALL_ROWMAX = 512;                         // [4 warps][32] floats: a tile's row maxima; the unit's row sums
+    static constexpr int SMALL_BARS = 1024;                          // 24 mbarriers
     static constexpr int SMALL_TMEM = SMALL_BARS + 24 * 8;
     static constexpr int SMALL_ABORT = SMALL_TMEM + 4;
     static constexpr int SMALL_VOTES = SMALL_ABORT + 4;              // three ints: the softmax threads' votes, by the tile modulo 3
-    static constexpr int SMALL_LIST = 1152;                          // unit_first [SW_MAX_LIST + 1] ints (padded)
+    static constexpr int SMALL_LIST = 1280;                          // unit_first [SW_MAX_LIST + 1] ints (padded)
     static constexpr int SMALL_COUNT = SMALL_LIST + (SW_MAX_LIST + 4) * 4;
     static constexpr int SMALL_START = SMALL_COUNT + SW_MAX_LIST * 4;
     static constexpr int SMALL_ROW = SMALL_START + SW_MAX_LIST * 4;
@@ -61,9 +62,9 @@ struct SwCfg {
 };
 
 // mbarriers: stage s of keys / values full and empty; scores buffer b full / free; P^T buffer b full / its second product
-// done; the unit's queries; the softmax threads' vote and meeting
+// done; the queries of an even / odd unit; the softmax threads' vote and meeting
 enum { SW_KFULL = 0, SW_VFULL = 3, SW_KEMPTY = 6, SW_VEMPTY = 9, SW_SFULL = 12, SW_SFREE = 14, SW_PFULL = 16, SW_PVDONE = 18,
-       SW_QFULL = 20, SW_VOTE = 21, SW_MEET = 22 };
+       SW_QFULL = 20, SW_VOTE = 22, SW_MEET = 23 };
 
 // kind::f8f6f4 instruction descriptor, E4M3 x E4M3 -> F32, with either operand K-major (0) or MN-major (1).
 __device__ __forceinline__ uint32_t idesc_f8_majors(bool a_mn_major, bool b_mn_major, int M, int N) {
@@ -169,13 +170,14 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
             mbar_init(bar(SW_SFULL + b), 1), mbar_init(bar(SW_SFREE + b), 128);
             mbar_init(bar(SW_PFULL + b), 128), mbar_init(bar(SW_PVDONE + b), 1);
         }
-        mbar_init(bar(SW_QFULL), 32);
+        mbar_init(bar(SW_QFULL), 32), mbar_init(bar(SW_QFULL + 1), 32);
         mbar_init(bar(SW_VOTE), 128), mbar_init(bar(SW_MEET), 128);
         *abort_flag = 0;
         for (int v = 0; v < 3; ++v) reinterpret_cast<volatile int*>(small + C::SMALL_VOTES)[v] = 0;
         mbar_init_fence();
     }
-    for (int idx = tid; idx < 3 * C::OPER / 16; idx += SW_THREADS) reinterpret_cast<uint4*>(qbuf)[idx] = make_uint4(0, 0, 0, 0);
+    if (tid < 32) mref[tid] = -INFINITY;
+    for (int idx = tid; idx < 4 * C::OPER / 16; idx += SW_THREADS) reinterpret_cast<uint4*>(qbuf)[idx] = make_uint4(0, 0, 0, 0);
     for (int rr = tid; rr < p.n_rows; rr += SW_THREADS) {
         int cnt = p.counts ? p.counts[rr] : p.columns;
         cnt = cnt > p.columns ? p.columns : (cnt < 0 ? 0 : cnt);
@@ -344,6 +346,7 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
             }
         };
         auto store_q = [&](int k) {
+            unsigned char* qdst = qbuf + (k & 1) * C::OPER;
 #pragma unroll
             for (int ps = 0; ps < NR / 8; ++ps) {
                 const int r = ps * 8 + (lane >> 2);
@@ -382,48 +385,37 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const int chunk = 2 * qt + c;
-                    *reinterpret_cast<uint4*>(qbuf + row_hi * 128 + ((chunk ^ (row_hi & 7)) << 4)) =
+                    *reinterpret_cast<uint4*>(qdst + row_hi * 128 + ((chunk ^ (row_hi & 7)) << 4)) =
                         make_uint4(hi[4 * c], hi[4 * c + 1], hi[4 * c + 2], hi[4 * c + 3]);
-                    *reinterpret_cast<uint4*>(qbuf + row_lo * 128 + ((chunk ^ (row_lo & 7)) << 4)) =
+                    *reinterpret_cast<uint4*>(qdst + row_lo * 128 + ((chunk ^ (row_lo & 7)) << 4)) =
                         make_uint4(lo[4 * c], lo[4 * c + 1], lo[4 * c + 2], lo[4 * c + 3]);
                 }
                 if (qt == 0) qfac[(k & 1) * 32 + r] = down * sl2;
             }
             fence_proxy_async();
-            mbar_arrive(bar(SW_QFULL));
+            mbar_arrive(bar(SW_QFULL + (k & 1)));
             __syncwarp();
         };
-        DtWalk w;
+        // The queries run a unit ahead of the products: unit k's sit in buffer k & 1 when its first product is issued, and
+        // unit k + 1's are written over unit k - 1's right after unit k's first tile is under way (by then the second
+        // product of unit k - 1's last tile has been issued, which waited for its probabilities: every product that read
+        // that buffer has completed and the softmax threads are done with its factors); unit k + 2's leave global memory.
+        DtWalk w, ahead;
         w.begin(p, rows);
         load_q(w);
+        if (w.live) store_q(0);
+        ahead = w, ahead.next_unit(p, rows);
+        load_q(ahead);
         int t = 0;
         while (w.live && ok) {
             const int stage = t % SW_STAGES, sb = t & 1;
-            if (w.i == 0) {
-                // A new unit: the last unit's final second product first (its epilogue waits for it), then this unit's
-                // queries over the last one's, once the last scores product that read them has completed.
-                if (have_prev) {
-                    issue_pv();
-                    have_prev = false;
-                    if (!ok) break;
-                }
-                if (t > 0) {
-                    ok = dt_wait<32>(bar(SW_SFULL + ((t - 1) & 1)), (uint32_t)((t - 1) >> 1) & 1u, abort_flag);
-                    ok = __all_sync(FULLMASK, ok);
-                    if (!ok) break;
-                }
-                store_q(w.k);
-                DtWalk after = w;           // the next unit's queries start their way from global memory now
-                after.next_unit(p, rows);
-                load_q(after);
-            }
             ok = dt_wait<32>(bar(SW_KFULL + stage), (uint32_t)(t / SW_STAGES) & 1u, abort_flag) &&
                  dt_wait<32>(bar(SW_SFREE + sb), (uint32_t)((t >> 1) & 1) ^ 1u, abort_flag);
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             tc_fence_after();
             if (lane == 0) {
-                const uint32_t qa = smem_addr(qbuf), ka = smem_addr(stages + stage * DT_STAGE);
+                const uint32_t qa = smem_addr(qbuf + (w.k & 1) * C::OPER), ka = smem_addr(stages + stage * DT_STAGE);
 #pragma unroll
                 for (int kk = 0; kk < DT_D / 32; ++kk)
                     umma_f8(tmem + (sb ? SW_S1 : 0u), smem_desc_sw128(ka + kk * 32, 0, 1024), smem_desc_sw128(qa + kk * 32, 0, 1024),
@@ -433,6 +425,12 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
             }
             __syncwarp();
             if (have_prev) issue_pv();
+            if (!ok) break;
+            if (w.i == 0) {
+                if (ahead.live) store_q(ahead.k);
+                ahead.next_unit(p, rows);
+                load_q(ahead);
+            }
             have_prev = true, prev_t = t, prev_acc = w.i > 0;
             w.next(p, rows);
             ++t;
@@ -490,11 +488,13 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
         DtWalk w;
         w.begin(p, rows);
         int t = 0;
+        int mb = 0;             // which of the two reference arrays is current (every thread toggles it at the same points)
         while (w.live && ok) {
             const int k = w.k;
             DtWalk after = w;
             after.next_unit(p, rows);
-            ok = dt_wait(bar(SW_QFULL), (uint32_t)k & 1u, abort_flag);
+            const int prow_first = p.offsets ? p.offsets[w.u.r] - p.offsets[0] : w.u.r * p.columns;
+            ok = dt_wait(bar(SW_QFULL + (k & 1)), (uint32_t)(k >> 1) & 1u, abort_flag);
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             const int rows_live = w.u.count * G;                 // the unit's query rows (row r: column r / G)
@@ -503,12 +503,7 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
             float l_part[NR];
 #pragma unroll
             for (int r = 0; r < NR; ++r) l_part[r] = 0.f;
-            // the rows' references start at -inf (every thread reads them; thread r writes row r)
-            ok = __all_sync(FULLMASK, meet());
-            if (!ok) break;
-            if (tid < NR) mref[tid] = -INFINITY;
-            ok = __all_sync(FULLMASK, meet());
-            if (!ok) break;
+            // (the rows' references are -inf here: every thread wrote them so itself, at the launch's or the last unit's end)
             for (int i = 0; i < w.u.ntiles; ++i, ++t) {
                 const int stage = t % SW_STAGES, sb = t & 1, pb = t & 1;
                 const int tile_pos = (int)w.u.begin + i * DT_N;
@@ -552,14 +547,16 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                     float x = s[r] * (a_r[r] * kf) + lv;
                     if (edge && (r >= rows_live || pos > first32 + r / G)) x = -INFINITY;
                     s[r] = x;
-                    passes |= x > mref[r] + DT_LAZY;
+                    passes |= x > mref[mb * 32 + r] + DT_LAZY;
                 }
                 const int voted = vote(passes, t);
                 ok = __all_sync(FULLMASK, voted >= 0);
                 if (!ok) break;
                 if (voted) {
                     // some score passed its row's reference by 2^8 (or the unit starts): the rows' maxima exactly, over the
-                    // block; the references, the sums and the outputs follow the rows that moved
+                    // block; the references, the sums and the outputs follow the rows that moved.  Every thread works the
+                    // new references out itself and writes them, all the same, to the array that is not current (last read
+                    // before the vote above), so one meeting serves
 #pragma unroll
                     for (int r = 0; r < NR; ++r) {
                         const float top = warp_max_redux(s[r]);
@@ -571,20 +568,15 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                     float alpha[NR];
 #pragma unroll
                     for (int r = 0; r < NR; ++r) {
-                        const float old = mref[r];
+                        const float old = mref[mb * 32 + r];
                         const float top = fmaxf(fmaxf(rowmax[r], rowmax[32 + r]), fmaxf(rowmax[64 + r], rowmax[96 + r]));
                         const bool go = top > old + DT_LAZY || (old == -INFINITY && top > -INFINITY);
                         alpha[r] = go && old > -INFINITY ? ex2(old - top) : 1.f;
                         moved |= alpha[r] != 1.f;
                         l_part[r] *= alpha[r];
+                        mref[(mb ^ 1) * 32 + r] = go ? top : old;
                     }
-                    ok = __all_sync(FULLMASK, meet());          // (every thread has read the old references and the maxima)
-                    if (!ok) break;
-                    if (tid < NR) {
-                        const float old = mref[tid];
-                        const float top = fmaxf(fmaxf(rowmax[tid], rowmax[32 + tid]), fmaxf(rowmax[64 + tid], rowmax[96 + tid]));
-                        if (top > old + DT_LAZY || (old == -INFINITY && top > -INFINITY)) mref[tid] = top;
-                    }
+                    mb ^= 1;
                     if (moved && i > 0) {
                         // every second product so far has landed; O^T: lane = value column, column j = row j (hi) or j - NR (lo)
                         ok = dt_wait(bar(SW_PVDONE + ((t - 1) & 1)), (uint32_t)((t - 1) >> 1) & 1u, abort_flag);
@@ -617,8 +609,6 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                         }
                         tc_fence_before();
                     }
-                    ok = __all_sync(FULLMASK, meet());          // (the new references are written)
-                    if (!ok) break;
                 }
                 // this tile's P^T buffer is free once the second product of the tile two before has landed
                 ok = dt_wait(bar(SW_PVDONE + pb), (uint32_t)((t >> 1) & 1) ^ 1u, abort_flag);
@@ -630,9 +620,9 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
 #pragma unroll
                 for (int r2 = 0; r2 < NR / 2; ++r2) {
                     const int ra = 2 * r2, rb = ra + 1;
-                    const float ma = mref[ra], mb = mref[rb];
+                    const float ma = mref[mb * 32 + ra], mbr = mref[mb * 32 + rb];
                     const float pa = ex2(s[ra] - (ma == -INFINITY ? 0.f : ma));
-                    const float pbv = ex2(s[rb] - (mb == -INFINITY ? 0.f : mb));
+                    const float pbv = ex2(s[rb] - (mbr == -INFINITY ? 0.f : mbr));
                     l_part[ra] += pa * rv, l_part[rb] += pbv * rv;
                     uint32_t h2, l2;
                     split_e4m3x2<16>(pa, pbv, h2, l2);
@@ -662,7 +652,6 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
             ok = __all_sync(FULLMASK, meet());
             if (!ok) break;
             const bool whole = w.u.nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS);
-            const int prow_first = p.offsets ? p.offsets[w.u.r] - p.offsets[0] : w.u.r * p.columns;
             const bool fits = whole || (p.workspace && w.u.split < p.max_splits && prow_first >= 0 && prow_first + w.u.count <= p.partial_rows);
             if (!fits && tid == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
             const int dv = pos_in_tile;             // this thread's value column
@@ -690,7 +679,7 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                         const int token = w.u.start + colx, head = w.u.h * G + gqx;
                         const float value = (hi[rr] + lo[rr] * (1.f / 16.f)) * vmul;
                         const float l = (rowmax[r] + rowmax[32 + r]) + (rowmax[64 + r] + rowmax[96 + r]);
-                        const float top = mref[r];
+                        const float top = mref[mb * 32 + r];
                         if (whole) {
                             const float inv = l > 0.f ? 1.f / l : 0.f;
                             const int64_t at = (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head + dv;
@@ -709,6 +698,11 @@ decode_sw_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 }
             }
             tc_fence_before();
+            // the next unit's references: -inf in the array that is not current (last read before the meeting above), which
+            // every thread writes for itself and then takes as current
+#pragma unroll
+            for (int r = 0; r < NR; ++r) mref[(mb ^ 1) * 32 + r] = -INFINITY;
+            mb ^= 1;
             w = after;
         }
         if (!ok) where = 0x540;

@@ -42,5 +42,18 @@ inline bool page_map(CUtensorMap* map, const void* pages, int pk, int dim, int k
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same E4M3 page tensor with the dimensions permuted, [128 bytes][slots][kv_heads]: a box is 16 slots of ALL kv
+// heads, one contiguous piece of the tensor (16 x kv_heads x 128 bytes) that lands head-major, row 16 * head + slot.
+inline bool page_rows_map(CUtensorMap* map, const void* pages, int dim, int kv_heads, int64_t slots) {
+    encode_tiled_fn encode = encoder();
+    if (!encode || dim != 128 || kv_heads < 1 || kv_heads > 8) return false;
+    const cuuint64_t dims[3] = {128, (cuuint64_t)slots, (cuuint64_t)kv_heads};
+    const cuuint64_t strides[2] = {(cuuint64_t)128 * kv_heads, 128};
+    const cuuint32_t box[3] = {128, 16, (cuuint32_t)kv_heads};
+    const cuuint32_t steps[3] = {1, 1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(pages), dims, strides, box, steps,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 }  // namespace crit_b200

@@ -126,6 +126,12 @@ int crit_b200_slots(const crit_b200_slots_params* params, void* stream);
 #define CRIT_B200_ATTEND_TCGEN05T 64 /* the tcgen05 kernel with the operands swapped (the key and value tiles on the MMA's 128
                                         rows, the query rows on its columns) or CRIT_B200_EUNSUPPORTED: the same launches
                                         CRIT_B200_ATTEND_TCGEN05 takes */
+#define CRIT_B200_ATTEND_TCGEN05P 128 /* the tcgen05 kernel over whole page rows (a unit reads all kv heads of its positions: one
+                                         contiguous piece of HBM a tile; the launch's tiles are dealt out evenly, so a split
+                                         may be shared by two blocks) or CRIT_B200_EUNSUPPORTED: E4M3 pages of 128-wide heads,
+                                         8 kv heads, columns x group heads <= 8, chunk a multiple of 16 up to 2,048, a workspace
+                                         with max_splits >= 2 x the splits of the longest row: a split has two states there,
+                                         and both launches (decode and merge) carry the flag */
 #define CRIT_B200_ATTEND_PARTIALS 32 /* every row's split states go to the workspace, a row of one split too (the first launch
                                         writes nothing to out / lse): what crit_b200_merge_push sends, or what
                                         crit_b200_merge folds */

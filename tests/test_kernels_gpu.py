@@ -231,6 +231,86 @@ def test_tcgen05_tiles_edge_cases(pk, engine):
     assert pk.status() == 0
 
 
+# The tcgen05 engine over whole page rows: a unit reads all 8 kv heads of its positions (one contiguous piece of HBM a
+# tile), kv head h's query rows on TMEM lanes 16 h .. 16 h + 15.
+@pytest.mark.parametrize("kind", ["fp8", "fp8:row", "fp8:page"])
+@pytest.mark.parametrize("hq,cols", [(64, 1), (32, 2), (16, 4), (8, 5), (56, 1), (24, 2)])
+@pytest.mark.parametrize("page,chunk", [(16, 16), (16, 128), (48, 256), (16, 1024), (64, 2048)])
+def test_windows_on_whole_page_rows_match_the_oracle(pk, kind, hq, cols, page, chunk):
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, 8, 128, 128, page, [130, 64, 1, 517, 1300])
+    firsts = [125, 59, 0, 400, 1290]
+    counts = [min(cols, n) for n in [5, 5, 1, 3, 5]]
+    rows, starts = [0, 1, 2, 3, 4], [0, 5, 10, 15, 20]
+    q = queries(25, hq, 128, 3)
+    lse = torch.full((25, hq), 7.0, device="cuda")
+    out = cache.attend(q, rows, starts, firsts, cols, counts=counts, lse=lse, chunk=chunk, engine="tcgen05p")
+    assert pk.status() == 0
+    want, want_lse = cache.oracle(q, rows, starts, firsts, cols, counts=counts)
+    tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
+    assert_attention_close(out, lse, want, want_lse, tokens)
+
+
+@pytest.mark.parametrize("kind", ["fp8:page", "fp8:row"])
+def test_whole_page_rows_with_outliers_and_long_rows(pk, kind):
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, 8, 128, 128, 16, [1000, 37, 16, 2049, 5000], outliers=True)
+    q = queries(5, 64, 128, 9)
+    rows, starts, firsts = [0, 1, 2, 3, 4], [0, 1, 2, 3, 4], [999, 36, 15, 2048, 4999]
+    lse = torch.empty(5, 64, device="cuda")
+    out = cache.attend(q, rows, starts, firsts, 1, lse=lse, chunk=512, engine="tcgen05p")
+    assert pk.status() == 0
+    want, want_lse = cache.oracle(q, rows, starts, firsts, 1)
+    assert_attention_close(out, lse, want, want_lse, [0, 1, 2, 3, 4], rel=2.0 ** -7)
+    again = cache.attend(q, rows, starts, firsts, 1, chunk=512, engine="tcgen05p")
+    assert torch.equal(out, again)                                       # the same launch twice: the same bits
+    # a row alone is cut into other units than in a batch (the launch's tiles are dealt out evenly): other bits, the
+    # same attention
+    alone = cache.attend(q[3:4], [3], [0], [2048], 1, chunk=512, engine="tcgen05p")
+    assert_attention_close(alone, None, want[3:4], None, [0], rel=2.0 ** -7)
+
+
+def test_whole_page_rows_edge_cases(pk):
+    """A NaN query stays in its own token, rows with no columns write nothing, FP16 queries, packed partial rows, and what
+    the engine does not serve is refused."""
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache("fp8:page", 8, 128, 128, 16, [200, 1300, 40], spare=8)
+    q = queries(12, 16, 128, 2)
+    rows, starts, firsts = [0, 1, 2], [0, 4, 8], [196, 1296, 36]
+    clean = cache.attend(q, rows, starts, firsts, 4, engine="tcgen05p", chunk=256)
+    q2 = q.clone()
+    q2[5, 3, 7] = float("nan")
+    got = cache.attend(q2, rows, starts, firsts, 4, engine="tcgen05p", chunk=256)
+    assert torch.isnan(got[5, 3]).all()
+    keep = torch.ones(12, 16, dtype=torch.bool)
+    keep[5, 3] = False
+    assert torch.equal(got.cpu()[keep], clean.cpu()[keep])
+    marked = torch.full_like(clean, 7.0)
+    some = cache.attend(q, rows, starts, firsts, 4, counts=[4, 0, 9], out=marked, engine="tcgen05p", chunk=256)
+    assert torch.equal(some[0:4], clean[0:4]) and torch.equal(some[8:12], clean[8:12]) and bool((some[4:8] == 7.0).all())
+    qh = queries(12, 16, 128, 4, torch.float16)
+    cache16 = Cache("fp8:row", 8, 128, 128, 16, [200, 1300, 40], spare=8)
+    lse = torch.empty(12, 16, device="cuda")
+    out = cache16.attend(qh, rows, starts, firsts, 4, lse=lse, engine="tcgen05p", chunk=256)
+    want, want_lse = cache16.oracle(qh, rows, starts, firsts, 4)
+    assert_attention_close(out, lse, want, want_lse, list(range(12)))
+    offsets = torch.tensor([0, 2, 3], dtype=torch.int32, device="cuda")
+    splits = pk.parts_for(cache.tables.shape[1] * 16, 256)
+    space = torch.empty(pk.workspace_floats(7, 16, 2 * splits, 128), device="cuda")       # a split's head and tail
+    padded = cache.attend(q, rows, starts, firsts, 4, counts=[2, 1, 4], chunk=256, engine="tcgen05p")
+    packed = cache.attend(q, rows, starts, firsts, 4, counts=[2, 1, 4], offsets=offsets, tokens=7, workspace=space, chunk=256,
+                          engine="tcgen05p")
+    for start, count in zip(starts, [2, 1, 4]):
+        assert torch.equal(packed[start:start + count], padded[start:start + count])
+    assert pk.status() == 0
+    with pytest.raises(Exception):        # 4 kv heads
+        Cache("fp8:page", 4, 128, 128, 16, [100]).attend(queries(1, 8, 128, 1), [0], [0], [99], 1, engine="tcgen05p")
+    with pytest.raises(Exception):        # 5 columns x 2 heads of a group: more than 8 query rows a kv head
+        cache.attend(queries(5, 16, 128, 1), [0], [0], [95], 5, engine="tcgen05p")
+    with pytest.raises(Exception):        # bf16 pages
+        Cache("bf16", 8, 128, 128, 16, [100]).attend(queries(1, 8, 128, 1), [0], [0], [99], 1, engine="tcgen05p")
+
+
 def test_tcgen05_tiles_refuse_launches_they_do_not_serve(pk):
     from helpers import Cache, queries
     cache = Cache("bf16", 2, 128, 128, 16, [100])
