@@ -312,6 +312,7 @@ def launches_per_step(state):
 # once; the writes are the partial states, a fixed number per split), so a launch's traffic is its algorithmic bytes
 # times the ratio.  None where no capture was made.
 TRAFFIC_RATIO = {("c2", "mma.sync"): (540.9e6 + 9.7e6) / 537.9e6,      # decode_kernel, FP8 decode at full size
+                 ("c2", "tcgen05p"): (270.6e6 + 5.3e6) / 269.0e6,      # decode_ph_kernel, FP8 decode at 32 sequences
                  ("c3", "mma.sync"): (819.4e6 + 7.6e6) / 819.2e6,      # decode_kernel (TMA), the long context at full size
                  ("c5", "tcgen05"): (167.9e6 + 4.7e6) / 167.0e6}       # decode_tc_kernel<4>, verify at 8 sequences
 
@@ -526,7 +527,7 @@ def measure(name, w, args, device, rank, world, local, primary):
     else:
         kv_total, tokens_total, decode_max = kv, tokens, decode_s
     hbm_peak, tensor_peak, peak_source = peaks()
-    engine = args.engine or ("library default (tcgen05 tiles for verify windows over E4M3 pages, m16n8k16 tiles otherwise)")
+    engine = args.engine or ("library default: " + engine_of(args, state))
     found = {"workload": w["name"], "value": kv_total / seconds / 1e9, "unit": "GB/s", "ms_per_step": seconds * 1e3,
              "ms_per_step_min": fastest * 1e3, "ms_per_step_max": slowest * 1e3, "timed_batches": samples, "steps_per_batch": steps,
              "tokens_per_s": tokens_total / seconds, "hbm_frac_of_8TBps": kv_total / world / seconds / 8e12,
@@ -551,7 +552,7 @@ def measure(name, w, args, device, rank, world, local, primary):
                                  "kernels of its neighbour"},
              "parity": checked}
     achieved = state["kv_bytes"] / decode_s / 1e9 if decode_s > 0 else 0.0
-    found["roofline"] = {"bound": "hbm", "kernel": "split-K decode launch over paged KV (decode_kernel / decode_tc_kernel)",
+    found["roofline"] = {"bound": "hbm", "kernel": "split-K decode launch over paged KV (" + {"mma.sync": "decode_kernel: m16n8k16", "tcgen05": "decode_tc_kernel: tcgen05, one kv head a unit", "tcgen05t": "decode_sw_kernel: tcgen05, operands swapped", "tcgen05p": "decode_ph_kernel: tcgen05, whole page rows"}.get(engine_of(args, state), "decode_kernel") + ")",
                          "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                          "frac_of_8TBps": achieved / 8000.0, "peak_source": peak_source, "us_per_launch": decode_s * 1e6,
                          "us_per_launch_max_over_ranks": decode_max * 1e6,
@@ -574,10 +575,21 @@ def measure(name, w, args, device, rank, world, local, primary):
     return found, state
 
 
+def engine_of(args, state):
+    """The decode kernel the step's launch runs on: the one asked for, or crit_b200's own choice for the launch."""
+    import crit_b200 as pk
+    w = state["w"]
+    if args.engine or state.get("merger") is not None or args.staging:
+        return args.engine or "mma.sync"
+    rows = int(state["rows"].shape[0]) if hasattr(state.get("rows"), "shape") else len(state["live"])
+    return pk.engine_for(w["kind"], w["d"], w["d"], w["hq"], w["hkv"], min(w["columns"], 64), rows,
+                         int(state["tables"].shape[1]) * w["page"])
+
+
 def traffic(name, args, state):
     if args.staging or args.chunk:
         return None
-    engine = args.engine or ("tcgen05" if state["w"]["columns"] > 1 and state["w"]["kind"].startswith("fp8") else "mma.sync")
+    engine = engine_of(args, state)
     ratio = TRAFFIC_RATIO.get((name, engine))
     return None if ratio is None else ratio * state["kv_bytes"]
 

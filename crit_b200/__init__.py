@@ -26,7 +26,8 @@ import torch
 from . import _lib
 
 __all__ = ["KINDS", "MAX_COLUMNS", "attend", "chunk_for", "gather", "merge_shards", "owner", "partitions", "parts_for",
-           "piece_size", "plan", "prefill", "prefill_serves", "release", "slots_at", "status", "tcgen05_serves", "tile_for", "workspace_floats", "write"]
+           "engine_for", "piece_size", "plan", "prefill", "prefill_serves", "release", "slots_at", "states_for", "status", "tcgen05_serves",
+           "tcgen05p_serves", "tile_for", "workspace_floats", "write"]
 
 KINDS = {"bf16": 0, "fp16": 0, "fp8": 1, "fp8:row": 2, "int8": 3, "fp8:page": 4}
 MAX_COLUMNS = 64            # columns of one row a launch reads
@@ -138,22 +139,55 @@ def status(device=None):
 # -- geometry rules -----------------------------------------------------------------------------------------------------
 def chunk_for(head_dim, value_dim, heads, kv_heads, page, kind="bf16", engine=None, columns=1):
     """Positions per split of a launch over a cache of this geometry (a multiple of 16).  One per cache for the
-    m16n8k16 kernel, never by the batch, so a column's bits are the same alone and in any window.  Launches the tcgen05
-    kernel takes (engine "tcgen05", or the library's choice for windows of several columns over E4M3 pages) use splits
-    of 2,048: a unit's fold of its lane replicas is paid once per split."""
-    if engine in ("tcgen05", "tcgen05t", "tcgen05p") or (engine is None and columns > 1 and
-                               tcgen05_serves(kind, head_dim, value_dim, heads, kv_heads, columns, 2 * DEFAULT_CHUNK)):
-        return 2 * DEFAULT_CHUNK
-    return DEFAULT_CHUNK
+    m16n8k16 kernel, never by the batch, so a column's bits are the same alone and in any window.  Launches of the
+    tcgen05 kernel that gives a unit one kv head (engine "tcgen05", or attend's own choice for windows of several columns
+    over E4M3 pages) use splits of 2,048: a unit's fold of its lane replicas is paid once per split."""
+    if engine is None:
+        engine = engine_for(kind, head_dim, value_dim, heads, kv_heads, columns)
+    return 2 * DEFAULT_CHUNK if engine in ("tcgen05", "tcgen05t") else DEFAULT_CHUNK
 
 
 def tcgen05_serves(kind, head_dim, value_dim, heads, kv_heads, columns, chunk, rows=1):
     """Whether the tcgen05 kernel takes a launch: E4M3 pages of 128-wide heads, at most 32 query rows a unit (columns
     x heads of a kv head's group), splits of whole 128-position tiles up to 2,048 positions, up to 256 window rows (the
-    same test the library makes: decode.cu, tc_serves).  The library sends such launches there by itself when they have
-    more than one column; engine="mma.sync" keeps them on the m16n8k16 kernel."""
+    same test the library makes: decode.cu, tc_serves)."""
     return (str(kind).startswith("fp8") and head_dim == 128 and value_dim == 128 and columns * (heads // kv_heads) <= 32
             and chunk % 128 == 0 and chunk <= 2048 and rows <= 256)
+
+
+def tcgen05p_serves(kind, head_dim, value_dim, heads, kv_heads, columns, chunk, rows=1):
+    """Whether the tcgen05 kernel over whole page rows takes a launch: E4M3 pages of 128-wide heads, 8 kv heads, at most 8
+    query rows a kv head (columns x heads of a group), splits of whole 16-position tiles up to 2,048 positions, up to 256
+    window rows (the same test the library makes: decode.cu, ph_serves)."""
+    return (str(kind).startswith("fp8") and head_dim == 128 and value_dim == 128 and kv_heads == 8 and
+            columns * (heads // kv_heads) <= 8 and chunk % 16 == 0 and chunk <= 2048 and rows <= 256)
+
+
+# Launches below this many positions (window rows x the positions their tables hold) stay on the m16n8k16 kernel: the
+# whole-page-rows kernel deals whole splits to its blocks, and a small launch has too few to fill the device.
+PAGE_ROWS_FROM = 1 << 16
+
+
+def engine_for(kind, head_dim, value_dim, heads, kv_heads, columns, rows=1, positions=None, engine=None):
+    """The kernel a launch runs on: `engine` when one is named, else attend's own choice: "tcgen05p" (whole page rows:
+    every kv head of a position in one contiguous read) for E4M3 pages of 8 kv heads x 128 with at most 8 query rows a
+    kv head, when the launch is large enough to fill the device that way; "tcgen05" for other windows of several
+    columns over E4M3 pages of 128-wide heads; "mma.sync" (m16n8k16) for everything else.  Only the last gives a column
+    the same bits alone and in any window or batch."""
+    if engine is not None:
+        return engine
+    if tcgen05p_serves(kind, head_dim, value_dim, heads, kv_heads, columns, DEFAULT_CHUNK, rows) and \
+            positions is not None and rows * positions >= PAGE_ROWS_FROM:
+        return "tcgen05p"
+    if columns > 1 and tcgen05_serves(kind, head_dim, value_dim, heads, kv_heads, columns, 2 * DEFAULT_CHUNK, rows):
+        return "tcgen05"
+    return "mma.sync"
+
+
+def states_for(parts, engine):
+    """Split states a partial row takes in the workspace for `parts` splits: the whole-page-rows kernel deals the
+    launch's tiles out evenly, so a split may be shared by two blocks and has two states (its head and its tail)."""
+    return 2 * parts if engine == "tcgen05p" else parts
 
 
 def parts_for(positions, chunk):
@@ -376,11 +410,18 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
         raise ValueError("pages are contiguous [slots][kv_heads][dim] storage")
     device = q.device
     positions = tables.shape[1] * page
+    chosen = engine is None
+    if chosen and (shards is not None or persistent or staging is not None):
+        engine = "mma.sync"               # what those arguments are about
+    engine = engine_for(kind, d, dv, hq, hkv, int(columns), R, positions, engine)
     chunk = int(chunk or chunk_for(d, dv, hq, hkv, page, kind, engine, int(columns)))
     if partitions:
         chunk = max(chunk, -(-positions // int(partitions)))
     chunk = -(-chunk // TILE) * TILE
-    splits = parts_for(positions, chunk) * (2 if engine == "tcgen05p" else 1)       # that engine: a split's head and tail
+    if chosen and ((engine == "tcgen05p" and not tcgen05p_serves(kind, d, dv, hq, hkv, int(columns), chunk, R)) or
+                   (engine == "tcgen05" and not tcgen05_serves(kind, d, dv, hq, hkv, int(columns), chunk, R))):
+        engine = "mma.sync"               # the caller's chunk is not one the chosen kernel takes
+    splits = states_for(parts_for(positions, chunk), engine)
     partial_rows = R * columns if offsets is None else int(tokens)
     out = torch.empty(T, hq, dv, dtype=q.dtype, device=device) if out is None else out
     if out.dtype != q.dtype or out.stride(-1) != 1:
@@ -408,7 +449,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     if staging not in (None, "tma", "cp.async"):
         raise ValueError("staging is None, tma or cp.async")
     p.flags = ({None: 0, "cp.async": 1, "tma": 2}[staging] | (4 if persistent else 0) |
-               {None: 0, "tcgen05": 8, "mma.sync": 16, "tcgen05t": 64, "tcgen05p": 128}[engine] | (32 if shards is not None else 0))
+               {"tcgen05": 8, "mma.sync": 16, "tcgen05t": 64, "tcgen05p": 128}[engine] | (32 if shards is not None else 0))
     p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])

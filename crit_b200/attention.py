@@ -49,16 +49,17 @@ class DeviceAttention:
         """kernels: the crit_b200 module (default).  partitions: the most splits of a partial row (0: what the tables
         need); chunk: positions per split (0: the kernels' rule).  kernels_mib: the most partials a launch takes from
         `scratch` (the engine's Scratch, crit_plugins.memory) when one is given.  prompt_reader: "prefill" or "decode".
-        window_engine: "auto" (the kernels' choice: windows of several columns over E4M3 pages on tcgen05 tiles, decode
-        rows on m16n8k16 tiles; a column's bits then depend on the window it is read in: exactness "repeatable"),
-        "mma.sync" (the m16n8k16 kernel always: a column's bits are the same alone and in any window, "row-exact") or
-        "tcgen05" (tcgen05 tiles wherever that kernel serves a launch, decode rows included).
+        window_engine: "auto" (the kernels' choice, crit_b200.engine_for: E4M3 pages through tcgen05.mma where a kernel for
+        it serves the step, m16n8k16 tiles otherwise; a column's bits then depend on the window and the step it is read
+        in: exactness "repeatable"), "mma.sync" (the m16n8k16 kernel always: a column's bits are the same alone and in
+        any window or batch, "row-exact"), "tcgen05" (one kv head a unit, wherever that kernel serves a launch) or
+        "tcgen05p" (whole page rows a unit, where that kernel serves the step).
         mode "torch", decode "flashinfer", flashinfer "auto", int8_qk and latent are the reference's other readers: not
         served here."""
         if mode == "torch" or decode != "split" or flashinfer != "off" or int8_qk or latent is not None:
             raise ValueError("crit_b200 serves its own CUDA kernels only (mode auto, decode split, flashinfer off)")
-        if window_engine not in ("auto", "mma.sync", "tcgen05"):
-            raise ValueError(f"window_engine is auto, mma.sync or tcgen05, not {window_engine!r}")
+        if window_engine not in ("auto", "mma.sync", "tcgen05", "tcgen05p"):
+            raise ValueError(f"window_engine is auto, mma.sync, tcgen05 or tcgen05p, not {window_engine!r}")
         self.window_engine = window_engine
         if prompt_reader not in ("prefill", "decode"):
             raise ValueError(f"prompt_reader is prefill or decode, not {prompt_reader!r}")
@@ -76,7 +77,7 @@ class DeviceAttention:
     def facts(self):
         return {"reader": "crit_b200: a row's positions in contiguous splits of one chunk per pool, folded in split order; " +
                           ("a column's bits are the same alone and in any window" if self.window_engine == "mma.sync" else
-                           "windows over E4M3 pages through tcgen05.mma where served: a column's bits depend on its window"),
+                           "E4M3 pages through tcgen05.mma where served: a column's bits depend on its window and its step"),
                 "prompt_reads": "through the prefill kernel" if self.prompt_reader == "prefill" else
                                 "in the decode's reduction (pieces of up to 64 columns)",
                 "split_kv_wide_windows": "16- or 32-row tiles; wider windows read their pages once per tile"}
@@ -152,12 +153,17 @@ class DeviceAttention:
         multipliers = pool.scale_values[pool.layers[layer]] if pool.dtype == "fp8" else (1.0, 1.0)
         kernels = self.kernels
         positions = meta.tables.shape[1] * pool.page
+        geometry = (pool.dtype, pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, meta.columns)
+        # the kernel the step's windows run on: the kernels' choice for the whole step, or the one the option names
+        named = kernels.engine_for(*geometry, len(meta), positions, None if self.window_engine == "auto" else self.window_engine)
         chunk = self.chunk or kernels.chunk_for(pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, pool.page, pool.dtype,
-                                                None if self.window_engine == "auto" else self.window_engine, meta.columns)
+                                                named, meta.columns)
         if self.partitions:
             chunk = max(chunk, -(-positions // self.partitions))
         chunk = -(-chunk // 16) * 16
-        parts = kernels.parts_for(positions, chunk)
+        if named == "tcgen05p" and not kernels.tcgen05p_serves(*geometry, chunk, len(meta)):
+            named = "mma.sync"
+        parts = kernels.states_for(kernels.parts_for(positions, chunk), named)
         launches, workspace = [(slice(0, len(meta)), meta.total)], None
         if self.partial_bytes and parts > 1:
             # the partials come from the engine's scratch: as many rows a launch as its share of the scratch holds
@@ -168,11 +174,9 @@ class DeviceAttention:
             workspace = self.scratch.take(min(self.partial_bytes, 4 * per * most)).view(torch.float32)
 
         def engine(rows):
-            if self.window_engine == "tcgen05":
-                serves = kernels.tcgen05_serves(pool.dtype, pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads,
-                                                meta.columns, chunk, rows)
-                return "tcgen05" if serves else "mma.sync"
-            return None if self.window_engine == "auto" else "mma.sync"
+            if named == "tcgen05":
+                return "tcgen05" if kernels.tcgen05_serves(*geometry, chunk, rows) else "mma.sync"
+            return named
 
         for cut, tokens in launches:
             part = (lambda t: t[cut]) if not cut.start else (lambda t: t[cut].clone())

@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
     for (int s = warp; s < nsplit; s += MERGE_WARPS) {
         const float ms = pm[base + s], ls = pl[base + s];
-        if (ms == -INFINITY) continue;
+        if (ms == -INFINITY && ls == 0.f) continue;         // a state that holds nothing (a NaN row's sum is not 0)
         const float* o = p.workspace + (base + s) * DV + lane * per;
         float v[8];
 #pragma unroll
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
     for (int i = 0; i < PER; ++i) acc[i] = 0.f;
 #pragma unroll 4
     for (int s = 0; s < nsplit; ++s) {
-        if (pm[base + s] == -INFINITY) continue;
+        if (pm[base + s] == -INFINITY && pl[base + s] == 0.f) continue;         // a state that holds nothing
         const float w = ex2(pm[base + s] - sub);
         total += pl[base + s] * w;
         const float* o = p.workspace + (base + s) * DV + lane * PER;
@@ -201,7 +201,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_push_kernel(const crit
 #pragma unroll 4
         for (int s = warp; s < nsplit; s += MERGE_WARPS) {
             const float ms = pm[base + s], ls = pl[base + s];
-            if (ms == -INFINITY) continue;
+            if (ms == -INFINITY && ls == 0.f) continue;         // a state that holds nothing (a NaN row's sum is not 0)
             const float* o = p.workspace + (base + s) * DV + lane * PER;
             float v[PER];
 #pragma unroll
@@ -534,8 +534,11 @@ static int launch_decode_ph(const crit_b200_attend_params& p, cudaStream_t s) {
         !page_rows_map(&vmap, p.value_pages, p.value_dim, p.kv_heads, p.slots))
         return CRIT_B200_EUNSUPPORTED;
     typedef void (*ph_fn)(const crit_b200_attend_params, const CUtensorMap, const CUtensorMap);
-    static const ph_fn fns[3] = {decode_ph_kernel<0>, decode_ph_kernel<1>, decode_ph_kernel<2>};
-    const ph_fn fn = fns[scale_mode(p.kind)];
+    static const ph_fn fns[2][3] = {{decode_ph_kernel<0, 1>, decode_ph_kernel<1, 1>, decode_ph_kernel<2, 1>},
+                                    {decode_ph_kernel<0, 2>, decode_ph_kernel<1, 2>, decode_ph_kernel<2, 2>}};
+    const int per_sm = (p.flags & CRIT_B200_ATTEND_PERSISTENT) ? 1 : 2;        // (a measurement's switch)
+    const ph_fn fn = fns[per_sm - 1][scale_mode(p.kind)];
+    const int PH_SMEM = per_sm == 1 ? PhCfg<1>::SMEM : PhCfg<2>::SMEM;
     cudaError_t ce = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, PH_SMEM);
     if (ce != cudaSuccess) return (int)ce;
     int device = 0, sms = 0;
@@ -543,7 +546,7 @@ static int launch_decode_ph(const crit_b200_attend_params& p, cudaStream_t s) {
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms < 1)
         return CRIT_B200_EUNSUPPORTED;
     const int64_t most = (int64_t)((p.max_splits + 1) / 2) * p.n_rows;         // splits the launch can have: a block holds one at least
-    const unsigned blocks = (unsigned)(most < 2 * sms ? most : 2 * sms);       // two persistent blocks per SM
+    const unsigned blocks = (unsigned)(most < per_sm * sms ? most : per_sm * sms);
     fn<<<blocks, PH_THREADS, PH_SMEM, s>>>(p, kmap, vmap);
     CRIT_CHECK_LAUNCH();
     return 0;

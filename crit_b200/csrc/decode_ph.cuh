@@ -23,9 +23,9 @@
 // where a row or a split of `chunk` positions ends, so a split belongs to one block or to two; its partial state goes
 // to slot 2 s of the row's states (its head) or 2 s + 1 (its tail), and a block that holds a whole split marks slot
 // 2 s + 1 empty (m = -inf, l = 0; the fold passes such states over).  A block's consecutive units mostly belong to one
-// row, whose queries are split into the A operand once.  Roles as in decode_tc.cuh: warps 0-3 softmax (thread = TMEM lane), warp 4 producer (TMA; the tile's
-// scales come by a bulk copy onto the same mbarrier as its keys), warp 5 queries and MMA issue.  Every wait is bounded
-// in time and polls the block's abort flag.
+// row, whose queries are split into the A operand once.  Roles: warps 0-3 softmax (thread = TMEM lane), warp 4
+// producer (TMA; a tile's scales come by a bulk copy onto the same mbarrier as its keys), warp 5 the rows' queries and
+// the first products, warp 6 the second products.  Every wait is bounded in time and polls the block's abort flag.
 //
 // Serves: E4M3 pages of 128-wide heads, 8 kv heads, columns x heads-per-group <= 8, chunks of whole 16-position tiles
 // up to 2,048 positions.  HBM traffic per unit: its keys and values once, the pages' scales, one partial state.
@@ -38,26 +38,40 @@ namespace crit_b200 {
 
 constexpr int PH_TILE = 16;               // positions a tile holds
 constexpr int PH_HEADS = 8;               // kv heads: 16 x 8 = the 128 rows of an operand
-constexpr int PH_THREADS = 192;
+constexpr int PH_THREADS = 224;            // 4 softmax warps, a producer warp, a warp for each product's MMAs
 constexpr int PH_MAX_LIST = 256;          // window rows a launch lists its work for
 
-// shared memory (after the 1 KB alignment): Q | P | stages (keys 16 KB | values 16 KB) | the tiles' scales (1 KB a tile,
-// four tiles in turn) | small
+// PER_SM blocks an SM.  One: all 512 TMEM columns (scores of the even and of the odd tiles at 0 and 128, outputs at 256),
+// probabilities of the even and of the odd tiles, 5 stages.  Two: 256 columns each (scores at 0, outputs at 128), one tile
+// of probabilities, 2 stages.  Shared memory (after the 1 KB alignment): Q | P x NBUF | stages (keys 16 KB | values
+// 16 KB) | the tiles' scales (1 KB a tile, SCALE_SLOTS tiles in turn) | small.
+template <int PER_SM>
+struct PhCfg {
+    static constexpr int STAGES = PER_SM == 1 ? 5 : 2;
+    static constexpr int NBUF = PER_SM == 1 ? 2 : 1;            // tiles of scores (TMEM) and of probabilities (shared memory) in turn
+    static constexpr int SCALE_SLOTS = PER_SM == 1 ? 8 : 4;
+    static constexpr uint32_t COLUMNS = PER_SM == 1 ? 512 : 256, O = 128 * NBUF;
+    static constexpr int OFF_P = DT_OPER;
+    static constexpr int OFF_STAGES = (1 + NBUF) * DT_OPER;
+    static constexpr int OFF_SCALES = OFF_STAGES + STAGES * 2 * DT_KV_BYTES;
+    static constexpr int OFF_SMALL = OFF_SCALES + SCALE_SLOTS * 1024;
+    // mbarriers: stage s of keys / values full and empty; the scores' buffers full and read; the probabilities' buffers
+    // written and their second product done; the queries
+    static constexpr int KFULL = 0, VFULL = STAGES, KEMPTY = 2 * STAGES, VEMPTY = 3 * STAGES, SFULL = 4 * STAGES, SFREE = SFULL + NBUF,
+                         PFULL = SFREE + NBUF, PVDONE = PFULL + NBUF, QFULL = PVDONE + NBUF, BARS = QFULL + 1;
+    static constexpr int SMALL_QFAC = 0;                          // [2][64] floats: the rows' score factors, by the parity of the queries
+    static constexpr int SMALL_BARS = 512;                        // up to 29 mbarriers
+    static constexpr int SMALL_TMEM = SMALL_BARS + 29 * 8;
+    static constexpr int SMALL_ABORT = SMALL_TMEM + 4;
+    static constexpr int SMALL_LIST = 768;                        // unit_first [PH_MAX_LIST + 1] ints (padded)
+    static constexpr int SMALL_COUNT = SMALL_LIST + (PH_MAX_LIST + 4) * 4;
+    static constexpr int SMALL_START = SMALL_COUNT + PH_MAX_LIST * 4;
+    static constexpr int SMALL_ROW = SMALL_START + PH_MAX_LIST * 4;
+    static constexpr int SMALL_SPLITS = SMALL_ROW + PH_MAX_LIST * 4;
+    static constexpr int SMALL_FIRST = SMALL_SPLITS + PH_MAX_LIST * 4;
+    static constexpr int SMEM = 1024 + OFF_SMALL + SMALL_FIRST + PH_MAX_LIST * 8;
+};
 constexpr int PH_STAGE = 2 * DT_KV_BYTES;
-constexpr int PH_SCALE_SLOTS = 4;
-constexpr int PH_OFF_SCALES = 2 * DT_OPER + DT_STAGES * PH_STAGE;
-constexpr int PH_OFF_SMALL = PH_OFF_SCALES + PH_SCALE_SLOTS * 1024;
-constexpr int PH_SMALL_QFAC = 0;                              // [2][64] floats: the rows' score factors, by the parity of the queries
-constexpr int PH_SMALL_BARS = 512;                            // 16 mbarriers (decode_tc.cuh's, the fold's unused)
-constexpr int PH_SMALL_TMEM = PH_SMALL_BARS + 16 * 8;
-constexpr int PH_SMALL_ABORT = PH_SMALL_TMEM + 4;
-constexpr int PH_SMALL_LIST = 768;                            // unit_first [PH_MAX_LIST + 1] ints (padded)
-constexpr int PH_SMALL_COUNT = PH_SMALL_LIST + (PH_MAX_LIST + 4) * 4;
-constexpr int PH_SMALL_START = PH_SMALL_COUNT + PH_MAX_LIST * 4;
-constexpr int PH_SMALL_ROW = PH_SMALL_START + PH_MAX_LIST * 4;
-constexpr int PH_SMALL_SPLITS = PH_SMALL_ROW + PH_MAX_LIST * 4;
-constexpr int PH_SMALL_FIRST = PH_SMALL_SPLITS + PH_MAX_LIST * 4;
-constexpr int PH_SMEM = 1024 + PH_OFF_SMALL + PH_SMALL_FIRST + PH_MAX_LIST * 8;
 
 struct PhUnit {
     int r, split, slot, count, ntiles, start;
@@ -117,47 +131,54 @@ struct PhWalk {
 };
 
 // SMODE as in decode_tc.cuh: 0 static multipliers, 1 a scale per (slot, kv head), 2 a scale per (page, kv head).
-template <int SMODE>
-__global__ void __launch_bounds__(PH_THREADS, 2)
+template <int SMODE, int PER_SM>
+__global__ void __launch_bounds__(PH_THREADS, PER_SM)
 decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap) {
+    using C = PhCfg<PER_SM>;
     constexpr int smode = SMODE;
+    constexpr int PH_STAGES = C::STAGES, NBUF = C::NBUF, PH_SCALE_SLOTS = C::SCALE_SLOTS;
+    constexpr int PH_KFULL = C::KFULL, PH_VFULL = C::VFULL, PH_KEMPTY = C::KEMPTY, PH_VEMPTY = C::VEMPTY, PH_SFULL = C::SFULL,
+                  PH_SFREE = C::SFREE, PH_PFULL = C::PFULL, PH_PVDONE = C::PVDONE, PH_QFULL = C::QFULL;
+    constexpr uint32_t PH_O = C::O, PH_COLUMNS = C::COLUMNS;
     constexpr uint32_t FULLMASK = 0xffffffffu;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024 - (smem_addr(smem_raw) & 1023)) & 1023);
     unsigned char* qbuf = smem;
-    unsigned char* pbuf = smem + DT_OPER;
-    unsigned char* stages = smem + 2 * DT_OPER;
-    float* scales = reinterpret_cast<float*>(smem + PH_OFF_SCALES);
-    unsigned char* small = smem + PH_OFF_SMALL;
-    float* qfac = reinterpret_cast<float*>(small + PH_SMALL_QFAC);
-    const uint32_t bars = smem_addr(small + PH_SMALL_BARS);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(small + PH_SMALL_TMEM);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(small + PH_SMALL_ABORT);
-    int* unit_first = reinterpret_cast<int*>(small + PH_SMALL_LIST);
-    int* m_count = reinterpret_cast<int*>(small + PH_SMALL_COUNT);
-    int* m_start = reinterpret_cast<int*>(small + PH_SMALL_START);
-    int* m_row = reinterpret_cast<int*>(small + PH_SMALL_ROW);
-    int* m_splits = reinterpret_cast<int*>(small + PH_SMALL_SPLITS);
-    int64_t* m_first = reinterpret_cast<int64_t*>(small + PH_SMALL_FIRST);
+    unsigned char* pbufs = smem + C::OFF_P;
+    unsigned char* stages = smem + C::OFF_STAGES;
+    float* scales = reinterpret_cast<float*>(smem + C::OFF_SCALES);
+    unsigned char* small = smem + C::OFF_SMALL;
+    float* qfac = reinterpret_cast<float*>(small + C::SMALL_QFAC);
+    const uint32_t bars = smem_addr(small + C::SMALL_BARS);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(small + C::SMALL_TMEM);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(small + C::SMALL_ABORT);
+    int* unit_first = reinterpret_cast<int*>(small + C::SMALL_LIST);
+    int* m_count = reinterpret_cast<int*>(small + C::SMALL_COUNT);
+    int* m_start = reinterpret_cast<int*>(small + C::SMALL_START);
+    int* m_row = reinterpret_cast<int*>(small + C::SMALL_ROW);
+    int* m_splits = reinterpret_cast<int*>(small + C::SMALL_SPLITS);
+    int64_t* m_first = reinterpret_cast<int64_t*>(small + C::SMALL_FIRST);
     auto bar = [&](int which) { return bars + (uint32_t)which * 8u; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = p.q_heads / p.kv_heads;
 
     // -- setup ---------------------------------------------------------------------------------------------------------
-    if (warp == 0) tmem_alloc(smem_addr(tmem_slot), DT_COLUMNS);
+    if (warp == 0) tmem_alloc(smem_addr(tmem_slot), PH_COLUMNS);
     if (tid == 32) {
-        for (int s = 0; s < DT_STAGES; ++s) {
-            mbar_init(bar(DT_KFULL + s), 1), mbar_init(bar(DT_KEMPTY + s), 1);
-            mbar_init(bar(DT_VFULL + s), 1), mbar_init(bar(DT_VEMPTY + s), 1);
+        for (int s = 0; s < PH_STAGES; ++s) {
+            mbar_init(bar(PH_KFULL + s), 1), mbar_init(bar(PH_KEMPTY + s), 1);
+            mbar_init(bar(PH_VFULL + s), 1), mbar_init(bar(PH_VEMPTY + s), 1);
         }
-        mbar_init(bar(DT_SFULL), 1), mbar_init(bar(DT_SFREE), 128);
-        mbar_init(bar(DT_PFULL), 128), mbar_init(bar(DT_PVDONE), 1);
-        mbar_init(bar(DT_QFULL), 32);
+        for (int b = 0; b < NBUF; ++b) {
+            mbar_init(bar(PH_SFULL + b), 1), mbar_init(bar(PH_SFREE + b), 128);
+            mbar_init(bar(PH_PFULL + b), 128), mbar_init(bar(PH_PVDONE + b), 1);
+        }
+        mbar_init(bar(PH_QFULL), 32);
         *abort_flag = 0;
         mbar_init_fence();
     }
-    for (int idx = tid; idx < 2 * DT_OPER / 16; idx += PH_THREADS) reinterpret_cast<uint4*>(qbuf)[idx] = make_uint4(0, 0, 0, 0);
+    for (int idx = tid; idx < (1 + NBUF) * DT_OPER / 16; idx += PH_THREADS) reinterpret_cast<uint4*>(qbuf)[idx] = make_uint4(0, 0, 0, 0);
     for (int rr = tid; rr < p.n_rows; rr += PH_THREADS) {
         int cnt = p.counts ? p.counts[rr] : p.columns;
         cnt = cnt > p.columns ? p.columns : (cnt < 0 ? 0 : cnt);
@@ -218,21 +239,21 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
         };
         // A tile's keys are asked for one tile before the values of the tile before it: the keys' place frees early (after
         // the first product), the values' late (after the second), and neither request waits behind the other's place.
-        // The tile's scales travel with its keys (the softmax needs them with the scores), into one of four places in
-        // turn: the place of tile t is written again for tile t + 4, whose keys are asked for after the scores of tile
-        // t + 2 are complete, which were issued after every softmax thread had read the scores of tile t + 1.
+        // The tile's scales travel with its keys (the softmax needs them with the scores), into one of eight places in
+        // turn: the place of tile t is written again for tile t + 8, whose keys are asked for after the scores of tile
+        // t + 3 are complete, which were issued after every softmax thread had read the scores of tile t + 1.
         int pg0[DT_NB], pg1[DT_NB];
         fetch_pages(w0, pg0);
         int t = 0, v_slot = 0;
         bool ok = true;
         auto ask_values = [&](int tv, int slot0) {
-            const int stage = tv % DT_STAGES;
-            ok = dt_wait<100>(bar(DT_VEMPTY + stage), (uint32_t)((tv / DT_STAGES) & 1) ^ 1u, abort_flag);
+            const int stage = tv % PH_STAGES;
+            ok = dt_wait<100>(bar(PH_VEMPTY + stage), (uint32_t)((tv / PH_STAGES) & 1) ^ 1u, abort_flag);
             ok = __all_sync(FULLMASK, ok);
             if (!ok) return;
             if (lane == 0) {
-                mbar_expect_tx(bar(DT_VFULL + stage), (uint32_t)DT_KV_BYTES);
-                tma_load_3d(smem_addr(stages + stage * PH_STAGE) + DT_KV_BYTES, &vmap, 0, slot0, 0, bar(DT_VFULL + stage));
+                mbar_expect_tx(bar(PH_VFULL + stage), (uint32_t)DT_KV_BYTES);
+                tma_load_3d(smem_addr(stages + stage * PH_STAGE) + DT_KV_BYTES, &vmap, 0, slot0, 0, bar(PH_VFULL + stage));
             }
             __syncwarp();
         };
@@ -246,8 +267,8 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 const int pgb = __shfl_sync(FULLMASK, pgs, i & 31);
                 const uint32_t tile16 = (uint32_t)(w0.u.begin >> 4) + (uint32_t)i;
                 const int slot0 = pgb >= 0 ? (int)((int64_t)pgb * p.page + ((tile16 % tpp) << 4)) : (int)p.slots;
-                const int stage = t % DT_STAGES;
-                ok = dt_wait<100>(bar(DT_KEMPTY + stage), (uint32_t)((t / DT_STAGES) & 1) ^ 1u, abort_flag);
+                const int stage = t % PH_STAGES;
+                ok = dt_wait<100>(bar(PH_KEMPTY + stage), (uint32_t)((t / PH_STAGES) & 1) ^ 1u, abort_flag);
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 float* scs = scales + (t % PH_SCALE_SLOTS) * 256;
@@ -256,7 +277,7 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                     __syncwarp();
                 }
                 if (lane == 0) {
-                    const uint32_t full = bar(DT_KFULL + stage);
+                    const uint32_t full = bar(PH_KFULL + stage);
                     if (smode == 2 && pgb >= 0) {
                         mbar_expect_tx(full, (uint32_t)DT_KV_BYTES + 64u);
                         bulk_load(smem_addr(scs), p.key_scales + (int64_t)pgb * PH_HEADS, 32u, full);
@@ -284,37 +305,17 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
         if (ok && t > 0) ask_values(t - 1, v_slot);
         if (!ok) {              // leaving early: the copies in flight land first (bounded)
             where = 0x610;
-            for (int tt = t > DT_STAGES ? t - DT_STAGES : 0; tt <= t; ++tt) {
-                mbar_wait(bar(DT_KFULL + tt % DT_STAGES), (uint32_t)(tt / DT_STAGES) & 1u, 20000000ull);
-                if (tt + 1 < t) mbar_wait(bar(DT_VFULL + tt % DT_STAGES), (uint32_t)(tt / DT_STAGES) & 1u, 20000000ull);
+            for (int tt = t > PH_STAGES ? t - PH_STAGES : 0; tt <= t; ++tt) {
+                mbar_wait(bar(PH_KFULL + tt % PH_STAGES), (uint32_t)(tt / PH_STAGES) & 1u, 20000000ull);
+                if (tt + 1 < t) mbar_wait(bar(PH_VFULL + tt % PH_STAGES), (uint32_t)(tt / PH_STAGES) & 1u, 20000000ull);
             }
         }
     } else if (warp == 5) {
-        // -- query preparation and MMA issue ------------------------------------------------------------------------------
+        // -- the rows' queries and the first products, S = Q K^T of every tile in order -----------------------------------------
         const uint32_t idesc_s = idesc_f8(false, 128, 128);
-        const uint32_t idesc_o = idesc_f8(true, 128, DT_D);
         const float sl2 = p.scale * LOG2E * (smode == 0 ? p.key_multiplier : 1.f);
         const int qt = lane & 3, jr = lane >> 2;
-        bool ok = true, have_prev = false, prev_acc = false;
-        int prev_t = 0;
-        auto issue_pv = [&]() {             // O (+)= P V of tile prev_t
-            const int pstage = prev_t % DT_STAGES;
-            ok = dt_wait<32>(bar(DT_PFULL), (uint32_t)prev_t & 1u, abort_flag) &&
-                 dt_wait<32>(bar(DT_VFULL + pstage), (uint32_t)(prev_t / DT_STAGES) & 1u, abort_flag);
-            ok = __all_sync(FULLMASK, ok);
-            if (!ok) return;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint32_t pa = smem_addr(pbuf), va = smem_addr(stages + pstage * PH_STAGE + DT_KV_BYTES);
-#pragma unroll
-                for (int kk = 0; kk < 4; ++kk)
-                    umma_f8(tmem + DT_O, smem_desc_sw128(pa + kk * 32, 0, 1024), smem_desc_sw128(va + kk * 4096, 16, 1024),
-                            idesc_o, prev_acc || kk > 0);
-                umma_commit(bar(DT_VEMPTY + pstage));
-                umma_commit(bar(DT_PVDONE));
-            }
-            __syncwarp();
-        };
+        bool ok = true;
         // A window row's queries as the A operand: row j of kv head h's group (column j / G, head h G + j % G) goes to
         // lanes 16 h + j (hi term) and 16 h + 8 + j (lo term); 4 lanes a row, one kv head a pass.
         auto store_q = [&](const PhUnit& u, int qn) {
@@ -374,32 +375,28 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 if (qt == 0) qfac[(qn & 1) * 64 + h * 8 + jr] = down * sl2;
             }
             fence_proxy_async();
-            mbar_arrive(bar(DT_QFULL));
+            mbar_arrive(bar(PH_QFULL));
             __syncwarp();
         };
         PhWalk w;
         w.begin(p, rows);
         int t = 0, qn = 0, q_row = -1;
         while (w.live && ok) {
-            const int stage = t % DT_STAGES;
+            const int stage = t % PH_STAGES, sb = t % NBUF;
             if (w.i == 0 && w.u.r != q_row) {
-                // Another window row: the last unit's final second product first (its epilogue waits for it), then the
-                // row's queries over the last row's, once the last scores are out of tensor memory (every first product
-                // that read the old queries has completed, and every softmax thread has passed its wait for them, so
-                // the queries' barrier never runs two phases ahead of a waiter).
-                if (have_prev) {
-                    issue_pv();
-                    have_prev = false;
+                // Another window row: once the last tile's probabilities are written, every first product that read the old
+                // queries has completed and every softmax thread has passed its wait for them (the queries' barrier never
+                // runs two phases ahead of a waiter): the row's queries go over the last row's.
+                if (t > 0) {
+                    ok = dt_wait<32>(bar(PH_PFULL + (t - 1) % NBUF), (uint32_t)((t - 1) / NBUF) & 1u, abort_flag);
+                    ok = __all_sync(FULLMASK, ok);
                     if (!ok) break;
                 }
-                ok = dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag);
-                ok = __all_sync(FULLMASK, ok);
-                if (!ok) break;
                 store_q(w.u, qn);
                 ++qn, q_row = w.u.r;
             }
-            ok = dt_wait<32>(bar(DT_KFULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag) &&
-                 dt_wait<32>(bar(DT_SFREE), (uint32_t)(t & 1) ^ 1u, abort_flag);
+            ok = dt_wait<32>(bar(PH_KFULL + stage), (uint32_t)(t / PH_STAGES) & 1u, abort_flag) &&
+                 dt_wait<32>(bar(PH_SFREE + sb), (uint32_t)((t / NBUF) & 1) ^ 1u, abort_flag);
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             tc_fence_after();
@@ -407,18 +404,45 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 const uint32_t qa = smem_addr(qbuf), ka = smem_addr(stages + stage * PH_STAGE);
 #pragma unroll
                 for (int kk = 0; kk < DT_D / 32; ++kk)
-                    umma_f8(tmem, smem_desc_sw128(qa + kk * 32, 0, 1024), smem_desc_sw128(ka + kk * 32, 0, 1024), idesc_s, kk > 0);
-                umma_commit(bar(DT_SFULL));
-                umma_commit(bar(DT_KEMPTY + stage));
+                    umma_f8(tmem + 128u * sb, smem_desc_sw128(qa + kk * 32, 0, 1024), smem_desc_sw128(ka + kk * 32, 0, 1024),
+                            idesc_s, kk > 0);
+                umma_commit(bar(PH_SFULL + sb));
+                umma_commit(bar(PH_KEMPTY + stage));
             }
             __syncwarp();
-            if (have_prev) issue_pv();
-            have_prev = true, prev_t = t, prev_acc = w.i > 0;
             w.next(p, rows);
             ++t;
         }
-        if (ok && have_prev) issue_pv();
         if (!ok) where = 0x620;
+    } else if (warp == 6) {
+        // -- the second products, O (+)= P V of every tile in order, from a warp of their own: issuing a tile's eight MMAs
+        //    and four commits from one thread took longer than the tile's softmax -------------------------------------------
+        const uint32_t idesc_o = idesc_f8(true, 128, DT_D);
+        bool ok = true;
+        PhWalk w;
+        w.begin(p, rows);
+        int t = 0;
+        while (w.live && ok) {
+            const int pstage = t % PH_STAGES, pb = t % NBUF;
+            ok = dt_wait<32>(bar(PH_PFULL + pb), (uint32_t)(t / NBUF) & 1u, abort_flag) &&
+                 dt_wait<32>(bar(PH_VFULL + pstage), (uint32_t)(t / PH_STAGES) & 1u, abort_flag);
+            ok = __all_sync(FULLMASK, ok);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t pa = smem_addr(pbufs + pb * DT_OPER), va = smem_addr(stages + pstage * PH_STAGE + DT_KV_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+                    umma_f8(tmem + PH_O, smem_desc_sw128(pa + kk * 32, 0, 1024), smem_desc_sw128(va + kk * 4096, 16, 1024),
+                            idesc_o, w.i > 0 || kk > 0);
+                umma_commit(bar(PH_VEMPTY + pstage));
+                umma_commit(bar(PH_PVDONE + pb));
+            }
+            __syncwarp();
+            w.next(p, rows);
+            ++t;
+        }
+        if (!ok) where = 0x630;
     } else {
         // -- softmax: thread = TMEM lane 32 * warp + lane.  Lane group lg (16 lanes) is kv head lg: lanes 0-7 hold the hi
         //    terms of its 8 query rows, lanes 8-15 their lo terms, and its columns of a tile are [16 lg, 16 lg + 16), the
@@ -435,8 +459,8 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
         const float vmul = smode == 0 ? p.value_multiplier : 1.f;
         const float lo_unscale = second ? 1.f / 16.f : 1.f;     // this lane's outputs: the lo probabilities were stored times 16
         const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
-        unsigned char* pb_hi = pbuf + row_hi * 128 + ((lg ^ (row_hi & 7)) << 4) + cofs;
-        unsigned char* pb_lo = pbuf + row_lo * 128 + ((lg ^ (row_lo & 7)) << 4) + cofs;
+        const int pb_hi = row_hi * 128 + ((lg ^ (row_hi & 7)) << 4) + cofs;       // this thread's bytes of a P tile
+        const int pb_lo = row_lo * 128 + ((lg ^ (row_lo & 7)) << 4) + cofs;
         bool ok = true;
         PhWalk w;
         w.begin(p, rows);
@@ -447,7 +471,7 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
             after.next_unit(p, rows);
             const int prow_first = p.offsets ? p.offsets[w.u.r] - p.offsets[0] : w.u.r * p.columns;
             if (w.u.r != q_row) {
-                ok = dt_wait(bar(DT_QFULL), (uint32_t)qn & 1u, abort_flag);
+                ok = dt_wait(bar(PH_QFULL), (uint32_t)qn & 1u, abort_flag);
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 a_r = qfac[(qn & 1) * 64 + lg * 8 + jr];
@@ -458,14 +482,14 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
             const int first32 = w.u.first > 0x7fffffffLL ? 0x7fffffff : (int)w.u.first;
             float m_run = -INFINITY, l_run = 0.f;
             for (int i = 0; i < w.u.ntiles; ++i, ++t) {
-                const int stage = t % DT_STAGES;
+                const int stage = t % PH_STAGES, sb = t % NBUF;
                 const int tile_pos = (int)w.u.begin + i * PH_TILE;
-                ok = dt_wait(bar(DT_SFULL), (uint32_t)t & 1u, abort_flag);
+                ok = dt_wait(bar(PH_SFULL + sb), (uint32_t)(t / NBUF) & 1u, abort_flag);
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 tc_fence_after();
                 if (tile_pos + PH_TILE > w.u.L) {
-                    ok = dt_wait(bar(DT_VFULL + stage), (uint32_t)(t / DT_STAGES) & 1u, abort_flag);
+                    ok = dt_wait(bar(PH_VFULL + stage), (uint32_t)(t / PH_STAGES) & 1u, abort_flag);
                     ok = __all_sync(FULLMASK, ok);
                     if (!ok) break;
                     // the row's last page is partly filled: its value rows past the last position hold whatever the
@@ -482,9 +506,9 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 float s[8];
                 {
                     float both[32];
-                    tmem_ld32(tmem + lane_base + (uint32_t)((lg >> 1) * 32), both);
+                    tmem_ld32(tmem + lane_base + 128u * sb + (uint32_t)((lg >> 1) * 32), both);
                     tc_fence_before();
-                    mbar_arrive(bar(DT_SFREE));
+                    mbar_arrive(bar(PH_SFREE + sb));
 #pragma unroll
                     for (int c = 0; c < 8; ++c) {
                         const float m0 = (lg & 1) ? both[16 + c] : both[c], m1 = (lg & 1) ? both[24 + c] : both[8 + c];
@@ -524,8 +548,8 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                 const bool rescale = moved && top != m_run && i > 0;
                 m_run = top;
 
-                // the P tile is free (and the outputs settled) once the second product of the tile before has landed
-                ok = dt_wait(bar(DT_PVDONE), (uint32_t)(t & 1) ^ 1u, abort_flag);
+                // this tile's P tile is free once the second product that read it last (NBUF tiles before) has landed
+                ok = dt_wait(bar(PH_PVDONE + sb), (uint32_t)((t / NBUF) & 1) ^ 1u, abort_flag);
                 ok = __all_sync(FULLMASK, ok);
                 if (!ok) break;
                 float psum = 0.f;
@@ -546,24 +570,28 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
                     if (c2 & 1) wh[c2 >> 1] |= h2 << 16, wl[c2 >> 1] |= l2 << 16;
                     else wh[c2 >> 1] = h2, wl[c2 >> 1] = l2;
                 }
-                *reinterpret_cast<uint2*>(pb_hi) = make_uint2(wh[0], wh[1]);
-                *reinterpret_cast<uint2*>(pb_lo) = make_uint2(wl[0], wl[1]);
+                *reinterpret_cast<uint2*>(pbufs + sb * DT_OPER + pb_hi) = make_uint2(wh[0], wh[1]);
+                *reinterpret_cast<uint2*>(pbufs + sb * DT_OPER + pb_lo) = make_uint2(wl[0], wl[1]);
                 l_run = l_run * alpha + psum * rv;
 
                 if (__any_sync(FULLMASK, rescale)) {
-                    // a maximum moved: the warp brings its output lanes to the new reference
+                    // a maximum moved: the warp brings its output lanes to the new reference, once the second product of
+                    // the tile before has landed (the products complete in order: the outputs are settled then)
+                    ok = dt_wait(bar(PH_PVDONE + (t - 1) % NBUF), (uint32_t)((t - 1) / NBUF) & 1u, abort_flag);
+                    ok = __all_sync(FULLMASK, ok);
+                    if (!ok) break;
                     tc_fence_after();
-                    dt_rescale(tmem + lane_base + DT_O, alpha);
+                    dt_rescale(tmem + lane_base + PH_O, alpha);
                 }
                 fence_proxy_async();
                 tc_fence_before();
-                mbar_arrive(bar(DT_PFULL));
+                mbar_arrive(bar(PH_PFULL + sb));
             }
             if (!ok) break;
 
             // -- the unit's result: its last second product, hi + lo of the outputs, one row a pair of lanes ------------------
             const int tl = t - 1;
-            ok = dt_wait(bar(DT_PVDONE), (uint32_t)tl & 1u, abort_flag);
+            ok = dt_wait(bar(PH_PVDONE + tl % NBUF), (uint32_t)(tl / NBUF) & 1u, abort_flag);
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             tc_fence_after();
@@ -576,8 +604,8 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
 #pragma unroll
             for (int c4 = 0; c4 < 2; ++c4) {
                 float oa[32], ob[32];
-                tmem_ld32(tmem + lane_base + DT_O + 32u * c4, oa);
-                tmem_ld32(tmem + lane_base + DT_O + 64u + 32u * c4, ob);
+                tmem_ld32(tmem + lane_base + PH_O + 32u * c4, oa);
+                tmem_ld32(tmem + lane_base + PH_O + 64u + 32u * c4, ob);
                 float keep[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
@@ -610,7 +638,7 @@ decode_ph_kernel(const crit_b200_attend_params p, const __grid_constant__ CUtens
     if (where && p.status) atomicExch(p.status, where);
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) tmem_dealloc(tmem, DT_COLUMNS);
+    if (warp == 0) tmem_dealloc(tmem, PH_COLUMNS);
 }
 
 }  // namespace crit_b200

@@ -287,7 +287,10 @@ def test_whole_page_rows_edge_cases(pk):
     assert torch.equal(got.cpu()[keep], clean.cpu()[keep])
     marked = torch.full_like(clean, 7.0)
     some = cache.attend(q, rows, starts, firsts, 4, counts=[4, 0, 9], out=marked, engine="tcgen05p", chunk=256)
-    assert torch.equal(some[0:4], clean[0:4]) and torch.equal(some[8:12], clean[8:12]) and bool((some[4:8] == 7.0).all())
+    # (the launch's tiles are dealt out evenly, so other rows in the launch mean other units: the same attention, not the same bits)
+    assert bool((some[4:8] == 7.0).all())
+    assert float((some[0:4].float() - clean[0:4].float()).abs().max()) <= 1e-2
+    assert float((some[8:12].float() - clean[8:12].float()).abs().max()) <= 1e-2
     qh = queries(12, 16, 128, 4, torch.float16)
     cache16 = Cache("fp8:row", 8, 128, 128, 16, [200, 1300, 40], spare=8)
     lse = torch.empty(12, 16, device="cuda")
@@ -362,7 +365,7 @@ def test_tma_and_cp_async_staging_give_the_same_bits(pk, kind, hq, hkv, d):
     rows, starts, firsts, counts = [0, 1, 2, 3, 4], [0, 5, 10, 15, 20], [125, 59, 0, 400, 990], [5, 5, 1, 3, 6]
     q = queries(26, hq, d, 3, torch.float16 if kind == "fp16" else torch.bfloat16)
     lse_a, lse_b = torch.empty(26, hq, device="cuda"), torch.empty(26, hq, device="cuda")
-    tma = cache.attend(q, rows, starts, firsts, 6, counts=counts, lse=lse_a, chunk=128)
+    tma = cache.attend(q, rows, starts, firsts, 6, counts=counts, lse=lse_a, chunk=128, engine="mma.sync")
     plain = cache.attend(q, rows, starts, firsts, 6, counts=counts, lse=lse_b, chunk=128, staging="cp.async")
     tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
     assert torch.equal(tma[tokens], plain[tokens]) and torch.equal(lse_a[tokens], lse_b[tokens])
