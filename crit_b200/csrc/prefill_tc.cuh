@@ -31,16 +31,16 @@ namespace crit_b200 {
 constexpr int TC_ROWS = 128;       // query rows a block holds
 constexpr int TC_BN = 64;          // positions a tile holds
 constexpr int TC_D = 128;          // head width
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 224;     // 4 softmax warps, a producer warp, a warp for each product's MMAs
 constexpr int TC_Q_BYTES = 2 * TC_ROWS * 128;               // two 64-value halves of [128 rows][128 bytes]
 constexpr int TC_K_BYTES = 2 * TC_BN * 128;                 // two halves of [64 positions][128 bytes]
 constexpr int TC_STAGE = 2 * TC_K_BYTES;                    // keys, values
-constexpr int TC_SMEM = TC_Q_BYTES + 2 * TC_STAGE + 128;
+constexpr int TC_SMEM = TC_Q_BYTES + 2 * TC_STAGE + 256;     // 16 mbarriers, the TMEM address, the abort flag
 constexpr uint32_t TC_COLUMNS = 256;                        // TMEM: scores at 0..63 and 64..127, outputs at 128..255
 constexpr uint32_t TC_O = 128;
 constexpr float TC_LAZY = 8.f;
 
-enum { TC_KFULL = 0, TC_VFULL = 2, TC_KEMPTY = 4, TC_VEMPTY = 6, TC_SFULL = 8, TC_SFREE = 10, TC_PFULL = 12, TC_PVDONE = 13 };
+enum { TC_KFULL = 0, TC_VFULL = 2, TC_KEMPTY = 4, TC_VEMPTY = 6, TC_SFULL = 8, TC_SFREE = 10, TC_PFULL = 12, TC_PVDONE = 13, TC_PFREE = 14 };
 
 __device__ __forceinline__ void tc_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -67,8 +67,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
     unsigned char* stages = smem + TC_Q_BYTES;
     unsigned char* small = stages + 2 * TC_STAGE;
     const uint32_t bars = smem_addr(small);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(small + 112);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(small + 116);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(small + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(small + 132);
     auto bar = [&](int which) { return bars + (uint32_t)which * 8u; };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -90,6 +90,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
             mbar_init(bar(TC_SFULL + b), 1), mbar_init(bar(TC_SFREE + b), 128);
         }
         mbar_init(bar(TC_PFULL), 128), mbar_init(bar(TC_PVDONE), 1);
+        mbar_init(bar(TC_PFREE), 1), mbar_init(bar(TC_PFREE + 1), 1);
         *abort_flag = 0;
         mbar_init_fence();
     }
@@ -161,13 +162,39 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
         }
         if (!ok) where = 0x110;
     } else if (warp == 5) {
-        // -- MMA issue -------------------------------------------------------------------------------------------------------
+        // -- the first products, S = Q K^T of every tile ------------------------------------------------------------------------
         const uint32_t idesc_s = idesc_f16(BF16, false, TC_ROWS, TC_BN);
-        const uint32_t idesc_o = idesc_f16(BF16, true, TC_ROWS, TC_D);
         // The operands' descriptors are made once: a step of 16 bytes in the address is a step of 1 in the descriptor, so a
         // tile's MMAs take theirs with one addition each (the issue of the twelve MMAs of a tile is what bounds the block).
         const uint64_t q_desc = smem_desc_sw128(smem_addr(qs), 0, 1024);
         const uint64_t k_desc0 = smem_desc_sw128(smem_addr(stages), 0, 1024);
+        bool ok = true;
+        for (int i = 0; i < ntiles && ok; ++i) {
+            const int s = i & 1;
+            // (a tile's probabilities sit over its scores: the buffer is free for the scores of tile i once the second
+            // product of tile i - 2 has read them; the two products are issued by different warps)
+            ok = tc_wait(bar(TC_KFULL + s), (uint32_t)(i >> 1) & 1u, abort_flag) &&
+                 tc_wait(bar(TC_SFREE + s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag) &&
+                 tc_wait(bar(TC_PFREE + s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag);
+            ok = __all_sync(FULLMASK, ok);
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint64_t kd = k_desc0 + (uint64_t)((s * TC_STAGE) >> 4);
+#pragma unroll
+                for (int ks = 0; ks < TC_D / 16; ++ks)
+                    umma_f16(tmem + (uint32_t)(s * TC_BN), q_desc + (uint64_t)(((ks >> 2) * (TC_ROWS * 128) + (ks & 3) * 32) >> 4),
+                             kd + (uint64_t)(((ks >> 2) * (TC_BN * 128) + (ks & 3) * 32) >> 4), idesc_s, ks > 0);
+                umma_commit(bar(TC_SFULL + s));
+                umma_commit(bar(TC_KEMPTY + s));
+            }
+            __syncwarp();
+        }
+        if (!ok) where = 0x120;
+    } else if (warp == 6) {
+        // -- the second products, O (+)= P V of every tile, from a warp of their own (one thread issuing a tile's twelve MMAs
+        //    was what bounded the block) -----------------------------------------------------------------------------------
+        const uint32_t idesc_o = idesc_f16(BF16, true, TC_ROWS, TC_D);
         const uint64_t v_desc0 = smem_desc_sw128(smem_addr(stages) + TC_K_BYTES, TC_BN * 128, 1024);
         bool ok = true;
         auto issue_pv = [&](int t) {        // O (+)= P V of tile t
@@ -186,30 +213,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
                 for (int kk = 1; kk < TC_BN / 16; ++kk) umma_f16_ts(tmem + TC_O, pa + kk * 8, vd + (uint64_t)(kk * 2048 >> 4), idesc_o, true);
                 umma_commit(bar(TC_VEMPTY + (t & 1)));
                 umma_commit(bar(TC_PVDONE));
+                umma_commit(bar(TC_PFREE + (t & 1)));
             }
             __syncwarp();
         };
-        for (int i = 0; i < ntiles && ok; ++i) {
-            const int s = i & 1;
-            ok = tc_wait(bar(TC_KFULL + s), (uint32_t)(i >> 1) & 1u, abort_flag) &&
-                 tc_wait(bar(TC_SFREE + s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag);
-            ok = __all_sync(FULLMASK, ok);
-            if (!ok) break;
-            tc_fence_after();
-            if (lane == 0) {
-                const uint64_t kd = k_desc0 + (uint64_t)((s * TC_STAGE) >> 4);
-#pragma unroll
-                for (int ks = 0; ks < TC_D / 16; ++ks)
-                    umma_f16(tmem + (uint32_t)(s * TC_BN), q_desc + (uint64_t)(((ks >> 2) * (TC_ROWS * 128) + (ks & 3) * 32) >> 4),
-                             kd + (uint64_t)(((ks >> 2) * (TC_BN * 128) + (ks & 3) * 32) >> 4), idesc_s, ks > 0);
-                umma_commit(bar(TC_SFULL + s));
-                umma_commit(bar(TC_KEMPTY + s));
-            }
-            __syncwarp();
-            if (i > 0) issue_pv(i - 1);
-        }
-        if (ok && ntiles > 0) issue_pv(ntiles - 1);
-        if (!ok) where = 0x120;
+        for (int i = 0; i < ntiles && ok; ++i) issue_pv(i);
+        if (!ok) where = 0x130;
     } else {
         // -- softmax: thread = query row row0 + tid = TMEM lane tid -------------------------------------------------------------
         const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
