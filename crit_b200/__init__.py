@@ -375,8 +375,9 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     out [tokens][heads][value_dim] (q's dtype) at the rows' tokens and lse [tokens][heads] FP32 when given; returns out.
     chunk: positions per split (default chunk_for()); partitions: the most splits a partial row may take (the
     workspace's, see partitions()).  piece, fused, vsplit, tile, num_warps, num_stages, maxnreg, flash and ramp are
-    accepted and change nothing (one launch shape per geometry).  parents, blocks, fresh, sinks, sliding and derive
-    are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
+    accepted and change nothing (one launch shape per geometry).  parents [tokens]: each token's parent column in its
+    row, -1 for none (a draft tree in topological order): a column then sees the context before its row's first position,
+    itself and its ancestors (the m16n8k16 kernel).  blocks, fresh, sinks, sliding and derive are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
     None (TMA tiled loads for 16-bit pages of 128- or 256-wide heads, cp.async otherwise: what measured faster), "tma"
     (TMA wherever the geometry allows it) or "cp.async" (never TMA); the same bits either way.  persistent: a fixed
     number of blocks walk a work list built on the device from the rows' lengths, instead of one block per (split, kv
@@ -386,7 +387,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     shards: a crit_b200.dist.ShardMerge: these pages hold one KV range of a context sharded over the ranks; every
     split state stays in the workspace, the fold of this rank's splits is stored into every rank's exchange buffer and
     out / lse get the merge over all ranks (three launches: decode, fold + push, wait + merge)."""
-    _refuse(parents=parents, blocks=blocks, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
+    _refuse(blocks=blocks, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
     T, hq, d = q.shape
@@ -410,6 +411,15 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
         raise ValueError("pages are contiguous [slots][kv_heads][dim] storage")
     device = q.device
     positions = tables.shape[1] * page
+    if parents is not None:
+        # a draft tree: parents [tokens] is each token's parent column in its row, -1 for none (topological order)
+        if engine not in (None, "mma.sync"):
+            raise NotImplementedError("draft trees (parents) are served by the m16n8k16 kernel: engine None or mma.sync")
+        parents = parents.reshape(-1)
+        if parents.dtype not in (torch.int32, torch.int64) or parents.numel() != T:
+            raise ValueError("parents are int32 or int64, one per token of q")
+        parents = _cuda(parents, "parents").to(torch.int32).contiguous()
+        engine = "mma.sync"
     chosen = engine is None
     if chosen and (shards is not None or persistent or staging is not None):
         engine = "mma.sync"               # what those arguments are about
@@ -453,6 +463,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])
+    p.parents = _ptr(parents)
     lib = _lib.load()
     if shards is not None:
         if lse is None:

@@ -5,7 +5,7 @@ from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int32, c_int6
 from pathlib import Path
 
 LIBRARY = Path(__file__).resolve().parent / "_native" / "libcrit_b200.so"
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 KIND_16BIT, KIND_FP8, KIND_FP8_ROW, KIND_INT8, KIND_FP8_PAGE = range(5)
 DTYPE_BF16, DTYPE_FP16, DTYPE_FP32 = range(3)
@@ -44,7 +44,8 @@ class AttendParams(Structure):
                 ("q_heads", c_int32), ("kv_heads", c_int32), ("head_dim", c_int32), ("value_dim", c_int32),
                 ("page", c_int32), ("kind", c_int32), ("page_dtype", c_int32), ("q_dtype", c_int32),
                 ("chunk", c_int32), ("max_splits", c_int32), ("flags", c_int32),
-                ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float)]
+                ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float),
+                ("parents", c_void_p)]
 
 
 class MergeShardsParams(Structure):

@@ -97,9 +97,11 @@ class DeviceAttention:
         step already); each token sees its sequence's positions up to its own.  lse: also return each token's
         log-sum-exp ([tokens][heads] FP32).  Returns out [tokens][heads][value dim] in the queries' dtype (and lse)."""
         import torch
-        if blocks is not None or parents is not None or sinks is not None or sliding or latent:
+        if blocks is not None or sinks is not None or sliding or latent:
             raise NotImplementedError("crit_b200's attention reads causal windows over the whole context: no block lists, "
-                                      "draft trees, sinks, sliding windows or latent attention yet")
+                                      "sinks, sliding windows or latent attention yet")
+        if parents is not None and getattr(batch, "prompt", False):
+            raise NotImplementedError("draft trees (parents) are read in window rows, not in a staged prompt chunk")
         if not queries.is_cuda:
             raise RuntimeError("crit_b200's attention runs on CUDA devices only (there is no CPU path)")
         scale = scale if scale is not None else queries.shape[-1] ** -0.5
@@ -113,22 +115,22 @@ class DeviceAttention:
             rows, cols = batch.rows, batch.width + 1
             meta = Windows(pool.round_tables, batch.slots_t[:rows].to(torch.int32), batch.starts_t[:rows], None,
                            batch.frontier_t, cols)
-            self._windows(layer, q, pool, meta, scale, out, found)
+            self._windows(layer, q, pool, meta, scale, out, found, parents)
         elif getattr(pool, "step_rows", 0):
             n = len(pool.windows)
             if n:
                 bounds = [batch.row(r)[2] for r in pool.windows]
                 meta = Windows(pool.d_tables, pool.d_rows[:n], pool.d_starts[:n], pool.d_counts[:n], pool.d_firsts[:n],
                                pool.window, offsets=pool.d_offsets[:n], packed=bounds, total=q.shape[0])
-                self._windows(layer, q, pool, meta, scale, out, found)
+                self._windows(layer, q, pool, meta, scale, out, found, parents)
             chosen = set(pool.windows)
-            self._prompts(layer, q, pool, batch, [r for r in range(batch.rows) if r not in chosen], scale, out, found)
+            self._prompts(layer, q, pool, batch, [r for r in range(batch.rows) if r not in chosen], scale, out, found, parents)
         else:
             short = [r for r in range(batch.rows) if batch.row(r)[2] <= pool.window]
             if short:
-                self._windows(layer, q, pool, self._step_windows(pool, batch, short, q.device), scale, out, found)
+                self._windows(layer, q, pool, self._step_windows(pool, batch, short, q.device), scale, out, found, parents)
             self._prompts(layer, q, pool, batch, [r for r in range(batch.rows) if batch.row(r)[2] > pool.window],
-                          scale, out, found)
+                          scale, out, found, parents)
         out = out if out.dtype == queries.dtype else out.to(queries.dtype)
         return (out, found) if lse else out
 
@@ -147,7 +149,7 @@ class DeviceAttention:
         self._steps["windows"] = (key, found)
         return found
 
-    def _windows(self, layer, q, pool, meta, scale, out, found):
+    def _windows(self, layer, q, pool, meta, scale, out, found, parents=None):
         pages = pool.layer_pages(layer)
         scaled = len(pages) == 4
         multipliers = pool.scale_values[pool.layers[layer]] if pool.dtype == "fp8" else (1.0, 1.0)
@@ -156,6 +158,8 @@ class DeviceAttention:
         geometry = (pool.dtype, pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, meta.columns)
         # the kernel the step's windows run on: the kernels' choice for the whole step, or the one the option names
         named = kernels.engine_for(*geometry, len(meta), positions, None if self.window_engine == "auto" else self.window_engine)
+        if parents is not None:
+            named = "mma.sync"             # draft trees are masked by the m16n8k16 kernel
         chunk = self.chunk or kernels.chunk_for(pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, pool.page, pool.dtype,
                                                 named, meta.columns)
         if self.partitions:
@@ -187,12 +191,15 @@ class DeviceAttention:
                            tokens=tokens if offsets is not None else None,
                            key_scales=pages[2] if scaled else None, value_scales=pages[3] if scaled else None,
                            multipliers=multipliers, scale=scale, chunk=chunk, out=out, lse=found, workspace=workspace,
-                           engine=engine(cut.stop - cut.start))
+                           engine=engine(cut.stop - cut.start), parents=parents)
 
     # -- prompt rows -----------------------------------------------------------------------------------------------------
-    def _prompts(self, layer, q, pool, batch, rows, scale, out, found):
+    def _prompts(self, layer, q, pool, batch, rows, scale, out, found, parents=None):
         if not rows:
             return
+        if parents is not None:
+            raise NotImplementedError("draft trees (parents) are read in window rows: a row of more than the pool's "
+                                      f"window of {pool.window} columns is a prompt row")
         if self.prompt_reader == "prefill" and self._prefill_serves(pool, q):
             pages = pool.layer_pages(layer)
             scaled = len(pages) == 4

@@ -13,6 +13,15 @@ template <typename TIN>
 __device__ __forceinline__ void load_row(const TIN* src, int dim, int lane, float (&x)[8]) {
     // dim <= 256: lane holds elements lane*per .. lane*per+per-1, per = dim / 32 (contiguous, vectorisable)
     const int per = dim >> 5;
+    if (sizeof(TIN) == 2 && (per == 4 || per == 8) && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+        // 16-bit rows of 128 or 256 elements: the lane's elements in one 8- or 16-byte load
+        alignas(16) TIN v[8];
+        if (per == 4) *reinterpret_cast<uint2*>(v) = *reinterpret_cast<const uint2*>(src + lane * 4);
+        else *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(src + lane * 8);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = i < per ? to_float<TIN>(v[i]) : 0.f;
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) x[i] = i < per ? to_float<TIN>(src[lane * per + i]) : 0.f;
 }
@@ -45,20 +54,37 @@ __device__ __forceinline__ void store_16bit(TPAGE* dst, const float (&x)[8], int
         if (i < per) dst[lane * per + i] = from_float<TPAGE>(x[i]);
 }
 
-__device__ __forceinline__ void store_e4m3(uint8_t* dst, const float (&x)[8], float div, int per, int lane) {
+// A lane's `per` consecutive codes as one store where they fill a word or two (heads of 128 or 256), else byte by byte.
+__device__ __forceinline__ void store_codes(uint8_t* dst, const uint8_t (&c)[8], int per, int lane) {
+    if (per == 4) {
+        *reinterpret_cast<uint32_t*>(dst + lane * 4) = (uint32_t)c[0] | ((uint32_t)c[1] << 8) | ((uint32_t)c[2] << 16) | ((uint32_t)c[3] << 24);
+    } else if (per == 8) {
+        *reinterpret_cast<uint2*>(dst + lane * 8) =
+            make_uint2((uint32_t)c[0] | ((uint32_t)c[1] << 8) | ((uint32_t)c[2] << 16) | ((uint32_t)c[3] << 24),
+                       (uint32_t)c[4] | ((uint32_t)c[5] << 8) | ((uint32_t)c[6] << 16) | ((uint32_t)c[7] << 24));
+    } else {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-        if (i < per) dst[lane * per + i] = float_to_e4m3(__fdiv_rn(x[i], div));
+        for (int i = 0; i < 8; ++i)
+            if (i < per) dst[lane * per + i] = c[i];
+    }
+}
+
+__device__ __forceinline__ void store_e4m3(uint8_t* dst, const float (&x)[8], float div, int per, int lane) {
+    uint8_t c[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c[i] = i < per ? float_to_e4m3(__fdiv_rn(x[i], div)) : (uint8_t)0;
+    store_codes(dst, c, per, lane);
 }
 
 __device__ __forceinline__ void store_int8(int8_t* dst, const float (&x)[8], float div, int per, int lane) {
+    uint8_t c[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-        if (i < per) {
-            float y = rintf(__fdiv_rn(x[i], div));
-            y = fminf(fmaxf(y, -127.f), 127.f);
-            dst[lane * per + i] = (int8_t)y;
-        }
+    for (int i = 0; i < 8; ++i) {
+        float y = rintf(__fdiv_rn(x[i], div));
+        y = fminf(fmaxf(y, -127.f), 127.f);
+        c[i] = i < per ? (uint8_t)(int8_t)y : (uint8_t)0;
+    }
+    store_codes(reinterpret_cast<uint8_t*>(dst), c, per, lane);
 }
 
 template <typename TIN>

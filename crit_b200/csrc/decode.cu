@@ -553,6 +553,8 @@ static int launch_decode_ph(const crit_b200_attend_params& p, cudaStream_t s) {
 }
 
 static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
+    // draft trees (parents) are masked by the m16n8k16 kernel only
+    if (p.parents && (p.flags & (CRIT_B200_ATTEND_TCGEN05P | CRIT_B200_ATTEND_TCGEN05T | CRIT_B200_ATTEND_TCGEN05))) return CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05P) return ph_serves(p) ? launch_decode_ph(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05T) return tc_serves(p) && p.n_rows <= SW_MAX_LIST ? launch_decode_sw(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05) return tc_serves(p) ? launch_decode_tc(p, s) : CRIT_B200_EUNSUPPORTED;
@@ -561,7 +563,7 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     // 32 query rows of accumulators a warp, which makes it issue-bound there), everything else, single-column decode
     // rows above all, to the m16n8k16 kernel.  A column's bits then depend on whether it is read alone or in a window;
     // CRIT_B200_ATTEND_MMA_SYNC keeps every launch on the m16n8k16 kernel, whose bits do not.
-    if (!(p.flags & CRIT_B200_ATTEND_MMA_SYNC) && p.columns > 1 && tc_serves(p)) return launch_decode_tc(p, s);
+    if (!(p.flags & CRIT_B200_ATTEND_MMA_SYNC) && p.columns > 1 && !p.parents && tc_serves(p)) return launch_decode_tc(p, s);
     const int G = p.q_heads / p.kv_heads;
     const int rows = p.columns * G;
     const int nt = row_tiles(rows, p.value_dim);

@@ -253,6 +253,24 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
             const int col = flat / G;
             lastpos[nt][e] = col < count ? (int)(first + col) : -1;
         }
+    // A draft tree (p.parents): of the window's own positions a query row sees its column and the column's ancestors, bit
+    // j of `seen` for column j (the chain of parents, at most `count` hops); the context before the window as ever.
+    const bool tree = p.parents != nullptr;
+    unsigned long long seen[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            seen[nt][e] = 0ull;
+            if (tree && lastpos[nt][e] >= 0) {
+                const int32_t* par = p.parents + p.starts[r];
+                int at = (ct * ROWS + nt * 8 + 2 * t + e) / G;
+                for (int hops = 0; at >= 0 && at < count && hops <= count; ++hops) {
+                    seen[nt][e] |= 1ull << at;
+                    at = par[at];
+                }
+            }
+        }
 
     // The B operand of the scores: Q^T, k16 x n8 per step; b0 holds k = 2t, 2t+1 and b1 k = 2t+8, 2t+9 of query row g.
     auto q_frag = [&](int nt, int ks, uint32_t& b0, uint32_t& b1) {
@@ -519,7 +537,15 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     float x = s[u][nt][e] * (sl2 * ksc[u][e >> 1]);
-                    if (masked && pos0[u] + g + 8 * (e >> 1) > lastpos[nt][e & 1]) x = -INFINITY;
+                    if (masked) {
+                        const int pos = pos0[u] + g + 8 * (e >> 1);
+                        if (!tree) {
+                            if (pos > lastpos[nt][e & 1]) x = -INFINITY;
+                        } else if (lastpos[nt][e & 1] < 0 || (pos >= first32 && (pos - first32 >= count ||
+                                                                                  !((seen[nt][e & 1] >> (pos - first32)) & 1ull)))) {
+                            x = -INFINITY;
+                        }
+                    }
                     s[u][nt][e] = x;
                     mx[e & 1] = fmaxf(mx[e & 1], x);
                 }

@@ -21,7 +21,7 @@
 extern "C" {
 #endif
 
-#define CRIT_B200_ABI_VERSION 2
+#define CRIT_B200_ABI_VERSION 3
 
 /* Page kinds (the reference's KINDS, paged_kv_attention/__init__.py:78, plus the per-page FP8 scale). */
 #define CRIT_B200_KIND_16BIT    0   /* bf16 or fp16 pages (page_dtype says which) */
@@ -171,6 +171,11 @@ typedef struct crit_b200_attend_params {
     int32_t max_splits;          /* splits a partial row has room for: ceil(positions a row may reach / chunk) */
     int32_t flags;               /* CRIT_B200_ATTEND_* */
     float scale, key_multiplier, value_multiplier;
+    const int32_t* parents;      /* NULL, or [tokens of q]: each token's parent COLUMN in its row, -1 for none (a draft tree,
+                                    the columns in topological order): a column then sees the positions before its row's
+                                    first and, of the window, itself and its ancestors instead of the columns before it
+                                    (paged_kv_attention/_kernels.py:154-165, :325-329).  Served by the m16n8k16 kernel; a
+                                    launch that names a tcgen05 kernel with parents is CRIT_B200_EUNSUPPORTED */
 } crit_b200_attend_params;
 
 /* out[0] positions per split this library would choose (a multiple of 16), out[1] bytes of dynamic shared memory a

@@ -160,6 +160,29 @@ def attend(q, k, v, tables, rows, starts, firsts, columns, page, scale=None, cou
     return out, lse
 
 
+def attend_tree(q, k, v, tables, rows, starts, firsts, columns, page, parents, scale=None, counts=None):
+    """attend() for the windows of a draft tree: parents [T] is each token's parent column in its row, -1 for none; a
+    column sees the context before its row's first position and, of the window, itself and its ancestors.
+    ref: paged_kv_attention/_kernels.py:154-165, :325-329."""
+    q, k, v = _c(q, np.float32), _c(k, np.float32), _c(v, np.float32)
+    tables = _c(tables, np.int32)
+    if tables.ndim == 1:
+        tables = tables[None]
+    rows, starts, parents = _c(rows, np.int32), _c(starts, np.int32), _c(parents, np.int32)
+    firsts = _c(firsts, np.int64)
+    counts = _c(counts, np.int32) if counts is not None else None
+    T, hq, d = q.shape
+    hkv, dv = k.shape[-2], v.shape[-1]
+    scale = float(scale if scale is not None else d ** -0.5)
+    out = np.zeros((T, hq, dv), np.float32)
+    lse = np.full((T, hq), -np.inf, np.float32)
+    i64 = ctypes.c_int64
+    lib().crit_oracle_attend_tree(_p(q), i64(hq), i64(d), _p(k), _p(v), i64(hkv), i64(dv), _p(tables),
+                                  i64(tables.shape[1]), _p(rows), _p(starts), _p(counts), _p(firsts), _p(parents),
+                                  i64(rows.size), i64(columns), i64(page), ctypes.c_float(scale), _p(out), _p(lse))
+    return out, lse
+
+
 def merge(outs, lses):
     """outs [parts][...][dv], lses [parts][...] -> (out, lse).  ref: inference/partitioned-attention/plugin.py:52-64."""
     outs, lses = _c(outs, np.float32), _c(lses, np.float32)

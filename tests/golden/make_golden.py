@@ -259,6 +259,37 @@ def verify_window():
     np.savez_compressed(OUT / "verify_fp8row.npz", **found)
 
 
+def tree_windows():
+    """Two rows of draft trees (parents per token, -1 for none, topological order) over bf16 pages, on the reference's
+    torch path: a column sees the context before its row's first position, itself and its ancestors."""
+    hq, hkv, d, page = 8, 2, 64, 16
+    g = torch.Generator().manual_seed(33)
+    pool = pages.KVPool([0], hkv, d, 24 * page, "cpu", "bf16", page=page)
+    lens = {"a": 150, "b": 37}
+    stored = {}
+    for s, n in lens.items():
+        pool.open(s)
+        k0, v0 = torch.randn(n, hkv, d, generator=g).bfloat16(), torch.randn(n, hkv, d, generator=g).bfloat16()
+        pool.write(0, pool.reserve(StepBatch.build([(s, 0, n)], "cpu")), k0, v0)
+        pool.keep(s, n)
+        stored[s] = (k0, v0)
+    batch = StepBatch.build([("a", 150, 7), ("b", 37, 5)], "cpu")
+    parents = torch.tensor([-1, 0, 0, 1, 1, 2, 5, -1, 0, 1, 0, 3], dtype=torch.int32)
+    k1, v1 = torch.randn(12, hkv, d, generator=g).bfloat16(), torch.randn(12, hkv, d, generator=g).bfloat16()
+    pool.write(0, pool.reserve(batch), k1, v1)
+    q = torch.randn(12, hq, d, generator=g).bfloat16()
+    eager = device_attention.DeviceAttention(None, "torch", device="cpu")
+    out, lse = eager.forward(0, q, pool, batch, parents=parents, lse=True)
+    width = max(len(pool.table(s)) for s in lens)
+    tables = np.zeros((2, width), np.int32)
+    for i, s in enumerate(lens):
+        tables[i, :len(pool.table(s))] = pool.table(s)
+    np.savez_compressed(OUT / "tree_bf16.npz", q=q.float().numpy(), parents=parents.numpy(), tables=tables,
+                        k_pages=pool.k[0].float().numpy(), v_pages=pool.v[0].float().numpy(), out=out.float().numpy(),
+                        lse=lse.numpy(), geometry=np.array([hq, hkv, d, page]), firsts=np.array([150, 37]),
+                        counts=np.array([7, 5]), starts=np.array([0, 7]))
+
+
 # -- 6. merges ---------------------------------------------------------------------------------------------------------
 def merges():
     g = torch.Generator().manual_seed(31)
@@ -289,6 +320,9 @@ def merges():
 
 if __name__ == "__main__":
     torch.set_num_threads(8)
+    if sys.argv[2:] == ["tree"]:           # that fixture alone: make_golden.py /path/to/reference tree
+        tree_windows()
+        raise SystemExit(0)
     e4m3_vectors()
     quantize()
     pool_script()
@@ -296,5 +330,6 @@ if __name__ == "__main__":
     np.savez_compressed(OUT / "c1_small.npz", **c1_step(8, 2, 16, 4, 64, [9, 33, 1, 20], 7, True))
     np.savez_compressed(OUT / "c1_full.npz", **c1_step(32, 8, 128, 16, 512, None, 1, False))
     verify_window()
+    tree_windows()
     merges()
     print("fixtures written to", OUT)

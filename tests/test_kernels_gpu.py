@@ -582,3 +582,71 @@ def test_the_peer_exchange_lands_every_ranks_message_and_a_missing_rank_runs_the
         torch.cuda.synchronize()
         for r in range(world):
             assert torch.equal(gathered[r][0], mine[0]) and torch.equal(gathered[r][1], mine[1]) and int(status[r].item()) == 0
+
+
+# -- draft trees: a column sees the context, itself and its ancestors ----------------------------------------------------
+def _random_tree(rng, count):
+    """Parents of `count` columns in topological order: column 0 a root, every later column under an earlier one or a
+    root of its own."""
+    return [-1] + [int(rng.integers(-1, c)) for c in range(1, count)]
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp8", "fp8:row", "int8", "fp8:page"])
+@pytest.mark.parametrize("hq,hkv,d", [(8, 2, 128), (24, 4, 256), (64, 8, 128), (4, 4, 64)])
+@pytest.mark.parametrize("page,chunk", [(16, 64), (48, 1024)])
+def test_draft_tree_windows_match_the_oracle(pk, kind, hq, hkv, d, page, chunk):
+    import oracle
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, hkv, d, d, page, [130, 64, 9, 517, 1300])
+    cols = min(8, 64 // (hq // hkv))
+    firsts = [130 - cols, 64 - 3, 0, 400, 1300 - cols]
+    counts = [cols, 3, min(cols, 9), min(cols, 5), cols]
+    rows, starts = [0, 1, 2, 3, 4], [0, 8, 16, 24, 32]
+    rng = np.random.default_rng(11)
+    parents = np.full(40, -1, np.int32)
+    for s, n in zip(starts, counts):
+        parents[s:s + n] = _random_tree(rng, n)
+    q = queries(40, hq, d, 3)
+    lse = torch.full((40, hq), 7.0, device="cuda")
+    out = cache.attend(q, rows, starts, firsts, cols, counts=counts, lse=lse, chunk=chunk,
+                       parents=torch.tensor(parents, device="cuda"))
+    assert pk.status() == 0
+    k, v = cache.stored()
+    want, want_lse = oracle.attend_tree(q.float().cpu().numpy(), k, v, cache.tables.cpu().numpy(), rows, starts, firsts, cols,
+                                        page, parents, counts=counts)
+    tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
+    assert_attention_close(out, lse, want, want_lse, tokens)
+    # a chain is the plain causal window, bit for bit; int64 parents are taken too
+    chain = np.full(40, -1, np.int64)
+    for s, n in zip(starts, counts):
+        chain[s:s + n] = np.arange(n) - 1
+    a = cache.attend(q, rows, starts, firsts, cols, counts=counts, chunk=chunk, parents=torch.tensor(chain, device="cuda"))
+    b = cache.attend(q, rows, starts, firsts, cols, counts=counts, chunk=chunk, engine="mma.sync")
+    assert torch.equal(a[tokens], b[tokens])
+
+
+def test_draft_trees_match_the_references_torch_path(pk, golden):
+    """The reference's own torch windows over a draft tree (tests/golden/make_golden.py: tree_windows), bf16 pages."""
+    from helpers import assert_attention_close
+    f = golden("tree_bf16.npz")
+    hq, hkv, d, page = (int(x) for x in f["geometry"])
+    dev = "cuda"
+    k = torch.tensor(f["k_pages"]).bfloat16().to(dev).reshape(-1, hkv, d)
+    v = torch.tensor(f["v_pages"]).bfloat16().to(dev).reshape(-1, hkv, d)
+    q = torch.tensor(f["q"]).bfloat16().to(dev)
+    lse = torch.empty(12, hq, device=dev)
+    out = pk.attend(q, k.view(-1, page, hkv, d), v.view(-1, page, hkv, d), "bf16", torch.tensor(f["tables"], device=dev),
+                    torch.tensor([0, 1], dtype=torch.int32, device=dev), torch.tensor(f["starts"], dtype=torch.int32, device=dev),
+                    torch.tensor(f["firsts"], dtype=torch.int64, device=dev), 7, page,
+                    counts=torch.tensor(f["counts"], dtype=torch.int32, device=dev), lse=lse,
+                    parents=torch.tensor(f["parents"], device=dev))
+    assert_attention_close(out, lse, f["out"], f["lse"], list(range(12)))
+
+
+def test_draft_trees_are_refused_by_the_tcgen05_kernels(pk):
+    from helpers import Cache, queries
+    cache = Cache("fp8:page", 8, 128, 128, 16, [100])
+    parents = torch.tensor([-1, 0], dtype=torch.int32, device="cuda")
+    for engine in ("tcgen05", "tcgen05p"):
+        with pytest.raises(NotImplementedError):
+            cache.attend(queries(2, 16, 128, 1), [0], [0], [98], 2, parents=parents, engine=engine)

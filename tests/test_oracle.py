@@ -238,3 +238,22 @@ def test_fold_in_split_order_equals_the_merge():
     want, want_lse = oracle.merge(o[:, None, :], lses[:, None])
     np.testing.assert_allclose(out, want[0], atol=1e-5)
     assert abs(lse - float(want_lse[0])) < 1e-5
+
+
+def test_tree_windows_match_the_references_torch_path(golden):
+    """Draft trees (parents per token): the oracle against the reference's own torch windows on bf16 pages
+    (tests/golden/make_golden.py: tree_windows)."""
+    import oracle
+    f = golden("tree_bf16.npz")
+    hq, hkv, d, page = (int(x) for x in f["geometry"])
+    k = f["k_pages"].reshape(-1, hkv, d)
+    v = f["v_pages"].reshape(-1, hkv, d)
+    out, lse = oracle.attend_tree(f["q"], k, v, f["tables"], [0, 1], f["starts"], f["firsts"], 7, page, f["parents"],
+                                  counts=f["counts"])
+    assert np.abs(out - f["out"]).max() <= 8e-3          # the reference's outputs are bf16
+    assert np.abs(lse - f["lse"]).max() <= 2e-5
+    # a chain (parent = the column before) is the plain causal window
+    chain = np.array([-1, 0, 1, 2, 3, 4, 5, -1, 0, 1, 2, 3], np.int32)
+    a, la = oracle.attend_tree(f["q"], k, v, f["tables"], [0, 1], f["starts"], f["firsts"], 7, page, chain, counts=f["counts"])
+    b, lb = oracle.attend(f["q"], k, v, f["tables"], [0, 1], f["starts"], f["firsts"], 7, page, counts=f["counts"])
+    assert np.array_equal(a, b) and np.array_equal(la, lb)
