@@ -25,7 +25,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["KINDS", "MAX_COLUMNS", "attend", "chunk_for", "gather", "merge_shards", "owner", "partitions", "parts_for",
+__all__ = ["KINDS", "MAX_COLUMNS", "attend", "chunk_for", "gather", "merge_shards", "move_rows", "owner", "partitions", "parts_for",
            "engine_for", "piece_size", "plan", "prefill", "prefill_serves", "release", "slots_at", "states_for", "status", "tcgen05_serves",
            "tcgen05p_serves", "tile_for", "workspace_floats", "write"]
 
@@ -348,6 +348,30 @@ def slots_at(tables, rows, positions, page, dump, capacity=None, out=None):
     with torch.cuda.device(tables.device):
         _lib.check(_lib.load().crit_b200_slots(ctypes.byref(p), _stream(tables.device)), "crit_b200.slots_at")
     return out.view(shape)
+
+
+def move_rows(store, source, target):
+    """Rows of one store moved between slots, in place: store [layers][slots][...] (keys, values or their row scales),
+    source / target [lists][width] int64 slots; for every list, in order j = 0 .. width - 1, the row at source[l][j] of
+    every layer goes to target[l][j] (nothing where the two are equal).  A list's moves happen one after another; lists
+    are independent.  What the pool's commit_round brings an accepted draft-tree path's KV together with
+    (reference: inference/attention-state/code/pages.py:662-684)."""
+    _cuda(store, "store")
+    if not store.is_contiguous() or store.dim() < 2:
+        raise ValueError("a store is contiguous [layers][slots][...]")
+    if source.dtype != torch.int64 or target.dtype != torch.int64 or source.shape != target.shape or source.dim() != 2:
+        raise ValueError("source and target are int64 [lists][width]")
+    source, target = source.contiguous(), target.contiguous()
+    layers, slots = store.shape[0], store.shape[1]
+    row_bytes = store[0, 0].numel() * store.element_size()
+    if row_bytes % 4:
+        raise ValueError("a store's rows are a multiple of 4 bytes")
+    p = _lib.MoveParams()
+    p.store, p.source, p.target = _ptr(store), _ptr(source), _ptr(target)
+    p.lists, p.width, p.slots, p.row_bytes, p.layers = source.shape[0], source.shape[1], slots, row_bytes, layers
+    p.status = _ptr(_status_word(store.device))
+    with torch.cuda.device(store.device):
+        _lib.check(_lib.load().crit_b200_move_rows(ctypes.byref(p), _stream(store.device)), "crit_b200.move_rows")
 
 
 # -- decode and verify windows ------------------------------------------------------------------------------------------

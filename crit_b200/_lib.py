@@ -33,6 +33,11 @@ class SlotsParams(Structure):
                 ("table_width", c_int32), ("page", c_int32), ("dump", c_int32)]
 
 
+class MoveParams(Structure):
+    _fields_ = [("store", c_void_p), ("source", c_void_p), ("target", c_void_p), ("lists", c_int64), ("width", c_int64),
+                ("slots", c_int64), ("row_bytes", c_int64), ("layers", c_int32), ("status", c_void_p)]
+
+
 class AttendParams(Structure):
     _fields_ = [("q", c_void_p), ("out", c_void_p), ("lse", c_void_p), ("key_pages", c_void_p),
                 ("value_pages", c_void_p), ("key_scales", c_void_p), ("value_scales", c_void_p),
@@ -82,6 +87,7 @@ SYMBOLS = {
     "crit_b200_attend": (c_int, [POINTER(AttendParams), c_void_p]),
     "crit_b200_attend_static": (c_int, [POINTER(AttendParams), c_void_p]),
     "crit_b200_merge_shards": (c_int, [POINTER(MergeShardsParams), c_void_p]),
+    "crit_b200_move_rows": (c_int, [POINTER(MoveParams), c_void_p]),
     "crit_b200_prefill": (c_int, [POINTER(PrefillParams), c_void_p]),
     "crit_b200_shard_push": (c_int, [POINTER(ExchangeParams), c_void_p]),
     "crit_b200_shard_wait": (c_int, [POINTER(ExchangeParams), c_void_p]),

@@ -103,6 +103,43 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_gather(const cri
     return 0;
 }
 
+namespace crit_b200 {
+
+// Block = (list, layer): the list's moves in order, each a copy of row_bytes bytes by the block's threads.
+__global__ void __launch_bounds__(128) move_rows_kernel(const crit_b200_move_params p) {
+    const int64_t list = blockIdx.x;
+    const int layer = blockIdx.y;
+    uint32_t* base = reinterpret_cast<uint32_t*>((char*)p.store + (int64_t)layer * p.slots * p.row_bytes);
+    const int64_t words = p.row_bytes >> 2;
+    for (int64_t j = 0; j < p.width; ++j) {
+        const int64_t from = p.source[list * p.width + j], to = p.target[list * p.width + j];
+        if (from == to) continue;                           // (block-uniform)
+        if (from < 0 || from >= p.slots || to < 0 || to >= p.slots) {
+            if (threadIdx.x == 0 && p.status) atomicExch(p.status, CRIT_B200_STATUS_BOUNDS);
+            continue;
+        }
+        const uint32_t* src = base + from * words;
+        uint32_t* dst = base + to * words;
+        for (int64_t w = threadIdx.x; w < words; w += blockDim.x) dst[w] = src[w];
+        __syncthreads();                                     // the next move of the list may read this one's target
+    }
+}
+
+}  // namespace crit_b200
+
+extern "C" __attribute__((visibility("default"))) int crit_b200_move_rows(const crit_b200_move_params* params, void* stream) {
+    if (!params) return CRIT_B200_EINVAL;
+    const crit_b200_move_params p = *params;
+    if (p.lists == 0 || p.width == 0) return 0;
+    if (!p.store || !p.source || !p.target || p.lists < 0 || p.width < 0 || p.slots < 1 || p.layers < 1 || p.row_bytes < 4 ||
+        p.row_bytes % 4 || p.lists > 0x7fffffffLL || p.layers > 65535)
+        return CRIT_B200_EINVAL;
+    dim3 grid((unsigned)p.lists, (unsigned)p.layers);
+    crit_b200::move_rows_kernel<<<grid, 128, 0, (cudaStream_t)stream>>>(p);
+    CRIT_CHECK_LAUNCH();
+    return 0;
+}
+
 extern "C" __attribute__((visibility("default"))) int crit_b200_slots(const crit_b200_slots_params* params, void* stream) {
     if (!params) return CRIT_B200_EINVAL;
     const crit_b200_slots_params p = *params;

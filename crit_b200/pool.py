@@ -134,6 +134,7 @@ class KVPool:
         self.round_capacity = torch.zeros(slots, dtype=torch.int64, device=self.device)
         self.round_lengths = torch.zeros(slots, dtype=torch.int64, device=self.device)
         self._start = torch.zeros(slots, dtype=torch.int64, device=self.device)
+        self._moved = torch.zeros(slots, dtype=torch.int64, device=self.device)     # a round's tree paths moved already
         self.prompt_slots = None
         self.prompt_table = torch.full((1, self.table_pages), self.dump, dtype=torch.int32, device=self.device)
 
@@ -435,17 +436,53 @@ class KVPool:
         self.keep(sequence, length)
 
     def start_round(self, view):
+        """A round begins: each row's valid length as the round finds it, and no row's draft-tree path moved yet.
+        Reference: pages.py:624-629."""
         rows = view.rows
         self._start[:rows].copy_(self.round_lengths[:rows])
+        self._moved[:rows].zero_()
 
     def commit_round(self, view):
         """Each row's valid length becomes its frontier where it emitted, and stays where it emitted nothing; on the
-        device.  Reference: pages.py:631-644 (a draft tree's path compaction is not served)."""
-        if getattr(view, "tree_path", None) is not None:
-            raise NotImplementedError("crit_b200's pool does not compact a draft tree's accepted path")
+        device.  With a draft tree (view.tree_path [rows][width + 1]: node 0, then the accepted nodes in order, -1 past
+        them) the accepted nodes' keys and values first move from their nodes' positions to consecutive ones, once a
+        round (a second commit of the same round finds the path moved).  Device work only.
+        Reference: pages.py:631-644, :662-684."""
         rows = view.rows
         emitted = view.n_emitted[:rows]
+        path = getattr(view, "tree_path", None)
+        if path is not None:
+            self._compact(rows, emitted, path[:rows])
         self.round_lengths[:rows].copy_(self.torch.where(emitted > 0, view.frontier[:rows], self._start[:rows]))
+
+    def _compact(self, rows, emitted, path):
+        """The accepted path's KV (node path[j], stored at position start + path[j]) to positions start + j, j < the row's
+        emitted count.  The slots come from the round tables on the device; the rows are moved by the kernels' move_rows,
+        a row's moves in order of j (path[j] >= j: no move reads what an earlier one of its row wrote over)."""
+        torch = self.torch
+        if self.dtype == "fp8:page":
+            raise NotImplementedError("a draft tree's accepted path is not compacted over fp8:page pages: a moved row "
+                                      "would change pages, and with them its scale")
+        width = path.shape[1]
+        columns = torch.arange(width, device=self.device)
+        start = self._start[:rows]
+        keep = (columns[None, :] < emitted[:, None]) & (columns[None, :] > 0) & (path >= 0) & (self._moved[:rows, None] == 0)
+        slot = torch.arange(rows, device=self.device)[:, None].expand(rows, width)
+        # columns not kept go from the dump page to itself (position -1 lies outside every slot's capacity): no move
+        source = self.slots_at(slot, torch.where(keep, start[:, None] + path.long(), -1))
+        target = self.slots_at(slot, torch.where(keep, start[:, None] + columns[None, :], -1))
+        n, held = len(self.layers), self.stored_slots
+        stores = [self.k.view(n, held, self.kv_heads, self.head_dim)]
+        if self.value_dim:
+            stores.append(self.v.view(n, held, self.kv_heads, self.value_dim))
+        if self.k_scales is not None:
+            stores += [scales.view(n, held, self.kv_heads) for scales in (self.k_scales, self.v_scales)]
+        if self.device.type != "cuda":
+            raise RuntimeError("a draft tree's accepted path is moved by the CUDA kernels: this pool is on the CPU "
+                               "(page tables and slot maps only)")
+        for store in stores:
+            self.kernels.move_rows(store, source, target)
+        self._moved[:rows] = 1
 
     def _reserve_round(self, batch):
         if batch.rows > self.round_rows:

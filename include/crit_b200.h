@@ -111,6 +111,24 @@ typedef struct crit_b200_slots_params {
 
 int crit_b200_slots(const crit_b200_slots_params* params, void* stream);
 
+/* Rows of one store (keys, values or their row scales, all layers) moved between slots: for every list r, in order
+ * j = 0 .. width - 1, the `row_bytes` bytes at slot source[r][j] of every layer go to slot target[r][j] (nothing where
+ * the two are equal).  A list's moves happen one after another, so a later move may read what an earlier one of the
+ * same list wrote over only if the lists say so; the accepted path of a draft tree (node path[j] -> position j, path[j]
+ * >= j) never does.  Lists are independent (their slots are disjoint).  The pool's commit_round uses it to bring an
+ * accepted path's KV to consecutive positions (inference/attention-state/code/pages.py:662-684). */
+typedef struct crit_b200_move_params {
+    void* store;                 /* [layers][slots] rows of row_bytes bytes */
+    const int64_t* source;       /* [lists][width] slots */
+    const int64_t* target;       /* [lists][width] slots */
+    int64_t lists, width, slots; /* slots: rows a layer holds (a slot outside [0, slots) is skipped and reported) */
+    int64_t row_bytes;           /* a multiple of 4 */
+    int32_t layers;
+    int32_t* status;             /* optional device word: CRIT_B200_STATUS_BOUNDS */
+} crit_b200_move_params;
+
+int crit_b200_move_rows(const crit_b200_move_params* params, void* stream);
+
 #define CRIT_B200_ATTEND_NO_TMA 1   /* stage pages with cp.async even where the TMA path serves the geometry */
 #define CRIT_B200_ATTEND_TMA    2   /* stage pages with TMA wherever it serves the geometry (default: 16-bit pages only,
                                        where it measured faster; 8-bit pages measured faster with cp.async) */
@@ -305,7 +323,7 @@ int crit_b200_prefill(const crit_b200_prefill_params* params, void* stream);
 /* -- housekeeping ------------------------------------------------------------------------------------------------ */
 int crit_b200_abi_version(void);
 /* sizeof of each parameter block, in the order append, gather, slots, attend, merge_shards, prefill: a binding checks
- * its own struct layout against it (the reference's crit_cw_params_size, cuda_window.cu:1495-1497). */
+ * its own struct layout against it (the reference's crit_cw_params_size, cuda_window.cu:1495-1497); 6 exchange, 7 move. */
 int crit_b200_params_size(int32_t which);
 const char* crit_b200_error(int32_t code);       /* host string; cudaGetErrorString for codes above 0 */
 int crit_b200_device_sms(void);                  /* SMs of the current device, or a negative error */

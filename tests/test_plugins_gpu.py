@@ -307,3 +307,81 @@ def test_facts_count_the_bytes_a_token_takes():
     kv.pool([0, 1], 8, 128, 1024, "cuda", "fp8:page")
     assert kv.facts()["kv_bytes_per_token"] == 2 * (8 * 128 * 2 + 8 * 2 * 4 / 16)
     assert attention.exactness()["decode"] == "row-exact"
+
+
+# -- draft trees: the window reads a tree, the round's commit brings the accepted path together ----------------------------
+def test_move_rows_moves_a_lists_rows_in_order():
+    """crit_b200.move_rows against gather-then-scatter: a path whose targets are other moves' sources (node 2 -> 1, node
+    3 -> 2), moves from a slot to itself, two stores of different row sizes."""
+    import crit_b200 as pk
+    g = torch.Generator().manual_seed(3)
+    store = torch.randn(3, 40, 2, 64, generator=g).bfloat16().cuda()
+    scales = torch.randn(3, 40, 2, generator=g).cuda()
+    source = torch.tensor([[5, 7, 8, 9, 39], [20, 23, 22, 39, 39]], dtype=torch.int64, device="cuda")
+    target = torch.tensor([[5, 6, 7, 8, 39], [20, 21, 22, 39, 39]], dtype=torch.int64, device="cuda")
+    for s in (store, scales):
+        want = s.clone()
+        want.index_copy_(1, target.reshape(-1), s.index_select(1, source.reshape(-1)))
+        pk.move_rows(s, source, target)
+        assert torch.equal(s, want)
+    assert pk.status() == 0
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8:row", "fp8"])
+def test_a_round_over_a_draft_tree_reads_ancestors_and_commits_the_accepted_path(dtype):
+    """A bound sequence, a round whose window is a draft tree: every node's KV is written at position start + node, the
+    attention sees a node's ancestors (parents), and commit_round(view.tree_path) moves the accepted nodes' KV to
+    consecutive positions, once, in every layer, codes and scales alike."""
+    import types
+    from crit_b200.batch import StepBatch
+    from helpers import assert_attention_close
+    kv, attention = parts(round_rows=2)
+    pool = kv.pool([0, 1], 2, 128, 16 * 40, "cuda", dtype)
+    if dtype == "fp8":
+        pool.set_scales(0, 0.05, 0.04), pool.set_scales(1, 0.03, 0.06)
+    pool.open("a")
+    first = pool.reserve(StepBatch.build([("a", 0, 45)], "cuda"))
+    for layer in (0, 1):
+        pool.write(layer, first, rows_of(45, 2, 128, 1 + layer), rows_of(45, 2, 128, 5 + layer))
+    pool.keep("a", 45)
+    pool.bind(0, "a", 45 + 16)
+    # the tree: node 0 the pending token; 1 and 2 its children; 3 under 1; 4 under 3; 5 under 2
+    parents = torch.tensor([-1, 0, 0, 1, 3, 2], dtype=torch.int32, device="cuda")
+    view = types.SimpleNamespace(rows=1, n_emitted=torch.tensor([4], device="cuda"), frontier=torch.tensor([49], device="cuda"),
+                                 tree_path=torch.tensor([[0, 1, 3, 4, -1, -1]], device="cuda"))
+    pool.start_round(view)
+    slots = pool.slots_at(torch.zeros(6, dtype=torch.int64, device="cuda"), 45 + torch.arange(6, device="cuda"))
+    for layer in (0, 1):
+        pool.write(layer, slots, rows_of(6, 2, 128, 20 + layer), rows_of(6, 2, 128, 30 + layer))
+    # the attention over the tree, layer 0
+    q = torch.randn(6, 8, 128, generator=torch.Generator().manual_seed(9)).bfloat16().cuda()
+    rb = types.SimpleNamespace(round=True, prompt=False, rows=1, width=5, slots_t=torch.zeros(1, dtype=torch.int64, device="cuda"),
+                               starts_t=torch.zeros(1, dtype=torch.int32, device="cuda"), frontier_t=torch.tensor([45], device="cuda"))
+    out, lse = attention.forward(0, q, pool, rb, parents=parents, lse=True)
+    k, v = stored(pool, 0)
+    table = pool.round_tables[0].cpu().numpy()[None]
+    want, want_lse = oracle.attend_tree(q.float().cpu().numpy(), k, v, table, [0], [0], [45], 6, pool.page, parents.cpu().numpy())
+    assert_attention_close(out, lse, want, want_lse, list(range(6)))
+    # the accepted path 0 -> 1 -> 3 -> 4 comes together at positions 45..48
+    stores = [pool.k, pool.v] + ([pool.k_scales, pool.v_scales] if pool.k_scales is not None else [])
+    snapshot = [t.clone() for t in stores]
+    pool.commit_round(view)
+
+    def flat(t):                # [layers][slots][...]
+        return t.reshape(t.shape[0], t.shape[1] * t.shape[2], *t.shape[3:])
+    s = slots.cpu().tolist()
+    for was, now in zip(snapshot, stores):
+        was, now = flat(was), flat(now)
+        for j, node in enumerate([0, 1, 3, 4]):
+            assert torch.equal(now[:, s[j]].contiguous().view(torch.uint8), was[:, s[node]].contiguous().view(torch.uint8))
+    assert int(pool.round_lengths[0]) == 49
+    # a second commit of the same round moves nothing more
+    again = [t.clone() for t in stores]
+    pool.commit_round(view)
+    for was, now in zip(again, stores):
+        assert torch.equal(was.view(torch.uint8), now.view(torch.uint8))
+    pool.unbind(0)
+    assert pool.length("a") == 49
+    with pytest.raises(NotImplementedError):
+        paged = kv.pool([0], 2, 128, 16 * 8, "cuda", "fp8:page", )
+        paged._compact(1, view.n_emitted, view.tree_path)
