@@ -401,7 +401,9 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     workspace's, see partitions()).  piece, fused, vsplit, tile, num_warps, num_stages, maxnreg, flash and ramp are
     accepted and change nothing (one launch shape per geometry).  parents [tokens]: each token's parent column in its
     row, -1 for none (a draft tree in topological order): a column then sees the context before its row's first position,
-    itself and its ancestors (the m16n8k16 kernel).  blocks, fresh, sinks, sliding and derive are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
+    itself and its ancestors.  sinks [heads] FP32: a logit a query head that joins the softmax's maximum and sum (and
+    the lse) without a value; sliding: the positions a column sees up to its own, 0 for all (all three on the m16n8k16
+    kernel).  blocks, fresh and derive are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
     None (TMA tiled loads for 16-bit pages of 128- or 256-wide heads, cp.async otherwise: what measured faster), "tma"
     (TMA wherever the geometry allows it) or "cp.async" (never TMA); the same bits either way.  persistent: a fixed
     number of blocks walk a work list built on the device from the rows' lengths, instead of one block per (split, kv
@@ -411,7 +413,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     shards: a crit_b200.dist.ShardMerge: these pages hold one KV range of a context sharded over the ranks; every
     split state stays in the workspace, the fold of this rank's splits is stored into every rank's exchange buffer and
     out / lse get the merge over all ranks (three launches: decode, fold + push, wait + merge)."""
-    _refuse(blocks=blocks, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
+    _refuse(blocks=blocks, fresh=fresh, derive=derive)
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
     T, hq, d = q.shape
@@ -444,6 +446,22 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
             raise ValueError("parents are int32 or int64, one per token of q")
         parents = _cuda(parents, "parents").to(torch.int32).contiguous()
         engine = "mma.sync"
+    sliding = int(sliding or 0)
+    if sinks is not None or sliding:
+        # a sink logit a query head (joins the softmax's maximum and sum, and the lse, in the fold of the splits), and a
+        # window of the `sliding` positions up to a column's own: the m16n8k16 kernel's
+        if engine not in (None, "mma.sync"):
+            raise NotImplementedError("sinks and sliding windows are served by the m16n8k16 kernel: engine None or mma.sync")
+        if shards is not None and sinks is not None:
+            raise NotImplementedError("a sharded context's merge does not take sinks")
+        if sliding < 0:
+            raise ValueError("sliding is the number of positions a column sees, 0 for all")
+        if sinks is not None:
+            sinks = _cuda(sinks, "sinks").reshape(-1)
+            if sinks.numel() != hq:
+                raise ValueError(f"sinks are one logit a query head ({hq}), not {sinks.numel()}")
+            sinks = sinks.float().contiguous()
+        engine = "mma.sync"
     chosen = engine is None
     if chosen and (shards is not None or persistent or staging is not None):
         engine = "mma.sync"               # what those arguments are about
@@ -461,7 +479,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     if out.dtype != q.dtype or out.stride(-1) != 1:
         raise ValueError("out is in q's dtype, its last dimension contiguous")
     p = _lib.AttendParams()
-    if splits > 1 or shards is not None:
+    if splits > 1 or shards is not None or sinks is not None:
         floats = workspace_floats(partial_rows, hq, splits, dv)
         space = _workspace(device, floats, workspace)
         p.workspace, p.workspace_floats = _ptr(space), space.numel()
@@ -487,7 +505,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])
-    p.parents = _ptr(parents)
+    p.parents, p.sinks, p.sliding = _ptr(parents), _ptr(sinks), sliding
     lib = _lib.load()
     if shards is not None:
         if lse is None:

@@ -97,9 +97,14 @@ class DeviceAttention:
         step already); each token sees its sequence's positions up to its own.  lse: also return each token's
         log-sum-exp ([tokens][heads] FP32).  Returns out [tokens][heads][value dim] in the queries' dtype (and lse)."""
         import torch
-        if blocks is not None or sinks is not None or sliding or latent:
-            raise NotImplementedError("crit_b200's attention reads causal windows over the whole context: no block lists, "
-                                      "sinks, sliding windows or latent attention yet")
+        if blocks is not None or latent:
+            raise NotImplementedError("crit_b200's attention does not serve block lists or latent attention yet")
+        if sinks is not None:
+            sinks = sinks.reshape(-1).float().contiguous()
+            if sinks.numel() != queries.shape[1] or not sinks.is_cuda:
+                raise ValueError("sinks are one logit a query head, on the queries' device")
+        # (the call's sinks and sliding window, for the launches below: reference device_attention.py:188-189, :382-386)
+        self._sinks, self._sliding = sinks, int(sliding or 0)
         if parents is not None and getattr(batch, "prompt", False):
             raise NotImplementedError("draft trees (parents) are read in window rows, not in a staged prompt chunk")
         if not queries.is_cuda:
@@ -131,6 +136,7 @@ class DeviceAttention:
                 self._windows(layer, q, pool, self._step_windows(pool, batch, short, q.device), scale, out, found, parents)
             self._prompts(layer, q, pool, batch, [r for r in range(batch.rows) if batch.row(r)[2] > pool.window],
                           scale, out, found, parents)
+        self._sinks, self._sliding = None, 0
         out = out if out.dtype == queries.dtype else out.to(queries.dtype)
         return (out, found) if lse else out
 
@@ -158,8 +164,9 @@ class DeviceAttention:
         geometry = (pool.dtype, pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, meta.columns)
         # the kernel the step's windows run on: the kernels' choice for the whole step, or the one the option names
         named = kernels.engine_for(*geometry, len(meta), positions, None if self.window_engine == "auto" else self.window_engine)
-        if parents is not None:
-            named = "mma.sync"             # draft trees are masked by the m16n8k16 kernel
+        sinks, sliding = getattr(self, "_sinks", None), getattr(self, "_sliding", 0)
+        if parents is not None or sinks is not None or sliding:
+            named = "mma.sync"             # draft trees, sinks and sliding windows are the m16n8k16 kernel's
         chunk = self.chunk or kernels.chunk_for(pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, pool.page, pool.dtype,
                                                 named, meta.columns)
         if self.partitions:
@@ -169,7 +176,7 @@ class DeviceAttention:
             named = "mma.sync"
         parts = kernels.states_for(kernels.parts_for(positions, chunk), named)
         launches, workspace = [(slice(0, len(meta)), meta.total)], None
-        if self.partial_bytes and parts > 1:
+        if self.partial_bytes and (parts > 1 or sinks is not None):
             # the partials come from the engine's scratch: as many rows a launch as its share of the scratch holds
             per = kernels.workspace_floats(1, q.shape[1], parts, pool.value_dim)
             launches = launch_cuts(meta, self.partial_bytes // 4 // per)
@@ -191,7 +198,7 @@ class DeviceAttention:
                            tokens=tokens if offsets is not None else None,
                            key_scales=pages[2] if scaled else None, value_scales=pages[3] if scaled else None,
                            multipliers=multipliers, scale=scale, chunk=chunk, out=out, lse=found, workspace=workspace,
-                           engine=engine(cut.stop - cut.start), parents=parents)
+                           engine=engine(cut.stop - cut.start), parents=parents, sinks=sinks, sliding=sliding)
 
     # -- prompt rows -----------------------------------------------------------------------------------------------------
     def _prompts(self, layer, q, pool, batch, rows, scale, out, found, parents=None):
@@ -200,7 +207,8 @@ class DeviceAttention:
         if parents is not None:
             raise NotImplementedError("draft trees (parents) are read in window rows: a row of more than the pool's "
                                       f"window of {pool.window} columns is a prompt row")
-        if self.prompt_reader == "prefill" and self._prefill_serves(pool, q):
+        special = getattr(self, "_sinks", None) is not None or getattr(self, "_sliding", 0)        # the decode kernel's rules
+        if self.prompt_reader == "prefill" and self._prefill_serves(pool, q) and not special:
             pages = pool.layer_pages(layer)
             scaled = len(pages) == 4
             multipliers = pool.scale_values[pool.layers[layer]] if pool.dtype == "fp8" else (1.0, 1.0)

@@ -17,6 +17,17 @@ constexpr int MERGE_WARPS = 8;
 
 // States a row of L positions has in the workspace: one a split, or two (a split's head and tail; m = -inf marks one
 // that holds nothing, and the folds pass it over) after a launch that deals tiles out evenly.
+// A sink logit (natural units of the scaled scores) joins a folded state (top in base-2 units, total relative to it):
+// the maximum and the sum take it, the outputs shrink by 2^(old top - new top).
+__device__ __forceinline__ void sink_fold(float sink, float& top, float& total, float& shrink) {
+    const float s2 = sink * LOG2E;
+    const float up = fmaxf(top, s2);
+    if (up == -INFINITY) return;
+    shrink = top == -INFINITY ? 0.f : ex2(top - up);
+    total = total * shrink + ex2(s2 - up);
+    top = up;
+}
+
 __device__ __forceinline__ int states_of(const crit_b200_attend_params& p, int64_t L) {
     const int n = (int)((L + p.chunk - 1) / p.chunk);
     return (p.flags & CRIT_B200_ATTEND_TCGEN05P) ? 2 * n : n;
@@ -34,7 +45,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     if (col >= count) return;
     const int64_t L = p.firsts[r] + count;
     const int nsplit = states_of(p, L);
-    if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS))) return;
+    if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS) && !p.sinks)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int DV = p.value_dim, per = DV >> 5;
     const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
@@ -77,7 +88,9 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     float total = 0.f;
 #pragma unroll
     for (int w = 0; w < MERGE_WARPS; ++w) total += sl[w] * ex2(sm[w] - sub);
-    const float inv = total > 0.f ? 1.f / total : 0.f;
+    float shrink = 1.f;                     // the head's sink, last: one position more without a value
+    if (p.sinks) sink_fold(p.sinks[head], top, total, shrink);
+    const float inv = total > 0.f ? shrink / total : 0.f;
     for (int c = threadIdx.x; c < DV; c += MERGE_WARPS * 32) {
         float o = 0.f;
 #pragma unroll
@@ -108,7 +121,7 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
     if (col >= count) return;
     const int64_t L = p.firsts[r] + count;
     const int nsplit = states_of(p, L);
-    if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS))) return;
+    if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS) && !p.sinks)) return;
     const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
     if (nsplit > p.max_splits || prow < 0 || prow >= p.partial_rows) {      // a plan too small for this row: nothing is read
         if (p.status && lane == 0) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
@@ -144,7 +157,9 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
             acc[0] += v.x * w, acc[1] += v.y * w;
         }
     }
-    const float inv = total > 0.f ? 1.f / total : 0.f;
+    float shrink = 1.f;                     // the head's sink, last: one position more without a value
+    if (p.sinks) sink_fold(p.sinks[head], top, total, shrink);
+    const float inv = total > 0.f ? shrink / total : 0.f;
     const int token = p.starts[r] + col;
     const int64_t at = (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head + lane * PER;
 #pragma unroll
@@ -437,7 +452,8 @@ static int check(const crit_b200_attend_params& p) {
         !aligned(p.value_pages, 16) || !aligned(p.out, 8) || p.out_stride_token % 4 || p.out_stride_head % 4)
         return CRIT_B200_EALIGN;
     if (p.head_dim < 1 || p.value_dim < 1 || p.head_dim > 1024 || p.value_dim > 1024) return CRIT_B200_EUNSUPPORTED;
-    if (p.max_splits > 1 || (p.flags & CRIT_B200_ATTEND_PARTIALS)) {
+    if (p.sliding < 0) return CRIT_B200_EINVAL;
+    if (p.max_splits > 1 || (p.flags & CRIT_B200_ATTEND_PARTIALS) || p.sinks) {
         // partial_rows <= 2^31, q_heads and max_splits below 2^31, value_dim + 2 <= 1026: compared by division, so that no
         // product of the four can wrap
         if (p.partial_rows < 1 || (!p.offsets && (int64_t)p.partial_rows < (int64_t)p.n_rows * p.columns)) return CRIT_B200_EINVAL;
@@ -553,8 +569,8 @@ static int launch_decode_ph(const crit_b200_attend_params& p, cudaStream_t s) {
 }
 
 static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
-    // draft trees (parents) are masked by the m16n8k16 kernel only
-    if (p.parents && (p.flags & (CRIT_B200_ATTEND_TCGEN05P | CRIT_B200_ATTEND_TCGEN05T | CRIT_B200_ATTEND_TCGEN05))) return CRIT_B200_EUNSUPPORTED;
+    // draft trees (parents), sliding windows and sinks are the m16n8k16 kernel's only
+    if ((p.parents || p.sinks || p.sliding > 0) && (p.flags & (CRIT_B200_ATTEND_TCGEN05P | CRIT_B200_ATTEND_TCGEN05T | CRIT_B200_ATTEND_TCGEN05))) return CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05P) return ph_serves(p) ? launch_decode_ph(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05T) return tc_serves(p) && p.n_rows <= SW_MAX_LIST ? launch_decode_sw(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05) return tc_serves(p) ? launch_decode_tc(p, s) : CRIT_B200_EUNSUPPORTED;
@@ -563,7 +579,7 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     // 32 query rows of accumulators a warp, which makes it issue-bound there), everything else, single-column decode
     // rows above all, to the m16n8k16 kernel.  A column's bits then depend on whether it is read alone or in a window;
     // CRIT_B200_ATTEND_MMA_SYNC keeps every launch on the m16n8k16 kernel, whose bits do not.
-    if (!(p.flags & CRIT_B200_ATTEND_MMA_SYNC) && p.columns > 1 && !p.parents && tc_serves(p)) return launch_decode_tc(p, s);
+    if (!(p.flags & CRIT_B200_ATTEND_MMA_SYNC) && p.columns > 1 && !p.parents && !p.sinks && p.sliding <= 0 && tc_serves(p)) return launch_decode_tc(p, s);
     const int G = p.q_heads / p.kv_heads;
     const int rows = p.columns * G;
     const int nt = row_tiles(rows, p.value_dim);
@@ -600,7 +616,7 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
 }
 
 static int launch_merge(const crit_b200_attend_params& p, cudaStream_t s) {
-    if (p.max_splits <= 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS)) return 0;
+    if (p.max_splits <= 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS) && !p.sinks) return 0;
     if (p.value_dim > 256 || p.value_dim % 32) return CRIT_B200_EUNSUPPORTED;
     if (p.max_splits <= 32) {
         const int64_t items = (int64_t)p.n_rows * p.columns * p.q_heads;

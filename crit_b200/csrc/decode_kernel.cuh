@@ -456,7 +456,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[u][nt][e] = u < have ? 0.f : -INFINITY;
             if (u >= have) continue;
-            masked |= pos0[u] + 16 > first32;
+            masked |= pos0[u] + 16 > first32 || p.sliding > 0;
             const int stage = (tbase + i + u) % C::STAGES;
             unsigned char* kst = tiles + stage * C::TILES;
             const float* scales = reinterpret_cast<const float*>(scales_ring + stage * scb);
@@ -539,6 +539,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
                     float x = s[u][nt][e] * (sl2 * ksc[u][e >> 1]);
                     if (masked) {
                         const int pos = pos0[u] + g + 8 * (e >> 1);
+                        if (p.sliding > 0 && pos <= lastpos[nt][e & 1] - p.sliding) x = -INFINITY;    // below the row's window
                         if (!tree) {
                             if (pos > lastpos[nt][e & 1]) x = -INFINITY;
                         } else if (lastpos[nt][e & 1] < 0 || (pos >= first32 && (pos - first32 >= count ||
@@ -688,7 +689,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     __syncthreads();
 
     const float vmul = (PK == 2 && smode == 0) ? p.value_multiplier : 1.f;
-    const bool whole = nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS);
+    const bool whole = nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS) && !p.sinks;     // (sinks join in the fold)
     const int64_t states = (int64_t)p.partial_rows * p.q_heads * p.max_splits;
     const int prow0 = p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns;
     // a plan too small for this unit (more splits or partial rows than the workspace was sized for): the unit's state

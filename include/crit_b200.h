@@ -194,6 +194,12 @@ typedef struct crit_b200_attend_params {
                                     first and, of the window, itself and its ancestors instead of the columns before it
                                     (paged_kv_attention/_kernels.py:154-165, :325-329).  Served by the m16n8k16 kernel; a
                                     launch that names a tcgen05 kernel with parents is CRIT_B200_EUNSUPPORTED */
+    const float* sinks;          /* NULL, or [q_heads] FP32: a sink logit a query head (in the units of the scaled scores), a
+                                    position more without a value: the fold of a row's splits adds it to the maximum and the
+                                    sum (and the lse), last.  The launch then takes the workspace whatever the splits
+                                    (device_attention.py:1301-1335, _kernels.py:597-598); m16n8k16 kernel only */
+    int32_t sliding;             /* 0, or the positions a column sees up to its own (a sliding window): positions at or
+                                    below its own minus `sliding` are masked (_kernels.py:332-333); m16n8k16 kernel only */
 } crit_b200_attend_params;
 
 /* out[0] positions per split this library would choose (a multiple of 16), out[1] bytes of dynamic shared memory a

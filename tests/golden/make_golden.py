@@ -280,6 +280,11 @@ def tree_windows():
     q = torch.randn(12, hq, d, generator=g).bfloat16()
     eager = device_attention.DeviceAttention(None, "torch", device="cpu")
     out, lse = eager.forward(0, q, pool, batch, parents=parents, lse=True)
+    # ... and the other visibility rules: a sliding window of 24 positions, a sink logit a head, and all three together
+    sinks = torch.randn(hq, generator=g) * 2.0
+    out_w, lse_w = eager.forward(0, q, pool, batch, lse=True, sliding=24)
+    out_s, lse_s = eager.forward(0, q, pool, batch, lse=True, sinks=sinks)
+    out_a, lse_a = eager.forward(0, q, pool, batch, parents=parents, lse=True, sinks=sinks, sliding=24)
     width = max(len(pool.table(s)) for s in lens)
     tables = np.zeros((2, width), np.int32)
     for i, s in enumerate(lens):
@@ -287,7 +292,9 @@ def tree_windows():
     np.savez_compressed(OUT / "tree_bf16.npz", q=q.float().numpy(), parents=parents.numpy(), tables=tables,
                         k_pages=pool.k[0].float().numpy(), v_pages=pool.v[0].float().numpy(), out=out.float().numpy(),
                         lse=lse.numpy(), geometry=np.array([hq, hkv, d, page]), firsts=np.array([150, 37]),
-                        counts=np.array([7, 5]), starts=np.array([0, 7]))
+                        counts=np.array([7, 5]), starts=np.array([0, 7]), sinks=sinks.numpy(), sliding=np.array(24),
+                        out_sliding=out_w.float().numpy(), lse_sliding=lse_w.numpy(), out_sinks=out_s.float().numpy(),
+                        lse_sinks=lse_s.numpy(), out_all=out_a.float().numpy(), lse_all=lse_a.numpy())
 
 
 # -- 6. merges ---------------------------------------------------------------------------------------------------------

@@ -650,3 +650,55 @@ def test_draft_trees_are_refused_by_the_tcgen05_kernels(pk):
     for engine in ("tcgen05", "tcgen05p"):
         with pytest.raises(NotImplementedError):
             cache.attend(queries(2, 16, 128, 1), [0], [0], [98], 2, parents=parents, engine=engine)
+
+
+# -- sliding windows and sinks --------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["bf16", "fp8:row", "fp8:page"])
+@pytest.mark.parametrize("hq,hkv,d", [(8, 2, 128), (24, 4, 256), (64, 8, 128)])
+@pytest.mark.parametrize("sliding,with_sinks,tree", [(100, False, False), (0, True, False), (37, True, False), (300, True, True)])
+@pytest.mark.parametrize("chunk", [64, 1024])
+def test_sliding_windows_and_sinks_match_the_oracle(pk, kind, hq, hkv, d, sliding, with_sinks, tree, chunk):
+    import oracle
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, hkv, d, d, 16, [130, 64, 9, 517, 1300])
+    cols = 4
+    firsts = [126, 61, 0, 400, 1296]
+    counts = [4, 3, 4, 2, 4]
+    rows, starts = [0, 1, 2, 3, 4], [0, 4, 8, 12, 16]
+    rng = np.random.default_rng(5)
+    parents = None
+    if tree:
+        parents = np.full(20, -1, np.int32)
+        for s, n in zip(starts, counts):
+            parents[s:s + n] = _random_tree(rng, n)
+    sinks = (rng.standard_normal(hq) * 2).astype(np.float32) if with_sinks else None
+    q = queries(20, hq, d, 3)
+    lse = torch.full((20, hq), 7.0, device="cuda")
+    out = cache.attend(q, rows, starts, firsts, cols, counts=counts, lse=lse, chunk=chunk, sliding=sliding,
+                       sinks=torch.tensor(sinks, device="cuda") if with_sinks else None,
+                       parents=torch.tensor(parents, device="cuda") if tree else None)
+    assert pk.status() == 0
+    k, v = cache.stored()
+    want, want_lse = oracle.attend_tree(q.float().cpu().numpy(), k, v, cache.tables.cpu().numpy(), rows, starts, firsts, cols,
+                                        16, parents, counts=counts, sinks=sinks, sliding=sliding)
+    tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
+    assert_attention_close(out, lse, want, want_lse, tokens)
+
+
+@pytest.mark.parametrize("case", ["sliding", "sinks", "all"])
+def test_sliding_windows_and_sinks_match_the_references_torch_path(pk, golden, case):
+    from helpers import assert_attention_close
+    f = golden("tree_bf16.npz")
+    hq, hkv, d, page = (int(x) for x in f["geometry"])
+    dev = "cuda"
+    k = torch.tensor(f["k_pages"]).bfloat16().to(dev).reshape(-1, page, hkv, d)
+    v = torch.tensor(f["v_pages"]).bfloat16().to(dev).reshape(-1, page, hkv, d)
+    q = torch.tensor(f["q"]).bfloat16().to(dev)
+    lse = torch.empty(12, hq, device=dev)
+    out = pk.attend(q, k, v, "bf16", torch.tensor(f["tables"], device=dev), torch.tensor([0, 1], dtype=torch.int32, device=dev),
+                    torch.tensor(f["starts"], dtype=torch.int32, device=dev), torch.tensor(f["firsts"], dtype=torch.int64, device=dev),
+                    7, page, counts=torch.tensor(f["counts"], dtype=torch.int32, device=dev), lse=lse,
+                    parents=torch.tensor(f["parents"], device=dev) if case == "all" else None,
+                    sinks=torch.tensor(f["sinks"], device=dev) if case != "sliding" else None,
+                    sliding=int(f["sliding"]) if case != "sinks" else 0)
+    assert_attention_close(out, lse, f["out_" + case], f["lse_" + case], list(range(12)))

@@ -257,3 +257,19 @@ def test_tree_windows_match_the_references_torch_path(golden):
     a, la = oracle.attend_tree(f["q"], k, v, f["tables"], [0, 1], f["starts"], f["firsts"], 7, page, chain, counts=f["counts"])
     b, lb = oracle.attend(f["q"], k, v, f["tables"], [0, 1], f["starts"], f["firsts"], 7, page, counts=f["counts"])
     assert np.array_equal(a, b) and np.array_equal(la, lb)
+
+
+@pytest.mark.parametrize("case", ["sliding", "sinks", "all"])
+def test_sliding_windows_and_sinks_match_the_references_torch_path(golden, case):
+    """A sliding window of 24 positions, a sink logit a head, and both over a draft tree: the oracle against the
+    reference's own torch windows (tests/golden/make_golden.py: tree_windows)."""
+    import oracle
+    f = golden("tree_bf16.npz")
+    hq, hkv, d, page = (int(x) for x in f["geometry"])
+    k, v = f["k_pages"].reshape(-1, hkv, d), f["v_pages"].reshape(-1, hkv, d)
+    out, lse = oracle.attend_tree(f["q"], k, v, f["tables"], [0, 1], f["starts"], f["firsts"], 7, page,
+                                  f["parents"] if case == "all" else None, counts=f["counts"],
+                                  sinks=f["sinks"] if case != "sliding" else None,
+                                  sliding=int(f["sliding"]) if case != "sinks" else 0)
+    assert np.abs(out - f["out_" + case]).max() <= 8e-3          # the reference's outputs are bf16
+    assert np.abs(lse - f["lse_" + case]).max() <= 2e-5

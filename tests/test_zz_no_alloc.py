@@ -5,6 +5,7 @@ caller's workspace.  Called through the C ABI, twice in a row over the same shar
 ordinary entry point gives with a caller-owned workspace; a launch that needs more partials than the array holds is
 refused with its own error and launches nothing.  Collected last, so a failure here stops no other test."""
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -36,10 +37,11 @@ def test_the_static_scratch_entry_point_gives_the_ordinary_ones_bits_twice_in_a_
         p, held = _params(pk, cache, q, want, want_lse, rows, starts, firsts, columns, chunk, workspace=space)
         assert lib.crit_b200_attend(ctypes.byref(p), stream) == 0
         p, held2 = _params(pk, cache, q, got, got_lse, rows, starts, firsts, columns, chunk)     # no workspace at all
+        gc.collect()            # (tensors other tests left behind go now, not during the call)
         before = torch.cuda.memory_allocated()
         assert lib.crit_b200_attend_static(ctypes.byref(p), stream) == 0
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.memory_allocated() <= before          # torch's allocator gave the call nothing
         torch.testing.assert_close(got.float(), want.float(), atol=0, rtol=0)
         torch.testing.assert_close(got_lse, want_lse, atol=0, rtol=0)
         assert want.float().abs().sum() > 0
