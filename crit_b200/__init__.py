@@ -403,7 +403,8 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     row, -1 for none (a draft tree in topological order): a column then sees the context before its row's first position,
     itself and its ancestors.  sinks [heads] FP32: a logit a query head that joins the softmax's maximum and sum (and
     the lse) without a value; sliding: the positions a column sees up to its own, 0 for all (all three on the m16n8k16
-    kernel).  blocks, fresh and derive are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
+    kernel).  blocks [tokens][k] int32 with block_size: the KV blocks (block_size positions each, -1 for none) a token
+    sees, as a mask over the m16n8k16 kernel's tiles (every position is still read).  fresh and derive are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
     None (TMA tiled loads for 16-bit pages of 128- or 256-wide heads, cp.async otherwise: what measured faster), "tma"
     (TMA wherever the geometry allows it) or "cp.async" (never TMA); the same bits either way.  persistent: a fixed
     number of blocks walk a work list built on the device from the rows' lengths, instead of one block per (split, kv
@@ -413,7 +414,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     shards: a crit_b200.dist.ShardMerge: these pages hold one KV range of a context sharded over the ranks; every
     split state stays in the workspace, the fold of this rank's splits is stored into every rank's exchange buffer and
     out / lse get the merge over all ranks (three launches: decode, fold + push, wait + merge)."""
-    _refuse(blocks=blocks, fresh=fresh, derive=derive)
+    _refuse(fresh=fresh, derive=derive)
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
     T, hq, d = q.shape
@@ -445,6 +446,14 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
         if parents.dtype not in (torch.int32, torch.int64) or parents.numel() != T:
             raise ValueError("parents are int32 or int64, one per token of q")
         parents = _cuda(parents, "parents").to(torch.int32).contiguous()
+        engine = "mma.sync"
+    if blocks is not None:
+        # block lists: blocks [tokens][k] KV block ids (-1 for none) of block_size positions: a token sees only those
+        if engine not in (None, "mma.sync"):
+            raise NotImplementedError("block lists are served by the m16n8k16 kernel: engine None or mma.sync")
+        if blocks.dim() != 2 or blocks.shape[0] != T or not block_size or int(block_size) < 1:
+            raise ValueError("blocks are [tokens][k] block ids, with the positions a block holds (block_size)")
+        blocks = _cuda(blocks, "blocks").to(torch.int32).contiguous()
         engine = "mma.sync"
     sliding = int(sliding or 0)
     if sinks is not None or sliding:
@@ -506,6 +515,8 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])
     p.parents, p.sinks, p.sliding = _ptr(parents), _ptr(sinks), sliding
+    if blocks is not None:
+        p.blocks, p.blocks_k, p.block_size = _ptr(blocks), blocks.shape[1], int(block_size)
     lib = _lib.load()
     if shards is not None:
         if lse is None:
@@ -551,7 +562,8 @@ def merge_shards(outs, lses, dtype=None):
 
 def prefill_serves(head_dim, value_dim, q_dtype, kind, page):
     """Whether prefill() reads a cache of this geometry (else prompt rows go through attend in pieces)."""
-    return head_dim == value_dim and head_dim in (64, 128) and page % TILE == 0 and kind in KINDS and \
+    widths = (64, 128, 256) if kind in ("bf16", "fp16") else (64, 128)        # 256-wide heads: 16-bit pages (m16n8k16 tiles)
+    return head_dim == value_dim and head_dim in widths and page % TILE == 0 and kind in KINDS and \
         q_dtype in (torch.bfloat16, torch.float16)
 
 

@@ -50,7 +50,8 @@ class AttendParams(Structure):
                 ("page", c_int32), ("kind", c_int32), ("page_dtype", c_int32), ("q_dtype", c_int32),
                 ("chunk", c_int32), ("max_splits", c_int32), ("flags", c_int32),
                 ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float),
-                ("parents", c_void_p), ("sinks", c_void_p), ("sliding", c_int32)]
+                ("parents", c_void_p), ("sinks", c_void_p), ("sliding", c_int32),
+                ("blocks_k", c_int32), ("block_size", c_int32), ("blocks", c_void_p)]
 
 
 class MergeShardsParams(Structure):

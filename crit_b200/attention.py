@@ -97,14 +97,17 @@ class DeviceAttention:
         step already); each token sees its sequence's positions up to its own.  lse: also return each token's
         log-sum-exp ([tokens][heads] FP32).  Returns out [tokens][heads][value dim] in the queries' dtype (and lse)."""
         import torch
-        if blocks is not None or latent:
-            raise NotImplementedError("crit_b200's attention does not serve block lists or latent attention yet")
+        if latent:
+            raise NotImplementedError("crit_b200's attention does not serve latent attention yet")
+        if blocks is not None and (not block_size or blocks.dim() != 2 or blocks.shape[0] != queries.shape[0]):
+            raise ValueError("blocks are [tokens][k] KV block ids with block_size positions each")
         if sinks is not None:
             sinks = sinks.reshape(-1).float().contiguous()
             if sinks.numel() != queries.shape[1] or not sinks.is_cuda:
                 raise ValueError("sinks are one logit a query head, on the queries' device")
         # (the call's sinks and sliding window, for the launches below: reference device_attention.py:188-189, :382-386)
         self._sinks, self._sliding = sinks, int(sliding or 0)
+        self._blocks = (blocks, int(block_size)) if blocks is not None else None
         if parents is not None and getattr(batch, "prompt", False):
             raise NotImplementedError("draft trees (parents) are read in window rows, not in a staged prompt chunk")
         if not queries.is_cuda:
@@ -136,7 +139,7 @@ class DeviceAttention:
                 self._windows(layer, q, pool, self._step_windows(pool, batch, short, q.device), scale, out, found, parents)
             self._prompts(layer, q, pool, batch, [r for r in range(batch.rows) if batch.row(r)[2] > pool.window],
                           scale, out, found, parents)
-        self._sinks, self._sliding = None, 0
+        self._sinks, self._sliding, self._blocks = None, 0, None
         out = out if out.dtype == queries.dtype else out.to(queries.dtype)
         return (out, found) if lse else out
 
@@ -165,7 +168,8 @@ class DeviceAttention:
         # the kernel the step's windows run on: the kernels' choice for the whole step, or the one the option names
         named = kernels.engine_for(*geometry, len(meta), positions, None if self.window_engine == "auto" else self.window_engine)
         sinks, sliding = getattr(self, "_sinks", None), getattr(self, "_sliding", 0)
-        if parents is not None or sinks is not None or sliding:
+        listed = getattr(self, "_blocks", None)
+        if parents is not None or sinks is not None or sliding or listed is not None:
             named = "mma.sync"             # draft trees, sinks and sliding windows are the m16n8k16 kernel's
         chunk = self.chunk or kernels.chunk_for(pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, pool.page, pool.dtype,
                                                 named, meta.columns)
@@ -198,7 +202,8 @@ class DeviceAttention:
                            tokens=tokens if offsets is not None else None,
                            key_scales=pages[2] if scaled else None, value_scales=pages[3] if scaled else None,
                            multipliers=multipliers, scale=scale, chunk=chunk, out=out, lse=found, workspace=workspace,
-                           engine=engine(cut.stop - cut.start), parents=parents, sinks=sinks, sliding=sliding)
+                           engine=engine(cut.stop - cut.start), parents=parents, sinks=sinks, sliding=sliding,
+                           blocks=listed[0] if listed else None, block_size=listed[1] if listed else None)
 
     # -- prompt rows -----------------------------------------------------------------------------------------------------
     def _prompts(self, layer, q, pool, batch, rows, scale, out, found, parents=None):
@@ -207,7 +212,8 @@ class DeviceAttention:
         if parents is not None:
             raise NotImplementedError("draft trees (parents) are read in window rows: a row of more than the pool's "
                                       f"window of {pool.window} columns is a prompt row")
-        special = getattr(self, "_sinks", None) is not None or getattr(self, "_sliding", 0)        # the decode kernel's rules
+        special = (getattr(self, "_sinks", None) is not None or getattr(self, "_sliding", 0) or
+                   getattr(self, "_blocks", None) is not None)                                  # the decode kernel's rules
         if self.prompt_reader == "prefill" and self._prefill_serves(pool, q) and not special:
             pages = pool.layer_pages(layer)
             scaled = len(pages) == 4

@@ -452,7 +452,7 @@ static int check(const crit_b200_attend_params& p) {
         !aligned(p.value_pages, 16) || !aligned(p.out, 8) || p.out_stride_token % 4 || p.out_stride_head % 4)
         return CRIT_B200_EALIGN;
     if (p.head_dim < 1 || p.value_dim < 1 || p.head_dim > 1024 || p.value_dim > 1024) return CRIT_B200_EUNSUPPORTED;
-    if (p.sliding < 0) return CRIT_B200_EINVAL;
+    if (p.sliding < 0 || (p.blocks && (p.blocks_k < 1 || p.block_size < 1))) return CRIT_B200_EINVAL;
     if (p.max_splits > 1 || (p.flags & CRIT_B200_ATTEND_PARTIALS) || p.sinks) {
         // partial_rows <= 2^31, q_heads and max_splits below 2^31, value_dim + 2 <= 1026: compared by division, so that no
         // product of the four can wrap
@@ -569,8 +569,8 @@ static int launch_decode_ph(const crit_b200_attend_params& p, cudaStream_t s) {
 }
 
 static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
-    // draft trees (parents), sliding windows and sinks are the m16n8k16 kernel's only
-    if ((p.parents || p.sinks || p.sliding > 0) && (p.flags & (CRIT_B200_ATTEND_TCGEN05P | CRIT_B200_ATTEND_TCGEN05T | CRIT_B200_ATTEND_TCGEN05))) return CRIT_B200_EUNSUPPORTED;
+    // draft trees (parents), sliding windows, sinks and block lists are the m16n8k16 kernel's only
+    if ((p.parents || p.sinks || p.sliding > 0 || p.blocks) && (p.flags & (CRIT_B200_ATTEND_TCGEN05P | CRIT_B200_ATTEND_TCGEN05T | CRIT_B200_ATTEND_TCGEN05))) return CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05P) return ph_serves(p) ? launch_decode_ph(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05T) return tc_serves(p) && p.n_rows <= SW_MAX_LIST ? launch_decode_sw(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05) return tc_serves(p) ? launch_decode_tc(p, s) : CRIT_B200_EUNSUPPORTED;
@@ -579,7 +579,7 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     // 32 query rows of accumulators a warp, which makes it issue-bound there), everything else, single-column decode
     // rows above all, to the m16n8k16 kernel.  A column's bits then depend on whether it is read alone or in a window;
     // CRIT_B200_ATTEND_MMA_SYNC keeps every launch on the m16n8k16 kernel, whose bits do not.
-    if (!(p.flags & CRIT_B200_ATTEND_MMA_SYNC) && p.columns > 1 && !p.parents && !p.sinks && p.sliding <= 0 && tc_serves(p)) return launch_decode_tc(p, s);
+    if (!(p.flags & CRIT_B200_ATTEND_MMA_SYNC) && p.columns > 1 && !p.parents && !p.sinks && p.sliding <= 0 && !p.blocks && tc_serves(p)) return launch_decode_tc(p, s);
     const int G = p.q_heads / p.kv_heads;
     const int rows = p.columns * G;
     const int nt = row_tiles(rows, p.value_dim);

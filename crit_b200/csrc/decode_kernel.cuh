@@ -456,7 +456,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[u][nt][e] = u < have ? 0.f : -INFINITY;
             if (u >= have) continue;
-            masked |= pos0[u] + 16 > first32 || p.sliding > 0;
+            masked |= pos0[u] + 16 > first32 || p.sliding > 0 || p.blocks != nullptr;
             const int stage = (tbase + i + u) % C::STAGES;
             unsigned char* kst = tiles + stage * C::TILES;
             const float* scales = reinterpret_cast<const float*>(scales_ring + stage * scb);
@@ -540,6 +540,13 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
                     if (masked) {
                         const int pos = pos0[u] + g + 8 * (e >> 1);
                         if (p.sliding > 0 && pos <= lastpos[nt][e & 1] - p.sliding) x = -INFINITY;    // below the row's window
+                        if (p.blocks && lastpos[nt][e & 1] >= 0) {      // block lists: only the positions of the token's blocks
+                            const int32_t* listed = p.blocks + (int64_t)(p.starts[r] + (lastpos[nt][e & 1] - first32)) * p.blocks_k;
+                            const int at = pos / p.block_size;
+                            bool member = false;
+                            for (int j = 0; j < p.blocks_k; ++j) member |= listed[j] == at;
+                            if (!member) x = -INFINITY;
+                        }
                         if (!tree) {
                             if (pos > lastpos[nt][e & 1]) x = -INFINITY;
                         } else if (lastpos[nt][e & 1] < 0 || (pos >= first32 && (pos - first32 >= count ||

@@ -347,6 +347,7 @@ template <int PK>
 static int prefill_pick(int d, prefill_fn* fn, int* smem) {
     if (d == 64) *fn = prefill_kernel<64, PK>, *smem = PrefillCfg<64, PK>::SMEM;
     else if (d == 128) *fn = prefill_kernel<128, PK>, *smem = PrefillCfg<128, PK>::SMEM;
+    else if (d == 256 && PK < 2) *fn = prefill_kernel<256, PK < 2 ? PK : 0>, *smem = PrefillCfg<256, PK < 2 ? PK : 0>::SMEM;   // 16-bit pages
     else return CRIT_B200_EUNSUPPORTED;
     return 0;
 }

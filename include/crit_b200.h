@@ -200,6 +200,10 @@ typedef struct crit_b200_attend_params {
                                     (device_attention.py:1301-1335, _kernels.py:597-598); m16n8k16 kernel only */
     int32_t sliding;             /* 0, or the positions a column sees up to its own (a sliding window): positions at or
                                     below its own minus `sliding` are masked (_kernels.py:332-333); m16n8k16 kernel only */
+    int32_t blocks_k, block_size;/* with `blocks`: ids a token lists, positions a block holds */
+    const int32_t* blocks;       /* NULL, or [tokens of q][blocks_k] KV block ids, -1 for none: of what the other rules
+                                    leave, a token sees only the positions of its listed blocks (block-sparse lists,
+                                    _kernels.py:481-555; here as a mask: every position is still read); m16n8k16 kernel only */
 } crit_b200_attend_params;
 
 /* out[0] positions per split this library would choose (a multiple of 16), out[1] bytes of dynamic shared memory a

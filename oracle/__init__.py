@@ -161,11 +161,12 @@ def attend(q, k, v, tables, rows, starts, firsts, columns, page, scale=None, cou
 
 
 def attend_tree(q, k, v, tables, rows, starts, firsts, columns, page, parents, scale=None, counts=None, sinks=None,
-                sliding=0):
+                sliding=0, blocks=None, block_size=0):
     """attend() with the reference's other visibility rules.  parents [T] (or None: causal) is each token's parent column
     in its row, -1 for none: a column sees the context before its row's first position and, of the window, itself and its
     ancestors.  sliding > 0: a column sees only the `sliding` positions up to its own.  sinks [hq] (or None): a logit a
-    query head that joins the softmax's maximum and sum (and the lse) without a value.
+    query head that joins the softmax's maximum and sum (and the lse) without a value.  blocks [T][k] (or None): the KV
+    blocks of block_size positions a token sees, -1 for none.
     ref: paged_kv_attention/_kernels.py:154-165, :325-333; device_attention.py:1301-1335."""
     q, k, v = _c(q, np.float32), _c(k, np.float32), _c(v, np.float32)
     tables = _c(tables, np.int32)
@@ -174,6 +175,7 @@ def attend_tree(q, k, v, tables, rows, starts, firsts, columns, page, parents, s
     rows, starts = _c(rows, np.int32), _c(starts, np.int32)
     parents = _c(parents, np.int32) if parents is not None else None
     sinks = _c(sinks, np.float32) if sinks is not None else None
+    blocks = _c(blocks, np.int32) if blocks is not None else None
     firsts = _c(firsts, np.int64)
     counts = _c(counts, np.int32) if counts is not None else None
     T, hq, d = q.shape
@@ -184,7 +186,8 @@ def attend_tree(q, k, v, tables, rows, starts, firsts, columns, page, parents, s
     i64 = ctypes.c_int64
     lib().crit_oracle_attend_tree(_p(q), i64(hq), i64(d), _p(k), _p(v), i64(hkv), i64(dv), _p(tables),
                                   i64(tables.shape[1]), _p(rows), _p(starts), _p(counts), _p(firsts), _p(parents),
-                                  _p(sinks), i64(int(sliding)), i64(rows.size), i64(columns), i64(page),
+                                  _p(sinks), i64(int(sliding)), _p(blocks), i64(blocks.shape[1] if blocks is not None else 0),
+                                  i64(int(block_size)), i64(rows.size), i64(columns), i64(page),
                                   ctypes.c_float(scale), _p(out), _p(lse))
     return out, lse
 

@@ -285,6 +285,17 @@ def tree_windows():
     out_w, lse_w = eager.forward(0, q, pool, batch, lse=True, sliding=24)
     out_s, lse_s = eager.forward(0, q, pool, batch, lse=True, sinks=sinks)
     out_a, lse_a = eager.forward(0, q, pool, batch, parents=parents, lse=True, sinks=sinks, sliding=24)
+    # ... and block lists: each token sees 3 KV blocks of 16 positions (-1: none), its own position's block among them
+    blocks = torch.full((12, 3), -1, dtype=torch.int32)
+    positions = [150 + c for c in range(7)] + [37 + c for c in range(5)]
+    for t, pos in enumerate(positions):
+        own = pos // 16
+        picks = torch.randperm(own + 1, generator=g)[:2].tolist()
+        blocks[t, 0] = own
+        blocks[t, 1] = picks[0]
+        if t % 3:
+            blocks[t, 2] = picks[-1]
+    out_b, lse_b = eager.forward(0, q, pool, batch, blocks=blocks, block_size=16, lse=True)
     width = max(len(pool.table(s)) for s in lens)
     tables = np.zeros((2, width), np.int32)
     for i, s in enumerate(lens):
@@ -294,7 +305,8 @@ def tree_windows():
                         lse=lse.numpy(), geometry=np.array([hq, hkv, d, page]), firsts=np.array([150, 37]),
                         counts=np.array([7, 5]), starts=np.array([0, 7]), sinks=sinks.numpy(), sliding=np.array(24),
                         out_sliding=out_w.float().numpy(), lse_sliding=lse_w.numpy(), out_sinks=out_s.float().numpy(),
-                        lse_sinks=lse_s.numpy(), out_all=out_a.float().numpy(), lse_all=lse_a.numpy())
+                        lse_sinks=lse_s.numpy(), out_all=out_a.float().numpy(), lse_all=lse_a.numpy(), blocks=blocks.numpy(),
+                        out_blocks=out_b.float().numpy(), lse_blocks=lse_b.numpy())
 
 
 # -- 6. merges ---------------------------------------------------------------------------------------------------------

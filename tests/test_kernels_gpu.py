@@ -463,6 +463,20 @@ def test_prompt_chunks_match_the_oracle(pk, kind, hq, hkv, d, position, tokens):
 
 
 @pytest.mark.parametrize("kind", ["bf16", "fp16"])
+@pytest.mark.parametrize("position,tokens", [(0, 70), (333, 150), (1000, 1), (2000, 300)])
+def test_prompt_chunks_of_256_wide_heads_match_the_oracle(pk, kind, position, tokens):
+    """24q/4kv x 256 (the long-context model's geometry) over 16-bit pages: the m16n8k16 prefill kernel."""
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, 4, 256, 256, 64, [position + tokens, 40], spare=20)
+    assert pk.prefill_serves(256, 256, torch.bfloat16, kind, 64) and not pk.prefill_serves(256, 256, torch.bfloat16, "fp8", 64)
+    q = queries(tokens, 24, 256, 13, torch.float16 if kind == "fp16" else torch.bfloat16)
+    lse = torch.empty(tokens, 24, device="cuda")
+    out = pk.prefill(q, cache.k, cache.v, kind, cache.tables[0].contiguous(), position, 64, lse=lse)
+    want, want_lse = cache.oracle(q, [0], [0], [position], tokens)
+    assert_attention_close(out, lse, want, want_lse, list(range(tokens)))
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16"])
 @pytest.mark.parametrize("hq,hkv", [(8, 2), (32, 8), (5, 1), (16, 16)])
 @pytest.mark.parametrize("position,tokens", [(0, 70), (333, 150), (1000, 1), (64, 64), (0, 32), (4090, 300)])
 def test_prompt_chunks_on_tcgen05_tiles_match_the_oracle(pk, kind, hq, hkv, position, tokens):
@@ -702,3 +716,49 @@ def test_sliding_windows_and_sinks_match_the_references_torch_path(pk, golden, c
                     sinks=torch.tensor(f["sinks"], device=dev) if case != "sliding" else None,
                     sliding=int(f["sliding"]) if case != "sinks" else 0)
     assert_attention_close(out, lse, f["out_" + case], f["lse_" + case], list(range(12)))
+
+
+# -- block lists ------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["bf16", "fp8:row", "fp8:page"])
+@pytest.mark.parametrize("hq,hkv,d", [(8, 2, 128), (24, 4, 256), (64, 8, 128)])
+@pytest.mark.parametrize("chunk", [64, 1024])
+def test_block_lists_match_the_oracle(pk, kind, hq, hkv, d, chunk):
+    import oracle
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, hkv, d, d, 16, [130, 64, 9, 517, 1300])
+    cols, firsts, counts = 4, [126, 61, 0, 400, 1296], [4, 3, 4, 2, 4]
+    rows, starts = [0, 1, 2, 3, 4], [0, 4, 8, 12, 16]
+    rng = np.random.default_rng(8)
+    blocks = np.full((20, 5), -1, np.int32)
+    for s, n, first in zip(starts, counts, firsts):
+        for c in range(n):
+            own = (first + c) // 32
+            picks = rng.permutation(own + 1)[:rng.integers(1, 5)]
+            blocks[s + c, :len(picks)] = picks
+            blocks[s + c, 4] = own if (s + c) % 4 else -1           # most tokens see their own block; a few may see nothing
+    q = queries(20, hq, d, 3)
+    lse = torch.full((20, hq), 7.0, device="cuda")
+    out = cache.attend(q, rows, starts, firsts, cols, counts=counts, lse=lse, chunk=chunk, blocks=torch.tensor(blocks, device="cuda"),
+                       block_size=32)
+    assert pk.status() == 0
+    k, v = cache.stored()
+    want, want_lse = oracle.attend_tree(q.float().cpu().numpy(), k, v, cache.tables.cpu().numpy(), rows, starts, firsts, cols,
+                                        16, None, counts=counts, blocks=blocks, block_size=32)
+    tokens = [s + c for s, n in zip(starts, counts) for c in range(n)]
+    assert_attention_close(out, lse, want, want_lse, tokens)
+
+
+def test_block_lists_match_the_references_torch_path(pk, golden):
+    from helpers import assert_attention_close
+    f = golden("tree_bf16.npz")
+    hq, hkv, d, page = (int(x) for x in f["geometry"])
+    dev = "cuda"
+    k = torch.tensor(f["k_pages"]).bfloat16().to(dev).reshape(-1, page, hkv, d)
+    v = torch.tensor(f["v_pages"]).bfloat16().to(dev).reshape(-1, page, hkv, d)
+    q = torch.tensor(f["q"]).bfloat16().to(dev)
+    lse = torch.empty(12, hq, device=dev)
+    out = pk.attend(q, k, v, "bf16", torch.tensor(f["tables"], device=dev), torch.tensor([0, 1], dtype=torch.int32, device=dev),
+                    torch.tensor(f["starts"], dtype=torch.int32, device=dev), torch.tensor(f["firsts"], dtype=torch.int64, device=dev),
+                    7, page, counts=torch.tensor(f["counts"], dtype=torch.int32, device=dev), lse=lse,
+                    blocks=torch.tensor(f["blocks"], device=dev), block_size=16)
+    assert_attention_close(out, lse, f["out_blocks"], f["lse_blocks"], list(range(12)))

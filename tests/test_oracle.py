@@ -273,3 +273,15 @@ def test_sliding_windows_and_sinks_match_the_references_torch_path(golden, case)
                                   sliding=int(f["sliding"]) if case != "sinks" else 0)
     assert np.abs(out - f["out_" + case]).max() <= 8e-3          # the reference's outputs are bf16
     assert np.abs(lse - f["lse_" + case]).max() <= 2e-5
+
+
+def test_block_lists_match_the_references_torch_path(golden):
+    """Each token sees only its listed KV blocks of 16 positions (tests/golden/make_golden.py: tree_windows)."""
+    import oracle
+    f = golden("tree_bf16.npz")
+    hq, hkv, d, page = (int(x) for x in f["geometry"])
+    k, v = f["k_pages"].reshape(-1, hkv, d), f["v_pages"].reshape(-1, hkv, d)
+    out, lse = oracle.attend_tree(f["q"], k, v, f["tables"], [0, 1], f["starts"], f["firsts"], 7, page, None,
+                                  counts=f["counts"], blocks=f["blocks"], block_size=16)
+    assert np.abs(out - f["out_blocks"]).max() <= 8e-3
+    assert np.abs(lse - f["lse_blocks"]).max() <= 2e-5
