@@ -374,6 +374,30 @@ def move_rows(store, source, target):
         _lib.check(_lib.load().crit_b200_move_rows(ctypes.byref(p), _stream(store.device)), "crit_b200.move_rows")
 
 
+def _listed_rows(tables, rows, starts, counts, firsts, blocks, block_size, page, columns, out, lse):
+    """Block lists as page tables of their own (crit_b200_compact_blocks): (tables, rows, starts, firsts, counts) of
+    one-column rows, a row a token, whose tables hold the pages of the token's listed blocks only; tokens that see
+    nothing get zeros in out (and -inf in lse) here."""
+    device = tables.device
+    R = int(starts.shape[0])
+    n, per = R * columns, block_size // page
+    t2 = torch.empty(n, blocks.shape[1] * per, dtype=torch.int32, device=device)
+    c2 = torch.empty(n, dtype=torch.int32, device=device)
+    f2 = torch.empty(n, dtype=torch.int64, device=device)
+    p = _lib.CompactParams()
+    p.tables, p.rows, p.starts, p.counts, p.firsts, p.blocks = (_ptr(x) for x in (tables, rows, starts, counts, firsts, blocks))
+    p.out_tables, p.out_counts, p.out_firsts, p.out, p.lse = _ptr(t2), _ptr(c2), _ptr(f2), _ptr(out), _ptr(lse)
+    p.n_rows, p.table_stride, p.table_width = R, tables.stride(0), tables.shape[1]
+    p.out_stride_token, p.out_stride_head = out.stride(0), out.stride(1)
+    p.columns, p.blocks_k, p.block_size, p.page = columns, blocks.shape[1], block_size, page
+    p.dump = 0              # (entries past a row's listed pages are never read: its last position ends before them)
+    p.q_heads, p.value_dim, p.out_dtype = out.shape[1], out.shape[2], _DTYPES[out.dtype]
+    with torch.cuda.device(device):
+        _lib.check(_lib.load().crit_b200_compact_blocks(ctypes.byref(p), _stream(device)), "crit_b200.attend (block lists)")
+    tokens = (starts[:, None] + torch.arange(columns, dtype=torch.int32, device=device)[None, :]).reshape(-1).contiguous()
+    return t2, torch.arange(n, dtype=torch.int32, device=device), tokens, f2, c2
+
+
 # -- decode and verify windows ------------------------------------------------------------------------------------------
 def _refuse(**given):
     asked = [name for name, value in given.items()
@@ -404,7 +428,10 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     itself and its ancestors.  sinks [heads] FP32: a logit a query head that joins the softmax's maximum and sum (and
     the lse) without a value; sliding: the positions a column sees up to its own, 0 for all (all three on the m16n8k16
     kernel).  blocks [tokens][k] int32 with block_size: the KV blocks (block_size positions each, -1 for none) a token
-    sees, as a mask over the m16n8k16 kernel's tiles (every position is still read).  fresh and derive are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
+    sees.  Where block_size is a multiple of the page (and no tree, sink or sliding window is asked for) the launch
+    reads the listed blocks only: every token becomes a one-column row over a page table of its blocks, built on the
+    device, on whichever kernel serves it; otherwise the lists are a mask over the m16n8k16 kernel's tiles (every
+    position is read).  fresh and derive are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
     None (TMA tiled loads for 16-bit pages of 128- or 256-wide heads, cp.async otherwise: what measured faster), "tma"
     (TMA wherever the geometry allows it) or "cp.async" (never TMA); the same bits either way.  persistent: a fixed
     number of blocks walk a work list built on the device from the rows' lengths, instead of one block per (split, kv
@@ -449,12 +476,23 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
         engine = "mma.sync"
     if blocks is not None:
         # block lists: blocks [tokens][k] KV block ids (-1 for none) of block_size positions: a token sees only those
-        if engine not in (None, "mma.sync"):
-            raise NotImplementedError("block lists are served by the m16n8k16 kernel: engine None or mma.sync")
         if blocks.dim() != 2 or blocks.shape[0] != T or not block_size or int(block_size) < 1:
             raise ValueError("blocks are [tokens][k] block ids, with the positions a block holds (block_size)")
         blocks = _cuda(blocks, "blocks").to(torch.int32).contiguous()
-        engine = "mma.sync"
+        if (int(block_size) % page == 0 and parents is None and sinks is None and not sliding and offsets is None and
+                shards is None and launch == "both" and not torch.cuda.is_current_stream_capturing()):
+            # the sparse reader: every token becomes a row of one column over a page table of its listed blocks only
+            # (built on the device), so the launch reads those blocks and nothing else, on whichever kernel serves it
+            out = torch.empty(T, hq, dv, dtype=q.dtype, device=q.device) if out is None else out
+            listed = _listed_rows(tables, rows, starts, counts, firsts, blocks, int(block_size), page, int(columns), out, lse)
+            return attend(q, key_pages, value_pages, kind, listed[0], listed[1], listed[2], listed[3], 1, page,
+                          counts=listed[4], key_scales=key_scales, value_scales=value_scales, multipliers=multipliers,
+                          scale=scale, partitions=partitions, out=out, lse=lse, workspace=workspace, chunk=chunk,
+                          engine=engine)
+        if engine not in (None, "mma.sync"):
+            raise NotImplementedError("block lists of blocks that are no multiple of the page, or with a tree, sinks or a "
+                                      "sliding window, are a mask of the m16n8k16 kernel: engine None or mma.sync")
+        engine = "mma.sync"             # as a mask over the m16n8k16 kernel's tiles: every position is read
     sliding = int(sliding or 0)
     if sinks is not None or sliding:
         # a sink logit a query head (joins the softmax's maximum and sum, and the lse, in the fold of the splits), and a

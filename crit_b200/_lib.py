@@ -38,6 +38,15 @@ class MoveParams(Structure):
                 ("slots", c_int64), ("row_bytes", c_int64), ("layers", c_int32), ("status", c_void_p)]
 
 
+class CompactParams(Structure):
+    _fields_ = [("tables", c_void_p), ("rows", c_void_p), ("starts", c_void_p), ("counts", c_void_p), ("firsts", c_void_p),
+                ("blocks", c_void_p), ("out_tables", c_void_p), ("out_counts", c_void_p), ("out_firsts", c_void_p),
+                ("out", c_void_p), ("lse", c_void_p), ("n_rows", c_int64), ("table_stride", c_int64),
+                ("out_stride_token", c_int64), ("out_stride_head", c_int64), ("table_width", c_int32), ("columns", c_int32),
+                ("blocks_k", c_int32), ("block_size", c_int32), ("page", c_int32), ("dump", c_int32), ("q_heads", c_int32),
+                ("value_dim", c_int32), ("out_dtype", c_int32)]
+
+
 class AttendParams(Structure):
     _fields_ = [("q", c_void_p), ("out", c_void_p), ("lse", c_void_p), ("key_pages", c_void_p),
                 ("value_pages", c_void_p), ("key_scales", c_void_p), ("value_scales", c_void_p),
@@ -89,6 +98,7 @@ SYMBOLS = {
     "crit_b200_attend_static": (c_int, [POINTER(AttendParams), c_void_p]),
     "crit_b200_merge_shards": (c_int, [POINTER(MergeShardsParams), c_void_p]),
     "crit_b200_move_rows": (c_int, [POINTER(MoveParams), c_void_p]),
+    "crit_b200_compact_blocks": (c_int, [POINTER(CompactParams), c_void_p]),
     "crit_b200_prefill": (c_int, [POINTER(PrefillParams), c_void_p]),
     "crit_b200_shard_push": (c_int, [POINTER(ExchangeParams), c_void_p]),
     "crit_b200_shard_wait": (c_int, [POINTER(ExchangeParams), c_void_p]),

@@ -169,8 +169,9 @@ class DeviceAttention:
         named = kernels.engine_for(*geometry, len(meta), positions, None if self.window_engine == "auto" else self.window_engine)
         sinks, sliding = getattr(self, "_sinks", None), getattr(self, "_sliding", 0)
         listed = getattr(self, "_blocks", None)
-        if parents is not None or sinks is not None or sliding or listed is not None:
-            named = "mma.sync"             # draft trees, sinks and sliding windows are the m16n8k16 kernel's
+        sparse = listed is not None and listed[1] % pool.page == 0           # the lists as page tables of their own: any kernel
+        if parents is not None or sinks is not None or sliding or (listed is not None and not sparse):
+            named = "mma.sync"             # draft trees, sinks, sliding windows and lists as masks are the m16n8k16 kernel's
         chunk = self.chunk or kernels.chunk_for(pool.head_dim, pool.value_dim, q.shape[1], pool.kv_heads, pool.page, pool.dtype,
                                                 named, meta.columns)
         if self.partitions:

@@ -13,6 +13,7 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_params_size(int3
         case 5: return (int)sizeof(crit_b200_prefill_params);
         case 6: return (int)sizeof(crit_b200_exchange_params);
         case 7: return (int)sizeof(crit_b200_move_params);
+        case 8: return (int)sizeof(crit_b200_compact_params);
         default: return CRIT_B200_EINVAL;
     }
 }

@@ -2,8 +2,8 @@
 // row: the bytes a block asks HBM for are whole page rows, 16 slots x 8 kv heads x 128 bytes = 16 KB in one piece.
 //
 // decode_tc.cuh gives a unit one kv head, so its TMA boxes are 16 rows of 128 bytes that lie 1 KB apart, and eight blocks
-// on eight SMs fetch the eight interleaved parts of a page at different times; streamed that way (loads alone, nothing
-// computed) the pages arrive at 0.83 of the copy bandwidth, as whole 16 KB pieces at 0.92 to 0.96.  Here a tile is 16
+// on eight SMs fetch the eight interleaved parts of a page at different times; streamed that way, even with nothing
+// computed, the pages arrive clearly below the copy bandwidth, as whole 16 KB pieces close to it.  Here a tile is 16
 // positions of all 8 kv heads, loaded by ONE box of a tensor map whose dimensions are permuted, [128 bytes][slots][kv
 // heads]: the box lands head-major, row 16 * head + slot of the operand, although its source is one contiguous piece.
 //

@@ -127,6 +127,86 @@ __global__ void __launch_bounds__(128) move_rows_kernel(const crit_b200_move_par
 
 }  // namespace crit_b200
 
+namespace crit_b200 {
+
+// Thread = (window row, column): the token's listed blocks as a page table of its own (see crit_b200_compact_params).
+__global__ void __launch_bounds__(128) compact_blocks_kernel(const crit_b200_compact_params p) {
+    const int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= p.n_rows * p.columns) return;
+    const int64_t r = item / p.columns;
+    const int c = (int)(item - r * p.columns);
+    int count = p.counts ? p.counts[r] : p.columns;
+    count = count > p.columns ? p.columns : count;
+    const int per = p.block_size / p.page;                       // pages a block holds
+    int32_t* table = p.out_tables + item * ((int64_t)p.blocks_k * per);
+    p.out_counts[item] = 0, p.out_firsts[item] = 0;
+    if (c >= count) return;
+    const int64_t token = p.starts[r] + c, pos = p.firsts[r] + c;
+    const int32_t* from = p.tables + (int64_t)p.rows[r] * p.table_stride;
+    const int32_t* listed = p.blocks + token * p.blocks_k;
+    const int64_t own = pos / p.block_size;
+    int placed = 0;
+    bool has_own = false;
+    for (int j = 0; j < p.blocks_k; ++j) {
+        const int64_t b = listed[j];
+        if (b < 0 || b > own) continue;                          // none, or wholly after the token's position
+        bool twice = false;
+        for (int i = 0; i < j; ++i) twice |= listed[i] == b;
+        if (twice) continue;
+        if (b == own) {                                          // goes last
+            has_own = true;
+            continue;
+        }
+        for (int i = 0; i < per; ++i) {
+            const int64_t at = b * per + i;
+            table[placed * per + i] = at < p.table_width ? from[at] : p.dump;
+        }
+        ++placed;
+    }
+    int64_t length = (int64_t)placed * p.block_size;
+    if (has_own) {
+        for (int i = 0; i < per; ++i) {
+            const int64_t at = own * per + i;
+            table[placed * per + i] = at < p.table_width ? from[at] : p.dump;
+        }
+        ++placed;
+        length += pos - own * p.block_size + 1;
+    }
+    for (int i = placed * per; i < p.blocks_k * per; ++i) table[i] = p.dump;
+    if (length > 0) {
+        p.out_counts[item] = 1, p.out_firsts[item] = length - 1;
+        return;
+    }
+    // the token sees nothing: zeros and -inf, as the fold of no state gives
+    if (p.out) {
+        for (int h = 0; h < p.q_heads; ++h)
+            for (int d = 0; d < p.value_dim; ++d) {
+                const int64_t at = token * p.out_stride_token + (int64_t)h * p.out_stride_head + d;
+                if (p.out_dtype == CRIT_B200_DTYPE_BF16) ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(0.f);
+                else ((__half*)p.out)[at] = __float2half_rn(0.f);
+            }
+    }
+    if (p.lse)
+        for (int h = 0; h < p.q_heads; ++h) p.lse[token * p.q_heads + h] = -INFINITY;
+}
+
+}  // namespace crit_b200
+
+extern "C" __attribute__((visibility("default"))) int crit_b200_compact_blocks(const crit_b200_compact_params* params, void* stream) {
+    if (!params) return CRIT_B200_EINVAL;
+    const crit_b200_compact_params p = *params;
+    if (p.n_rows == 0) return 0;
+    if (!p.tables || !p.rows || !p.starts || !p.firsts || !p.blocks || !p.out_tables || !p.out_counts || !p.out_firsts ||
+        p.n_rows < 0 || p.columns < 1 || p.blocks_k < 1 || p.page < 1 || p.block_size < p.page || p.block_size % p.page ||
+        p.table_width < 1)
+        return CRIT_B200_EINVAL;
+    if (p.out && p.out_dtype != CRIT_B200_DTYPE_BF16 && p.out_dtype != CRIT_B200_DTYPE_FP16) return CRIT_B200_EUNSUPPORTED;
+    const int64_t items = p.n_rows * p.columns;
+    crit_b200::compact_blocks_kernel<<<(unsigned)((items + 127) / 128), 128, 0, (cudaStream_t)stream>>>(p);
+    CRIT_CHECK_LAUNCH();
+    return 0;
+}
+
 extern "C" __attribute__((visibility("default"))) int crit_b200_move_rows(const crit_b200_move_params* params, void* stream) {
     if (!params) return CRIT_B200_EINVAL;
     const crit_b200_move_params p = *params;

@@ -129,6 +129,31 @@ typedef struct crit_b200_move_params {
 
 int crit_b200_move_rows(const crit_b200_move_params* params, void* stream);
 
+/* Block lists turned into page tables of their own (the block-sparse reader's gather, paged_kv_attention/_kernels.py:
+ * 481-555): every token of the launch's window rows (row r, column c: token starts[r] + c at position firsts[r] + c)
+ * becomes a row of ONE column whose table holds the pages of the token's listed KV blocks only (block_size a multiple of
+ * page; ids below 0, above the token's position, or listed twice are left out; the block holding the token's own position
+ * goes last and counts up to that position).  Attending the compact rows (rows = 0 .. n - 1, columns = 1, counts and
+ * firsts as written here) reads the listed blocks and nothing else.  A column past its row's count gets count 0; a token
+ * that sees no position gets count 0 and, when `out` is given, zeros there (and -inf in `lse`). */
+typedef struct crit_b200_compact_params {
+    const int32_t* tables;       /* [table rows][table_stride] page ids */
+    const int32_t* rows;         /* [n_rows] table row of each window row */
+    const int32_t* starts;       /* [n_rows] */
+    const int32_t* counts;       /* [n_rows] or NULL: `columns` each */
+    const int64_t* firsts;       /* [n_rows] */
+    const int32_t* blocks;       /* [tokens][blocks_k] */
+    int32_t* out_tables;         /* [n_rows * columns][blocks_k * block_size / page] */
+    int32_t* out_counts;         /* [n_rows * columns] 1 or 0 */
+    int64_t* out_firsts;         /* [n_rows * columns] the compact row's last position */
+    void* out;                   /* optional: the attention's out, for the tokens that see nothing */
+    float* lse;                  /* optional */
+    int64_t n_rows, table_stride, out_stride_token, out_stride_head;
+    int32_t table_width, columns, blocks_k, block_size, page, dump, q_heads, value_dim, out_dtype;
+} crit_b200_compact_params;
+
+int crit_b200_compact_blocks(const crit_b200_compact_params* params, void* stream);
+
 #define CRIT_B200_ATTEND_NO_TMA 1   /* stage pages with cp.async even where the TMA path serves the geometry */
 #define CRIT_B200_ATTEND_TMA    2   /* stage pages with TMA wherever it serves the geometry (default: 16-bit pages only,
                                        where it measured faster; 8-bit pages measured faster with cp.async) */
@@ -333,7 +358,7 @@ int crit_b200_prefill(const crit_b200_prefill_params* params, void* stream);
 /* -- housekeeping ------------------------------------------------------------------------------------------------ */
 int crit_b200_abi_version(void);
 /* sizeof of each parameter block, in the order append, gather, slots, attend, merge_shards, prefill: a binding checks
- * its own struct layout against it (the reference's crit_cw_params_size, cuda_window.cu:1495-1497); 6 exchange, 7 move. */
+ * its own struct layout against it (the reference's crit_cw_params_size, cuda_window.cu:1495-1497); 6 exchange, 7 move, 8 compact. */
 int crit_b200_params_size(int32_t which);
 const char* crit_b200_error(int32_t code);       /* host string; cudaGetErrorString for codes above 0 */
 int crit_b200_device_sms(void);                  /* SMs of the current device, or a negative error */
