@@ -412,7 +412,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
            partitions=None, parents=None, blocks=None, block_size=None, out=None, lse=None, workspace=None, piece=None,
            fused=False, fresh=None, vsplit=None, tile=None, num_warps=None, num_stages=None, maxnreg=None,
            flash=False, chunk=None, ramp=None, sinks=None, sliding=0, derive=None, launch="both", staging=None,
-           persistent=False, engine=None, shards=None):
+           persistent=False, engine=None, shards=None, context=False):
     """Decode and verify windows over paged KV (reference: paged_kv_attention/__init__.py:396-445, same arguments).
 
     q [tokens][heads][dim] bf16 or fp16 (fp16 for "fp16" pages); key_pages / value_pages one layer's pages
@@ -431,7 +431,10 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     sees.  Where block_size is a multiple of the page (and no tree, sink or sliding window is asked for) the launch
     reads the listed blocks only: every token becomes a one-column row over a page table of its blocks, built on the
     device, on whichever kernel serves it; otherwise the lists are a mask over the m16n8k16 kernel's tiles (every
-    position is read).  fresh and derive are not served.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
+    position is read).  context: every column of a row sees the positions before firsts[r] and none from there on (the
+    part of a prompt chunk's attention that reads the pages when its own keys and values are read fresh; an extension
+    of this module).  fresh (the reference's in-kernel fresh rows) and derive are not served: DeviceAttention reads a
+    pool's fresh rows as context rows + a prefill over the fresh chunk + merge_shards.  launch: "both", or "decode" / "merge" alone (a measurement's).  staging: how pages reach shared memory:
     None (TMA tiled loads for 16-bit pages of 128- or 256-wide heads, cp.async otherwise: what measured faster), "tma"
     (TMA wherever the geometry allows it) or "cp.async" (never TMA); the same bits either way.  persistent: a fixed
     number of blocks walk a work list built on the device from the rows' lengths, instead of one block per (split, kv
@@ -442,6 +445,10 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     split state stays in the workspace, the fold of this rank's splits is stored into every rank's exchange buffer and
     out / lse get the merge over all ranks (three launches: decode, fold + push, wait + merge)."""
     _refuse(fresh=fresh, derive=derive)
+    if context and (parents is not None or blocks is not None or sinks is not None or sliding or shards is not None or
+                    engine not in (None, "mma.sync")):
+        raise NotImplementedError("context rows (every column sees the positions before its row's first only) are the "
+                                  "m16n8k16 kernel's plain rows")
     k_kind = _check_kind(kind, key_scales)
     _cuda(q, "q")
     T, hq, d = q.shape
@@ -509,6 +516,8 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
                 raise ValueError(f"sinks are one logit a query head ({hq}), not {sinks.numel()}")
             sinks = sinks.float().contiguous()
         engine = "mma.sync"
+    if context:
+        engine = "mma.sync"
     chosen = engine is None
     if chosen and (shards is not None or persistent or staging is not None):
         engine = "mma.sync"               # what those arguments are about
@@ -548,7 +557,7 @@ def attend(q, key_pages, value_pages, kind, tables, rows, starts, firsts, column
     if staging not in (None, "tma", "cp.async"):
         raise ValueError("staging is None, tma or cp.async")
     p.flags = ({None: 0, "cp.async": 1, "tma": 2}[staging] | (4 if persistent else 0) |
-               {"tcgen05": 8, "mma.sync": 16, "tcgen05t": 64, "tcgen05p": 128}[engine] | (32 if shards is not None else 0))
+               {"tcgen05": 8, "mma.sync": 16, "tcgen05t": 64, "tcgen05p": 128}[engine] | (32 if shards is not None else 0) | (256 if context else 0))
     p.status = _ptr(_status_word(device))
     p.scale = float(scale if scale is not None else d ** -0.5)
     p.key_multiplier, p.value_multiplier = float(multipliers[0]), float(multipliers[1])

@@ -215,6 +215,11 @@ class DeviceAttention:
                                       f"window of {pool.window} columns is a prompt row")
         special = (getattr(self, "_sinks", None) is not None or getattr(self, "_sliding", 0) or
                    getattr(self, "_blocks", None) is not None)                                  # the decode kernel's rules
+        fresh = None
+        if not special and callable(getattr(pool, "fresh_rows", None)):
+            fresh = pool.fresh_rows(layer, q.shape[0])
+        if fresh is not None and self._fresh_serves(pool, q):
+            return self._fresh_prompts(layer, q, pool, batch, rows, scale, out, found, fresh)
         if self.prompt_reader == "prefill" and self._prefill_serves(pool, q) and not special:
             pages = pool.layer_pages(layer)
             scaled = len(pages) == 4
@@ -233,6 +238,56 @@ class DeviceAttention:
             for at in range(0, count, PIECE_COLUMNS):
                 pieces.append((sequence, first + at, min(PIECE_COLUMNS, count - at), position + at))
         self._windows(layer, q, pool, windows_of(pool, pieces, q.device), scale, out, found)
+
+    def _fresh_serves(self, pool, q):
+        serves = getattr(self.kernels, "prefill_serves", None)
+        kind = "fp16" if q.dtype == getattr(__import__("torch"), "float16") else "bf16"
+        return bool(serves and serves(pool.head_dim, pool.value_dim, q.dtype, kind, 16))
+
+    def _fresh_prompts(self, layer, q, pool, batch, rows, scale, out, found, fresh):
+        """Prompt rows of a pool that kept the step's keys and values as it got them (quantised pages, a fresh buffer): a
+        token attends its own chunk from those and the earlier positions from the pages, so it is scored with what it
+        was given (reference: device_attention.py:1136-1145, pages.py:300-308).  Three launches a row: the pages'
+        part as context rows (pieces of up to 64 columns that all see the positions before the chunk), the chunk's
+        part as a causal prefill over 16-bit pages made of the fresh rows, and the merge of the two by their lse."""
+        import torch
+        kernels = self.kernels
+        kind = "fp16" if q.dtype == torch.float16 else "bf16"
+        pages_ = pool.layer_pages(layer)
+        scaled = len(pages_) == 4
+        multipliers = pool.scale_values[pool.layers[layer]] if pool.dtype == "fp8" else (1.0, 1.0)
+        hkv, d, dv = pool.kv_heads, pool.head_dim, pool.value_dim
+        for r in rows:
+            sequence, first, count, position = batch.row(r)
+            span = slice(first, first + count)
+            heads = q.shape[1]
+            parts_o = q.new_zeros(2, count, heads, dv, dtype=torch.float32)
+            parts_l = q.new_full((2, count, heads), float("-inf"), dtype=torch.float32)
+            # the chunk's own part: the fresh rows as 16-bit pages of 16 positions, read causally from position 0
+            n_pages = -(-count // 16)
+            tk = q.new_zeros(n_pages * 16, hkv, d)
+            tv = q.new_zeros(n_pages * 16, hkv, dv)
+            tk[:count].copy_(fresh[0][span])
+            tv[:count].copy_(fresh[1][span])
+            own = q.new_empty(count, heads, dv)
+            kernels.prefill(q[span], tk.view(n_pages, 16, hkv, d), tv.view(n_pages, 16, hkv, dv), kind,
+                            torch.arange(n_pages, dtype=torch.int32, device=q.device), 0, 16, scale=scale, out=own,
+                            lse=parts_l[1])
+            parts_o[1].copy_(own)
+            # the pages' part: every column of a piece sees the positions before the chunk
+            if position > 0:
+                pieces = [(sequence, at, min(PIECE_COLUMNS, count - at), position) for at in range(0, count, PIECE_COLUMNS)]
+                meta = windows_of(pool, pieces, q.device)
+                before = q.new_empty(count, heads, dv)
+                kernels.attend(q[span], pages_[0], pages_[1], pool.dtype, meta.tables, meta.rows, meta.starts, meta.firsts,
+                               meta.columns, pool.page, counts=meta.counts, key_scales=pages_[2] if scaled else None,
+                               value_scales=pages_[3] if scaled else None, multipliers=multipliers, scale=scale,
+                               out=before, lse=parts_l[0], context=True)
+                parts_o[0].copy_(before)
+            merged, lse = kernels.merge_shards(parts_o, parts_l, dtype=q.dtype)
+            out[span].copy_(merged)
+            if found is not None:
+                found[span].copy_(lse)
 
     def _prefill_serves(self, pool, q):
         serves = getattr(self.kernels, "prefill_serves", None)

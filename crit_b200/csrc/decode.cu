@@ -43,7 +43,7 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     int count = p.counts ? p.counts[r] : p.columns;
     count = count > p.columns ? p.columns : count;
     if (col >= count) return;
-    const int64_t L = p.firsts[r] + count;
+    const int64_t L = p.firsts[r] + ((p.flags & CRIT_B200_ATTEND_CONTEXT) ? 0 : count);
     const int nsplit = states_of(p, L);
     if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS) && !p.sinks)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
     int count = p.counts ? p.counts[r] : p.columns;
     count = count > p.columns ? p.columns : count;
     if (col >= count) return;
-    const int64_t L = p.firsts[r] + count;
+    const int64_t L = p.firsts[r] + ((p.flags & CRIT_B200_ATTEND_CONTEXT) ? 0 : count);
     const int nsplit = states_of(p, L);
     if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS) && !p.sinks)) return;
     const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
@@ -570,7 +570,7 @@ static int launch_decode_ph(const crit_b200_attend_params& p, cudaStream_t s) {
 
 static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     // draft trees (parents), sliding windows, sinks and block lists are the m16n8k16 kernel's only
-    if ((p.parents || p.sinks || p.sliding > 0 || p.blocks) && (p.flags & (CRIT_B200_ATTEND_TCGEN05P | CRIT_B200_ATTEND_TCGEN05T | CRIT_B200_ATTEND_TCGEN05))) return CRIT_B200_EUNSUPPORTED;
+    if ((p.parents || p.sinks || p.sliding > 0 || p.blocks || (p.flags & CRIT_B200_ATTEND_CONTEXT)) && (p.flags & (CRIT_B200_ATTEND_TCGEN05P | CRIT_B200_ATTEND_TCGEN05T | CRIT_B200_ATTEND_TCGEN05))) return CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05P) return ph_serves(p) ? launch_decode_ph(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05T) return tc_serves(p) && p.n_rows <= SW_MAX_LIST ? launch_decode_sw(p, s) : CRIT_B200_EUNSUPPORTED;
     if (p.flags & CRIT_B200_ATTEND_TCGEN05) return tc_serves(p) ? launch_decode_tc(p, s) : CRIT_B200_EUNSUPPORTED;
@@ -579,7 +579,8 @@ static int launch_decode(const crit_b200_attend_params& p, cudaStream_t s) {
     // 32 query rows of accumulators a warp, which makes it issue-bound there), everything else, single-column decode
     // rows above all, to the m16n8k16 kernel.  A column's bits then depend on whether it is read alone or in a window;
     // CRIT_B200_ATTEND_MMA_SYNC keeps every launch on the m16n8k16 kernel, whose bits do not.
-    if (!(p.flags & CRIT_B200_ATTEND_MMA_SYNC) && p.columns > 1 && !p.parents && !p.sinks && p.sliding <= 0 && !p.blocks && tc_serves(p)) return launch_decode_tc(p, s);
+    if (!(p.flags & CRIT_B200_ATTEND_MMA_SYNC) && p.columns > 1 && !p.parents && !p.sinks && p.sliding <= 0 && !p.blocks && !(p.flags & CRIT_B200_ATTEND_CONTEXT) && tc_serves(p))
+        return launch_decode_tc(p, s);
     const int G = p.q_heads / p.kv_heads;
     const int rows = p.columns * G;
     const int nt = row_tiles(rows, p.value_dim);

@@ -154,7 +154,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
                     int cnt = p.counts ? p.counts[rr] : p.columns;
                     cnt = cnt > p.columns ? p.columns : cnt;
                     if (cnt > 0) {
-                        const int64_t len = p.firsts[rr] + cnt;
+                        const int64_t len = p.firsts[rr] + ((p.flags & CRIT_B200_ATTEND_CONTEXT) ? 0 : cnt);
                         mine_units = (int)((len + p.chunk - 1) / p.chunk) * ((cnt * G + ROWS - 1) / ROWS) * p.kv_heads;
                     }
                 }
@@ -191,7 +191,8 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
     count = count > p.columns ? p.columns : count;
     if (count <= 0) continue;
     const int64_t first = p.firsts[r];
-    const int64_t L = first + count;
+    const bool context = (p.flags & CRIT_B200_ATTEND_CONTEXT) != 0;       // the positions before `first` only
+    const int64_t L = context ? first : first + count;
     const int nsplit = (int)((L + p.chunk - 1) / p.chunk);
     if (persistent) {
         const int local = unit - unit_first[r];
@@ -251,7 +252,7 @@ decode_kernel(const crit_b200_attend_params p, const int ctiles, const int smode
         for (int e = 0; e < 2; ++e) {
             const int flat = ct * ROWS + nt * 8 + 2 * t + e;
             const int col = flat / G;
-            lastpos[nt][e] = col < count ? (int)(first + col) : -1;
+            lastpos[nt][e] = col < count ? (int)(context ? first - 1 : first + col) : -1;
         }
     // A draft tree (p.parents): of the window's own positions a query row sees its column and the column's ancestors, bit
     // j of `seen` for column j (the chain of parents, at most `count` hops); the context before the window as ever.

@@ -6,8 +6,10 @@ from . import pool as pages
 
 
 class KVStateCache:
-    def __init__(self, page=16, step_rows=0, step_tokens=0, window=16, round_rows=8, kernels=None, sequences=64):
-        self.page, self.kernels, self.sequences = page, kernels, sequences
+    def __init__(self, page=16, step_rows=0, step_tokens=0, window=16, round_rows=8, kernels=None, sequences=64, fresh=None):
+        """fresh: a fresh buffer (pool.FreshBuffer) the plugin's pools of quantised pages keep a prompt chunk's keys and
+        values in as they got them (reference: inference/attention-state/plugin.py:15-19, :145-151)."""
+        self.page, self.kernels, self.sequences, self.fresh = page, kernels, sequences, fresh
         self.step_rows, self.step_tokens, self.window, self.round_rows = step_rows, step_tokens, window, round_rows
         self.held = {}              # sequence -> host_form.Rows
         self.pools = []
@@ -58,7 +60,7 @@ class KVStateCache:
         made = pages.KVPool(layers, kv_heads, head_dim, tokens, device, dtype, page=page or self.page,
                             value_dim=value_dim, step_rows=rows, step_tokens=self.step_tokens if rows else 0,
                             window=self.window, round_rows=self.round_rows, kernels=self.kernels, spare=spare,
-                            sliding=sliding, span=span, positions=positions, sequences=self.sequences)
+                            sliding=sliding, span=span, positions=positions, sequences=self.sequences, fresh=self.fresh)
         self.pools.append(made)
         return made
 

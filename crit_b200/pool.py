@@ -16,8 +16,7 @@ What is built for the GPU instead of translated:
     CPU keeps page tables and slot maps only, for host-side tests).
   - "fp8:page": E4M3 pages with one FP32 scale per (page, kv head), scales [layers][pages + 1][kv_heads].
 
-Not served (the reference's other pool features): sliding rings, lending and elastic backing, fresh buffers, a draft
-tree's path compaction in commit_round.
+Not served (the reference's other pool features): sliding rings, lending and elastic backing.
 """
 import heapq
 import math
@@ -51,6 +50,15 @@ class _Tables:
         return default
 
 
+class FreshBuffer:
+    """A prompt chunk's keys and values as the projections gave them, one buffer for a plugin's pools: `data` the uint8
+    device buffer, `tag` (pool, layer, tokens, reserve) of the write that holds it now, so a pool reads it only while
+    its own write of that layer and step is the last one.  Reference: pages.py:65-71."""
+
+    def __init__(self, data):
+        self.data, self.tag = data, None
+
+
 class KVPool:
     """window: the most tokens of a row read as a window row; a longer row is a prompt row.  step_rows > 0 keeps a
     step's slots and window-row metadata at fixed device addresses (a model captures its decode step in a CUDA graph
@@ -64,8 +72,8 @@ class KVPool:
             raise ValueError(f"a KV pool stores {', '.join(DTYPES)}, not {dtype!r}")
         if kv_heads < 1 or head_dim < 1 or tokens < 1 or page < 1 or window < 1:
             raise ValueError("a KV pool has heads, a head dimension, tokens, a page size and a window of a token or more")
-        if spare or fresh is not None or sliding or elastic or host_bytes:
-            raise ValueError("crit_b200's KV pool does not serve spare bytes, fresh buffers, sliding rings or elastic pages")
+        if spare or sliding or elastic or host_bytes:
+            raise ValueError("crit_b200's KV pool does not serve spare bytes, sliding rings or elastic pages")
         self.torch = torch
         self.layers = {layer: i for i, layer in enumerate(layers)}
         self.kv_heads, self.head_dim = kv_heads, head_dim
@@ -97,6 +105,22 @@ class KVPool:
         self.scales = torch.ones(n, 2, dtype=torch.float32, device=self.device)
         self.scale_values = [(1.0, 1.0)] * n
         self.steps = 0
+        # A prompt chunk's keys and values as write() got them (pools of quantised pages given a fresh buffer: an object
+        # with .data, a uint8 tensor on the pool's device, and .tag): the attention reads the chunk's own positions from
+        # them and the earlier ones from the pages, so what a prompt token is scored with is what it was given.
+        # Reference: pages.py:180-196.
+        self.fresh_k = self.fresh_v = None
+        self.fresh_tokens, self._staging, self._reserves, self._fresh_buffer = 0, False, 0, None
+        if fresh is not None and dtype in QUANTIZED and self.value_dim and fresh.data.device.type == self.device.type:
+            size = torch.empty(0, dtype=self.compute).element_size()
+            self.fresh_tokens = fresh.data.numel() // (kv_heads * (head_dim + self.value_dim) * size)
+        if self.fresh_tokens:
+            cap = self.fresh_tokens
+            keys = cap * kv_heads * head_dim * size
+            self._fresh_buffer = fresh
+            self.fresh_k = fresh.data[:keys].view(self.compute).view(cap, kv_heads, head_dim)
+            self.fresh_v = fresh.data[keys:keys + cap * kv_heads * self.value_dim * size].view(self.compute).view(
+                cap, kv_heads, self.value_dim)
         # pages: a heap of the free ones (lowest first), a reference count each, and the floor (one past the highest
         # page in use)
         self.free = list(range(self.pages))
@@ -204,7 +228,12 @@ class KVPool:
         self.scale_values[self.layers[layer]] = (float(key_scale), float(value_scale))
 
     def fresh_rows(self, layer, tokens):
-        return None
+        """The keys and values the last write() of `layer` stored for this step's `tokens` tokens, as it got them
+        ([tokens][kv_heads][dim] each, the compute dtype), where the pool keeps them (quantised pages, a fresh buffer, a
+        step with prompt rows), else None.  Reference: pages.py:300-308."""
+        if self.fresh_k is None or self._fresh_buffer.tag != (id(self), layer, tokens, self._reserves):
+            return None
+        return self.fresh_k[:tokens], self.fresh_v[:tokens]
 
     def layer_pages(self, layer):
         """A layer's pages as stored: (keys [pages][page][kv_heads][head_dim], values); scaled kinds add their scales."""
@@ -226,6 +255,11 @@ class KVPool:
     def reserve(self, batch):
         """Each token's slot at its position ([tokens] int64 on the pool's device), pages taken as the sequences grow
         and a page a fork still shares copied before it is written.  Reference: pages.py:320-357."""
+        self._reserves += 1
+        # prompt tokens' keys and values are kept fresh for the step's attention: a PromptBatch's, a StepBatch's with a
+        # row past the window (a prompt row); never a round's (reference: pages.py:325-329)
+        self._staging = bool(getattr(batch, "prompt", False)) or (
+            not getattr(batch, "round", False) and any(batch.row(r)[2] > self.window for r in range(batch.rows)))
         if getattr(batch, "prompt", False):
             if self.prompt_slots is None:
                 raise ValueError("a prompt batch reads the slots stage_prompt(batch) staged: stage it first")
@@ -296,6 +330,11 @@ class KVPool:
         """Store a layer's keys [tokens][kv_heads][head_dim] and values at their slots; a slot below 0 is skipped."""
         self._on_gpu("write")
         i = self.layers[layer]
+        if self.fresh_k is not None and self._staging and keys.shape[0] <= self.fresh_tokens:
+            tokens = keys.shape[0]
+            self.fresh_k[:tokens].copy_(keys)
+            self.fresh_v[:tokens].copy_(values)
+            self._fresh_buffer.tag = (id(self), layer, tokens, self._reserves)
         scaled = self.dtype in SCALED
         self.kernels.write(keys, values if self.value_dim else None, slots, self.k[i],
                            self.v[i] if self.value_dim else None, self.dtype, self.k_scales[i] if scaled else None,

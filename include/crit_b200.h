@@ -175,6 +175,10 @@ int crit_b200_compact_blocks(const crit_b200_compact_params* params, void* strea
                                          8 kv heads, columns x group heads <= 8, chunk a multiple of 16 up to 2,048, a workspace
                                          with max_splits >= 2 x the splits of the longest row: a split has two states there,
                                          and both launches (decode and merge) carry the flag */
+#define CRIT_B200_ATTEND_CONTEXT 256 /* every column of a row sees the positions BEFORE firsts[r] and none from there on (the
+                                        part of a prompt chunk's attention that reads the pages, when the chunk's own keys
+                                        and values are read fresh from elsewhere and the two parts merged by their lse);
+                                        the m16n8k16 kernel's; both launches (decode and merge) carry the flag */
 #define CRIT_B200_ATTEND_PARTIALS 32 /* every row's split states go to the workspace, a row of one split too (the first launch
                                         writes nothing to out / lse): what crit_b200_merge_push sends, or what
                                         crit_b200_merge folds */

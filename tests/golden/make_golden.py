@@ -309,6 +309,31 @@ def tree_windows():
                         out_blocks=out_b.float().numpy(), lse_blocks=lse_b.numpy())
 
 
+def fresh_chunk():
+    """A prompt chunk over fp8:row pages with a fresh buffer: the chunk's own positions are read from the 16-bit rows
+    write() got, the earlier ones from the pages (the reference's torch path, device_attention.py:1136-1145)."""
+    hq, hkv, d, page, n, count = 8, 2, 64, 16, 150, 40
+    g = torch.Generator().manual_seed(44)
+    fresh = pages.FreshBuffer(torch.empty(1 << 18, dtype=torch.uint8))
+    pool = pages.KVPool([0], hkv, d, 24 * page, "cpu", "fp8:row", page=page, fresh=fresh)
+    pool.open("a")
+    k0, v0 = torch.randn(n, hkv, d, generator=g).bfloat16(), torch.randn(n, hkv, d, generator=g).bfloat16()
+    pool.write(0, pool.reserve(StepBatch.build([("a", 0, n)], "cpu")), k0, v0)
+    pool.keep("a", n)
+    batch = StepBatch.build([("a", n, count)], "cpu")
+    k1, v1 = torch.randn(count, hkv, d, generator=g).bfloat16(), torch.randn(count, hkv, d, generator=g).bfloat16()
+    slots = pool.reserve(batch)
+    pool.write(0, slots, k1, v1)
+    assert pool.fresh_rows(0, count) is not None
+    q = torch.randn(count, hq, d, generator=g).bfloat16()
+    eager = device_attention.DeviceAttention(None, "torch", device="cpu")
+    out, lse = eager.forward(0, q, pool, batch, lse=True)
+    np.savez_compressed(OUT / "fresh_fp8row.npz", q=q.float().numpy(), k1=k1.float().numpy(), v1=v1.float().numpy(),
+                        slots=slots.numpy(), table=np.array(pool.table("a"), np.int32), k_codes=u8(pool.k[0]),
+                        v_codes=u8(pool.v[0]), k_scales=pool.k_scales[0].numpy(), v_scales=pool.v_scales[0].numpy(),
+                        out=out.float().numpy(), lse=lse.numpy(), geometry=np.array([hq, hkv, d, page, n, count]))
+
+
 # -- 6. merges ---------------------------------------------------------------------------------------------------------
 def merges():
     g = torch.Generator().manual_seed(31)
@@ -339,8 +364,9 @@ def merges():
 
 if __name__ == "__main__":
     torch.set_num_threads(8)
-    if sys.argv[2:] == ["tree"]:           # that fixture alone: make_golden.py /path/to/reference tree
+    if sys.argv[2:] == ["tree"]:           # those fixtures alone: make_golden.py /path/to/reference tree
         tree_windows()
+        fresh_chunk()
         raise SystemExit(0)
     e4m3_vectors()
     quantize()
@@ -350,5 +376,6 @@ if __name__ == "__main__":
     np.savez_compressed(OUT / "c1_full.npz", **c1_step(32, 8, 128, 16, 512, None, 1, False))
     verify_window()
     tree_windows()
+    fresh_chunk()
     merges()
     print("fixtures written to", OUT)

@@ -285,3 +285,19 @@ def test_block_lists_match_the_references_torch_path(golden):
                                   counts=f["counts"], blocks=f["blocks"], block_size=16)
     assert np.abs(out - f["out_blocks"]).max() <= 8e-3
     assert np.abs(lse - f["lse_blocks"]).max() <= 2e-5
+
+
+def test_a_fresh_prompt_chunk_matches_the_references_torch_path(golden):
+    """A prompt chunk over fp8:row pages whose own positions are read from the 16-bit rows as given (the reference pool's
+    fresh buffer): the oracle over the stored pages with the chunk's slots replaced by those rows."""
+    import oracle
+    f = golden("fresh_fp8row.npz")
+    hq, hkv, d, page, n, count = (int(x) for x in f["geometry"])
+    k = oracle.dequantize(f["k_codes"].reshape(-1, hkv, d), "fp8:row", f["k_scales"].reshape(-1, hkv), page=page)
+    v = oracle.dequantize(f["v_codes"].reshape(-1, hkv, d), "fp8:row", f["v_scales"].reshape(-1, hkv), page=page)
+    plain, _ = oracle.attend(f["q"], k, v, f["table"], [0], [0], [n], count, page)
+    k[f["slots"]], v[f["slots"]] = f["k1"], f["v1"]
+    out, lse = oracle.attend(f["q"], k, v, f["table"], [0], [0], [n], count, page)
+    # (the reference's prompt rows gather their keys into bf16 before the SDPA: its lse carries that rounding)
+    assert np.abs(out - f["out"]).max() <= 8e-3 and np.abs(lse - f["lse"]).max() <= 2e-3
+    assert np.abs(plain - f["out"]).max() > np.abs(out - f["out"]).max()         # the pages alone are further away

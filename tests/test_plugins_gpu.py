@@ -385,3 +385,77 @@ def test_a_round_over_a_draft_tree_reads_ancestors_and_commits_the_accepted_path
     with pytest.raises(NotImplementedError):
         paged = kv.pool([0], 2, 128, 16 * 8, "cuda", "fp8:page", )
         paged._compact(1, view.n_emitted, view.tree_path)
+
+
+# -- fresh rows: a prompt chunk over quantised pages is scored with the keys and values it was given ---------------------
+@pytest.mark.parametrize("dtype", ["fp8:row", "fp8:page", "int8", "fp8"])
+@pytest.mark.parametrize("position,count", [(0, 70), (333, 150), (1000, 40)])
+def test_prompt_rows_read_their_own_chunk_fresh(dtype, position, count):
+    """A pool of quantised pages with a fresh buffer: a prompt row attends its chunk's own positions from the 16-bit rows
+    write() got and the earlier ones from the pages (reference: device_attention.py:1136-1145).  The oracle reads the
+    stored (dequantised) pages with the chunk's slots replaced by the rows as given."""
+    from crit_b200.attention import DeviceAttention, PartitionedAttention
+    from crit_b200.batch import StepBatch
+    from crit_b200.kv_state import KVStateCache
+    from crit_b200.pool import FreshBuffer
+    from helpers import assert_attention_close
+    import crit_b200
+    fresh = FreshBuffer(torch.empty(1 << 20, dtype=torch.uint8, device="cuda"))
+    kv = KVStateCache(page=16, kernels=crit_b200, fresh=fresh)
+    attention = PartitionedAttention(kv, {"world": 2, "page_size": 256}, DeviceAttention(device="cuda"))
+    pool = kv.pool([0], 2, 128, 16 * 100, "cuda", dtype)
+    if dtype == "fp8":
+        pool.set_scales(0, 0.05, 0.04)
+    assert pool.fresh_tokens == (1 << 20) // (2 * 256 * 2)
+    pool.open("a")
+    if position:
+        step(pool, [("a", 0, position)], seed=1)
+        pool.keep("a", position)
+    batch, keys, values = step(pool, [("a", position, count)], seed=7)
+    got = pool.fresh_rows(0, count)
+    assert got is not None and torch.equal(got[0], keys) and torch.equal(got[1], values)
+    q = torch.randn(count, 8, 128, generator=torch.Generator().manual_seed(3)).bfloat16().cuda()
+    out, lse = attention.forward(0, q, pool, batch, lse=True)
+    k, v = stored(pool, 0)
+    slots = pool.reserve(batch).cpu().numpy()            # (the same slots again: the chunk's)
+    k[slots], v[slots] = keys.float().cpu().numpy(), values.float().cpu().numpy()
+    table = np.array(pool.table("a"), np.int32)[None]
+    want, want_lse = oracle.attend(q.float().cpu().numpy(), k, v, table, [0], [0], [position], count, pool.page)
+    assert_attention_close(out, lse, want, want_lse, list(range(count)))
+    # without the buffer the chunk is read from the pages: the two differ by the pages' quantisation
+    plain_kv = KVStateCache(page=16, kernels=crit_b200)
+    assert plain_kv.pool([0], 2, 128, 16 * 8, "cuda", dtype).fresh_rows(0, count) is None
+    # a decode step after it keeps nothing fresh (no prompt row in the step)
+    pool.keep("a", position + count)
+    step(pool, [("a", position + count, 1)], seed=9)
+    assert pool.fresh_rows(0, 1) is None
+
+
+def test_a_fresh_prompt_chunk_matches_the_references_torch_path(golden):
+    """The reference pool's fresh chunk (tests/golden/make_golden.py: fresh_chunk): its stored codes and scales installed
+    in a pool here, the chunk written again through write() with a fresh buffer, forward() against the reference's
+    outputs."""
+    from crit_b200.attention import DeviceAttention
+    from crit_b200.batch import StepBatch
+    from crit_b200.kv_state import KVStateCache
+    from crit_b200.pool import FreshBuffer
+    from helpers import assert_attention_close
+    import crit_b200
+    f = golden("fresh_fp8row.npz")
+    hq, hkv, d, page, n, count = (int(x) for x in f["geometry"])
+    kv = KVStateCache(page=page, kernels=crit_b200, fresh=FreshBuffer(torch.empty(1 << 18, dtype=torch.uint8, device="cuda")))
+    pool = kv.pool([0], hkv, d, 24 * page, "cuda", "fp8:row")
+    pool.open("a")
+    pool.reserve(StepBatch.build([("a", 0, n)], "cuda"))
+    pool.keep("a", n)
+    assert pool.table("a") == f["table"].tolist()[:len(pool.table("a"))]          # the same page order as the reference's pool
+    pool.k[0].view(torch.uint8).copy_(torch.tensor(f["k_codes"]).view(pool.k[0].shape).cuda())
+    pool.v[0].view(torch.uint8).copy_(torch.tensor(f["v_codes"]).view(pool.v[0].shape).cuda())
+    pool.k_scales[0].copy_(torch.tensor(f["k_scales"]).cuda()), pool.v_scales[0].copy_(torch.tensor(f["v_scales"]).cuda())
+    batch = StepBatch.build([("a", n, count)], "cuda")
+    slots = pool.reserve(batch)
+    assert slots.cpu().tolist() == f["slots"].tolist()
+    pool.write(0, slots, torch.tensor(f["k1"]).bfloat16().cuda(), torch.tensor(f["v1"]).bfloat16().cuda())
+    q = torch.tensor(f["q"]).bfloat16().cuda()
+    out, lse = DeviceAttention(device="cuda").forward(0, q, pool, batch, lse=True)
+    assert_attention_close(out, lse, f["out"], f["lse"], list(range(count)))
