@@ -84,7 +84,8 @@ class ExchangeParams(Structure):
                 ("floats", c_int64), ("wait_ns", c_int64), ("world", c_int32), ("rank", c_int32)]
 
 
-STRUCTS = (AppendParams, GatherParams, SlotsParams, AttendParams, MergeShardsParams, PrefillParams, ExchangeParams)
+STRUCTS = (AppendParams, GatherParams, SlotsParams, AttendParams, MergeShardsParams, PrefillParams, ExchangeParams, MoveParams,
+           CompactParams)
 
 # name -> (restype, argtypes): every symbol include/crit_b200.h declares
 SYMBOLS = {
@@ -106,6 +107,16 @@ SYMBOLS = {
     "crit_b200_wait_merge": (c_int, [POINTER(ExchangeParams), POINTER(MergeShardsParams), c_void_p]),
     "crit_b200_exchange_merge": (c_int, [POINTER(AttendParams), POINTER(ExchangeParams), POINTER(MergeShardsParams), c_void_p]),
     "crit_b200_exchange_bytes": (c_int64, [c_int32, c_int64]),
+    "crit_b200_pager_create": (c_void_p, [c_int32]),
+    "crit_b200_pager_destroy": (None, [c_void_p]),
+    "crit_b200_pager_take": (c_int32, [c_void_p]),
+    "crit_b200_pager_drop": (c_int32, [c_void_p, c_int32]),
+    "crit_b200_pager_share": (c_int32, [c_void_p, c_int32]),
+    "crit_b200_pager_refs": (c_int32, [c_void_p, c_int32]),
+    "crit_b200_pager_free": (c_int32, [c_void_p]),
+    "crit_b200_pager_floor": (c_int32, [c_void_p]),
+    "crit_b200_pager_shared": (c_int32, [c_void_p]),
+    "crit_b200_pager_grow": (c_int64, [c_void_p, c_int32, c_void_p, c_void_p, c_void_p, c_int64]),
     "crit_b200_abi_version": (c_int, []),
     "crit_b200_params_size": (c_int, [c_int32]),
     "crit_b200_error": (c_char_p, [c_int32]),

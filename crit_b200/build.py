@@ -9,7 +9,7 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-SOURCES = ["abi.cu", "append.cu", "gather.cu", "decode.cu", "prefill.cu", "exchange.cu"]
+SOURCES = ["abi.cu", "append.cu", "gather.cu", "decode.cu", "prefill.cu", "exchange.cu", "pager.cu"]
 LIBRARY = HERE / "_native" / "libcrit_b200.so"
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
          "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]

@@ -18,6 +18,7 @@ What is built for the GPU instead of translated:
 
 Not served (the reference's other pool features): sliding rings, lending and elastic backing.
 """
+import ctypes
 import heapq
 import math
 
@@ -48,6 +49,57 @@ class _Tables:
 
     def pop(self, sequence, default=None):
         return default
+
+
+class Pager:
+    """The pool's page allocator, native (csrc/pager.cu behind the C ABI's crit_b200_pager_*): a min-heap of the free
+    page ids (the lowest free page is the next one taken), a reference count per page, the floor (one past the highest
+    page in use).  Host code: it needs the library, not a GPU."""
+
+    def __init__(self, pages):
+        from . import _lib
+        self._lib = _lib.load()
+        self._handle = ctypes.c_void_p(self._lib.crit_b200_pager_create(int(pages)))
+        if not self._handle:
+            raise MemoryError(f"no page allocator for {pages} pages")
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.crit_b200_pager_destroy(handle)
+
+    def take(self):
+        return self._lib.crit_b200_pager_take(self._handle)
+
+    def drop(self, page):
+        return self._lib.crit_b200_pager_drop(self._handle, int(page))
+
+    def share(self, page):
+        return self._lib.crit_b200_pager_share(self._handle, int(page))
+
+    def refs(self, page):
+        return self._lib.crit_b200_pager_refs(self._handle, int(page))
+
+    def free(self):
+        return self._lib.crit_b200_pager_free(self._handle)
+
+    def floor(self):
+        return self._lib.crit_b200_pager_floor(self._handle)
+
+    def shared(self):
+        return self._lib.crit_b200_pager_shared(self._handle)
+
+    def grow(self, have, need):
+        """Pages for a step's rows at once (row i from have[i] to need[i] pages, in row order, lowest free page first):
+        (the pages, whether the pool ran out before the last one)."""
+        rows = len(have)
+        most = sum(max(0, n - h) for h, n in zip(have, need))
+        out = (ctypes.c_int32 * max(most, 1))()
+        a, b = (ctypes.c_int32 * max(rows, 1))(*have), (ctypes.c_int32 * max(rows, 1))(*need)
+        taken = self._lib.crit_b200_pager_grow(self._handle, rows, a, b, out, most)
+        if taken < 0:
+            return list(out[:-taken - 1]), True
+        return list(out[:taken]), False
 
 
 class FreshBuffer:
@@ -123,9 +175,7 @@ class KVPool:
                 cap, kv_heads, self.value_dim)
         # pages: a heap of the free ones (lowest first), a reference count each, and the floor (one past the highest
         # page in use)
-        self.free = list(range(self.pages))
-        self.refs = [0] * self.pages
-        self.floor = 0
+        self.pager = Pager(self.pages)
         self._room = None
         self.tables, self.lengths = {}, {}
         self.kernels = kernels
@@ -192,7 +242,7 @@ class KVPool:
         shared = self._table(sequence)[:math.ceil(length / self.page)]
         self.open(new)
         for page in shared:
-            self.refs[page] += 1
+            self.pager.share(page)
         self.tables[new], self.lengths[new] = list(shared), length
         self._note(new, range(len(shared)))
         if sequence in self.slot_of and length % self.page:     # a bound sequence writes its tail without the host
@@ -249,7 +299,12 @@ class KVPool:
         return len(self._table(sequence))
 
     def free_pages(self):
-        return len(self.free)
+        return self.pager.free()
+
+    @property
+    def floor(self):
+        """One past the highest page in use."""
+        return self.pager.floor()
 
     # -- a step ----------------------------------------------------------------------------------------------------------
     def reserve(self, batch):
@@ -268,20 +323,38 @@ class KVPool:
             return self._reserve_round(batch)
         self.steps += 1
         rows = []
-        for r in range(batch.rows):
-            sequence, _, count, position = batch.row(r)
-            table = self._table(sequence)
-            last = position + count - 1
-            grown = len(table)
-            while len(table) < last // self.page + 1:
-                table.append(self._take())
-            changed = list(range(grown, len(table)))
-            for p in range(position // self.page, last // self.page + 1):
-                if self.refs[table[p]] > 1:
-                    table[p] = self._copy(table[p])
-                    changed.append(p)
-            self._note(sequence, changed)
-            rows.append(self.row_of[sequence])
+        if self.pager.shared() == 0 and self._room is None:
+            # no page is shared (nothing to copy before a write) and nobody to ask for room: the step's rows grow in one
+            # call of the allocator, the pages in the order a row-by-row loop would take them
+            found = [batch.row(r) for r in range(batch.rows)]
+            tables = [self._table(sequence) for sequence, _, _, _ in found]
+            have = [len(table) for table in tables]
+            need = [max(len(table), (position + count - 1) // self.page + 1) for table, (_, _, count, position) in zip(tables, found)]
+            pages, short = self.pager.grow(have, need)
+            at = 0
+            for table, (sequence, _, _, _), h, n in zip(tables, found, have, need):
+                got = pages[at:at + n - h]
+                at += len(got)
+                table.extend(got)
+                self._note(sequence, range(h, len(table)))
+                rows.append(self.row_of[sequence])
+            if short:
+                raise MemoryError(f"the KV pool's {self.pages} pages of {self.page} tokens are all in use")
+        else:
+            for r in range(batch.rows):
+                sequence, _, count, position = batch.row(r)
+                table = self._table(sequence)
+                last = position + count - 1
+                grown = len(table)
+                while len(table) < last // self.page + 1:
+                    table.append(self._take())
+                changed = list(range(grown, len(table)))
+                for p in range(position // self.page, last // self.page + 1):
+                    if self.pager.refs(table[p]) > 1:
+                        table[p] = self._copy(table[p])
+                        changed.append(p)
+                self._note(sequence, changed)
+                rows.append(self.row_of[sequence])
         if self.step_rows:
             return self._step_buffers(batch, rows)
         if self.device.type != "cuda":
@@ -406,7 +479,7 @@ class KVPool:
                     table.append(self._take())
                 changed = list(range(grown, len(table)))
                 for p in range(frontier // self.page, last // self.page + 1):
-                    if self.refs[table[p]] > 1:
+                    if self.pager.refs(table[p]) > 1:
                         table[p] = self._copy(table[p])
                         changed.append(p)
                 self._note(sequence, changed)
@@ -445,15 +518,15 @@ class KVPool:
                              f"({self.table_pages * self.page} positions: KVPool positions)")
         logical = math.ceil(capacity / self.page)
         wanted = max(0, logical - len(table))
-        if wanted > len(self.free):
+        if wanted > self.pager.free():
             raise MemoryError(f"binding {sequence!r} up to {capacity} positions takes {wanted} pages; "
-                              f"{len(self.free)} of the KV pool's {self.pages} are free")
+                              f"{self.pager.free()} of the KV pool's {self.pages} are free")
         grown = len(table)
         while len(table) < logical:
             table.append(self._take())
         changed = list(range(grown, len(table)))
         for p in range(length // self.page, max(logical, len(table))):
-            if self.refs[table[p]] > 1:
+            if self.pager.refs(table[p]) > 1:
                 table[p] = self._copy(table[p])
                 changed.append(p)
         self._note(sequence, changed)
@@ -551,21 +624,15 @@ class KVPool:
         return table[q // self.page] * self.page + q % self.page
 
     def _take(self):
-        while not self.free and self._room is not None and self._room():
-            pass
-        if not self.free:
+        page = self.pager.take()
+        while page < 0 and self._room is not None and self._room():
+            page = self.pager.take()
+        if page < 0:
             raise MemoryError(f"the KV pool's {self.pages} pages of {self.page} tokens are all in use")
-        page = heapq.heappop(self.free)
-        self.floor = max(self.floor, page + 1)
-        self.refs[page] = 1
         return page
 
     def _drop(self, page):
-        self.refs[page] -= 1
-        if self.refs[page] == 0:
-            heapq.heappush(self.free, page)
-            while self.floor and self.refs[self.floor - 1] == 0:
-                self.floor -= 1
+        self.pager.drop(page)
 
     def _copy(self, page):
         """A page of its own for a writer: every layer's rows (and scales) of `page` copied to a new page."""

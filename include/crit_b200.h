@@ -359,6 +359,24 @@ typedef struct crit_b200_prefill_params {
 
 int crit_b200_prefill(const crit_b200_prefill_params* params, void* stream);
 
+/* -- the pool's page allocator (host code: no stream, no device memory) ------------------------------------------- */
+/* A min-heap of the free page ids (the lowest free page is the next one taken: the order crit's pool keeps,
+ * inference/attention-state/code/pages.py:721-741), a reference count per page (forks share pages until one writes)
+ * and the floor (one past the highest page in use).  Not thread-safe: one pool, one caller at a time. */
+void* crit_b200_pager_create(int32_t pages);                 /* NULL when pages < 1 or out of memory */
+void crit_b200_pager_destroy(void* pager);
+int32_t crit_b200_pager_take(void* pager);                   /* the lowest free page, its count 1; -1 when none is free */
+int32_t crit_b200_pager_drop(void* pager, int32_t page);     /* one holder less: the count left (0: free again), -1 if not held */
+int32_t crit_b200_pager_share(void* pager, int32_t page);    /* one holder more: the count, -1 if not held */
+int32_t crit_b200_pager_refs(void* pager, int32_t page);
+int32_t crit_b200_pager_free(void* pager);                   /* free pages */
+int32_t crit_b200_pager_floor(void* pager);
+int32_t crit_b200_pager_shared(void* pager);                 /* pages held more than once */
+/* A step's rows grown at once: row i holds have[i] pages and needs need[i]; its new pages are taken in row order, lowest
+ * free page first, into out (capacity entries).  Returns how many; -(taken + 1) when the pool ran out (the pages taken
+ * so far stay taken and are in out). */
+int64_t crit_b200_pager_grow(void* pager, int32_t rows, const int32_t* have, const int32_t* need, int32_t* out, int64_t capacity);
+
 /* -- housekeeping ------------------------------------------------------------------------------------------------ */
 int crit_b200_abi_version(void);
 /* sizeof of each parameter block, in the order append, gather, slots, attend, merge_shards, prefill: a binding checks

@@ -19,7 +19,7 @@ def lib():
 def test_every_declared_symbol_is_exported(lib):
     from crit_b200 import _lib
     header = (ROOT / "include" / "crit_b200.h").read_text()
-    declared = set(re.findall(r"^(?:int|int64_t|const char\*)\s+(crit_b200_\w+)\s*\(", header, flags=re.M))
+    declared = set(re.findall(r"^(?:int|int32_t|int64_t|const char\*|void\*|void)\s+(crit_b200_\w+)\s*\(", header, flags=re.M))
     assert len(declared) >= 13
     assert declared == set(_lib.SYMBOLS), declared ^ set(_lib.SYMBOLS)
     raw = ctypes.CDLL(str(_lib.LIBRARY))

@@ -122,3 +122,20 @@ def test_kv_state_host_form_is_transactional():
         kv.rows("a")
     with pytest.raises(ValueError, match="KV capacity exhausted"):
         kv.stage("b", [[0.0, 0.0]] * 4, [[0.0]] * 4)
+
+
+def test_the_native_page_allocator_takes_the_lowest_free_page():
+    """crit_b200_pager_* (csrc/pager.cu): the lowest free page first, reference counts, the floor, a step's rows grown in one
+    call in the order a row-by-row loop would take their pages, and what is left when the pool runs out."""
+    from crit_b200.pool import Pager
+    pager = Pager(8)
+    assert [pager.take() for _ in range(3)] == [0, 1, 2] and (pager.free(), pager.floor(), pager.shared()) == (5, 3, 0)
+    assert pager.share(1) == 2 and pager.shared() == 1 and pager.refs(1) == 2
+    assert pager.drop(1) == 1 and pager.shared() == 0 and pager.free() == 5           # still held once
+    assert pager.drop(1) == 0 and pager.free() == 6 and pager.floor() == 3
+    assert pager.drop(2) == 0 and pager.floor() == 1                                  # the floor falls past both
+    assert pager.drop(5) == -1 and pager.share(5) == -1 and pager.refs(99) == -1
+    pages, short = pager.grow([1, 0, 2], [3, 1, 2])                                   # rows gain 2, 1 and 0 pages
+    assert (pages, short) == ([1, 2, 3], False) and pager.floor() == 4
+    pages, short = pager.grow([0, 0], [3, 3])                                         # 4 free, 6 wanted
+    assert (pages, short) == ([4, 5, 6, 7], True) and pager.free() == 0 and pager.take() == -1
