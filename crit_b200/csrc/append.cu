@@ -3,6 +3,8 @@
 // E4M3 conversion is the hardware's round-to-nearest-even with saturation, and nothing here is compiled with
 // fast-math.  Reference: paged_kv_attention/_kernels.py:112-150 (_write_kernel) and
 // inference/attention-state/code/pages.py:420-453, :872-895.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace crit_b200 {
@@ -13,14 +15,26 @@ template <typename TIN>
 __device__ __forceinline__ void load_row(const TIN* src, int dim, int lane, float (&x)[8]) {
     // dim <= 256: lane holds elements lane*per .. lane*per+per-1, per = dim / 32 (contiguous, vectorisable)
     const int per = dim >> 5;
-    if (sizeof(TIN) == 2 && (per == 4 || per == 8) && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-        // 16-bit rows of 128 or 256 elements: the lane's elements in one 8- or 16-byte load
-        alignas(16) TIN v[8];
-        if (per == 4) *reinterpret_cast<uint2*>(v) = *reinterpret_cast<const uint2*>(src + lane * 4);
-        else *reinterpret_cast<uint4*>(v) = *reinterpret_cast<const uint4*>(src + lane * 8);
+    if constexpr (sizeof(TIN) == 2) {
+        if ((per == 4 || per == 8) && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+            // 16-bit rows of 128 or 256 elements: the lane's elements in one 8- or 16-byte load, unpacked in registers
+            uint32_t w[4] = {0u, 0u, 0u, 0u};
+            if (per == 4) {
+                const uint2 v = *reinterpret_cast<const uint2*>(src + lane * 4);
+                w[0] = v.x, w[1] = v.y;
+            } else {
+                const uint4 v = *reinterpret_cast<const uint4*>(src + lane * 8);
+                w[0] = v.x, w[1] = v.y, w[2] = v.z, w[3] = v.w;
+            }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) x[i] = i < per ? to_float<TIN>(v[i]) : 0.f;
-        return;
+            for (int i = 0; i < 4; ++i) {
+                float2 f;
+                if constexpr (std::is_same<TIN, __nv_bfloat16>::value) f = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+                else f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+                x[2 * i] = 2 * i < per ? f.x : 0.f, x[2 * i + 1] = 2 * i + 1 < per ? f.y : 0.f;
+            }
+            return;
+        }
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) x[i] = i < per ? to_float<TIN>(src[lane * per + i]) : 0.f;
