@@ -284,13 +284,12 @@ def step(state, launch="both", append=True, buffers=0):
     if append and state["appends"]:
         pk.slots_at(state["tables"], state["token_rows"], state["positions"], w["page"], state["pool"], out=state["slots"])
         pk.write(b["k"], b["v"], state["slots"], state["k"], state["v"], w["kind"], state["ks"], state["vs"])
-    if w["columns"] > 64:        # a prompt chunk per sequence: one prefill launch a sequence
-        cols = w["columns"]
-        for i, s in enumerate(state["live"]):
-            span = slice(i * cols, (i + 1) * cols)
-            pk.prefill(b["q"][span], state["k"], state["v"], w["kind"], state["tables"][s], state["lens"][s] - cols,
-                       w["page"], key_scales=state["ks"], value_scales=state["vs"], out=b["out"][span],
-                       lse=b["lse"][span], engine=state.get("engine"))
+    if w["columns"] > 64:        # a prompt chunk per sequence: one prefill launch over all the sequences' chunks
+        if "prompt_tables" not in state:
+            state["prompt_tables"] = state["tables"][state["rows"].long()].to(torch.int32).contiguous()
+        pk.prefill(b["q"], state["k"], state["v"], w["kind"], state["prompt_tables"], state["firsts"], w["page"],
+                   key_scales=state["ks"], value_scales=state["vs"], out=b["out"], lse=b["lse"],
+                   engine=state.get("engine"))
         return
     pk.attend(b["q"], state["k"], state["v"], w["kind"], state["tables"], state["rows"], state["starts"],
               state["firsts"], w["columns"], w["page"], key_scales=state["ks"], value_scales=state["vs"],
@@ -303,7 +302,7 @@ def launches_per_step(state):
         return 0
     n = 2 if state["appends"] else 0
     if state["w"]["columns"] > 64:
-        return n + len(state["live"])
+        return n + 1
     return n + (3 if state["merger"] is not None and state["merger"].peer is not None else 2)
 
 
@@ -534,7 +533,7 @@ def measure(name, w, args, device, rank, world, local, primary):
              "scaling": "strong" if w["batch"] == 1 else "weak",
              "sharding": "KV range per GPU (fold + peer stores, wait + merge of shards)" if state["sharded"] else "sequences per GPU, no collective",
              "kv": w["kind"], "engine": engine, "graph_replay": graphs[0] is not None,
-             "steps_are": ("slot map + KV append + one prefill launch per sequence" if prompt else
+             "steps_are": ("slot map + KV append + one prefill launch over the sequences' chunks" if prompt else
                            "slot map + KV append + split-K decode + " +
                            ("fold of the splits" if state["merger"] is None else
                             ("fold + push to every rank, wait + merge of shards" if state["merger"].peer is not None
@@ -568,7 +567,7 @@ def measure(name, w, args, device, rank, world, local, primary):
         found["roofline"] = {"bound": "tensor", "kernel": "chunked prefill over paged KV (prefill_tc_kernel: tcgen05 / TMEM)"
                              if args.engine != "mma.sync" else "chunked prefill over paged KV (prefill_kernel: m16n8k16)",
                              "achieved": tf, "peak": tensor_peak, "unit": "TFLOP/s", "frac": tf / tensor_peak,
-                             "peak_source": peak_source, "us_per_launch": decode_s * 1e6 / max(len(state["live"]), 1),
+                             "peak_source": peak_source, "us_per_launch": decode_s * 1e6,
                              "algorithmic_flops_per_step": flops, "traffic": None}
     if append is not None:
         found["append"] = append

@@ -617,10 +617,12 @@ def prefill_serves(head_dim, value_dim, q_dtype, kind, page):
 # -- prompt chunks ------------------------------------------------------------------------------------------------------
 def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scales=None, value_scales=None,
             multipliers=(1.0, 1.0), scale=None, out=None, lse=None, int8_qk=False, fresh=None, flash=False,
-            sinks=None, sliding=0, splits=None, workspace=None, derive=None, engine=None):
+            sinks=None, sliding=0, splits=None, workspace=None, derive=None, engine=None, starts=None):
     """A prompt chunk of one sequence: q [T][heads][dim] at positions position.. (their keys and values written),
     table [pages] int32 (or int64) -> out [T][heads][dim] in q's dtype (and lse [T][heads] FP32 when given), causal.  position: an
-    int, or a one-element int64 device tensor read on the device.  engine: None (tcgen05.mma tiles with TMEM accumulators
+    int, or a one-element int64 device tensor read on the device.  Several sequences' chunks in ONE launch: table
+    [S][pages], position a list of S ints or an int64 device tensor [S], q the sequences' tokens one after another
+    (equal counts, or `starts`: S + 1 ints, sequence s's tokens being rows starts[s]..starts[s+1]).  engine: None (tcgen05.mma tiles with TMEM accumulators
     for 16-bit pages of 128-wide heads, m16n8k16 tiles otherwise), "mma.sync" or "tcgen05" (refused where not served).
     Reference: paged_kv_attention/__init__.py:1245-1332."""
     _refuse(int8_qk=int8_qk, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
@@ -633,15 +635,38 @@ def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scale
     if not key_pages.is_contiguous() or not value_pages.is_contiguous():
         raise ValueError("pages are contiguous [slots][kv_heads][dim] storage")
     out = torch.empty_like(q) if out is None else out
-    if table.dtype not in (torch.int32, torch.int64) or table.dim() != 1:
+    if table.dtype not in (torch.int32, torch.int64) or table.dim() not in (1, 2):
         raise ValueError("table is the sequence's page ids, int32 (read in place) or int64 (converted)")
     if table.dtype != torch.int32 or not table.is_contiguous():
         table = table.to(torch.int32).contiguous()       # (the reference's pool hands its tables over as int64 slices)
     if q.stride(-1) != 1 or out.stride(-1) != 1:
         raise ValueError("q and out have contiguous last dimensions")
+    p = _lib.PrefillParams()
+    if table.dim() == 2:             # several sequences, one launch
+        S = table.shape[0]
+        if not torch.is_tensor(position):
+            if len(position) != S:
+                raise ValueError("one position a sequence")
+            position = torch.tensor([int(x) for x in position], dtype=torch.int64, device=q.device)
+        if position.dtype != torch.int64 or position.numel() != S or not position.is_cuda or not position.is_contiguous():
+            raise ValueError("the sequences' positions are an int64 tensor [S] on the device")
+        if starts is None:
+            if T % S:
+                raise ValueError("sequences of unequal token counts give `starts`")
+            most = T // S
+        else:
+            starts = [int(x) for x in starts]
+            if len(starts) != S + 1 or starts[0] != 0 or starts[-1] != T or any(b < a for a, b in zip(starts, starts[1:])):
+                raise ValueError("starts: S + 1 rising row numbers from 0 to the number of tokens")
+            most = max(b - a for a, b in zip(starts, starts[1:]))
+            starts = torch.tensor(starts, dtype=torch.int32, device=q.device)
+            p.starts = _ptr(starts)
+        p.positions, p.sequences, p.table_stride = _ptr(position), S, table.stride(0)
+        T, position = most, 0
+    elif starts is not None:
+        raise ValueError("starts goes with a table of several sequences")
     if torch.is_tensor(position) and (position.dtype != torch.int64 or position.numel() != 1 or not position.is_cuda):
         raise ValueError("a position read on the device is a one-element int64 tensor there")
-    p = _lib.PrefillParams()
     p.q, p.out, p.lse = _ptr(q), _ptr(out), _ptr(lse)
     p.key_pages, p.value_pages = _ptr(key_pages), _ptr(value_pages)
     p.key_scales, p.value_scales = _ptr(key_scales), _ptr(value_scales)

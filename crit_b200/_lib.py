@@ -76,7 +76,8 @@ class PrefillParams(Structure):
                 ("out_stride_head", c_int64), ("tokens", c_int32), ("q_heads", c_int32), ("kv_heads", c_int32),
                 ("head_dim", c_int32), ("value_dim", c_int32), ("page", c_int32), ("kind", c_int32),
                 ("page_dtype", c_int32), ("q_dtype", c_int32), ("flags", c_int32),
-                ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float)]
+                ("scale", c_float), ("key_multiplier", c_float), ("value_multiplier", c_float),
+                ("starts", c_void_p), ("positions", c_void_p), ("sequences", c_int32), ("table_stride", c_int32)]
 
 
 class ExchangeParams(Structure):

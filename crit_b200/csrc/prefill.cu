@@ -44,8 +44,12 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const crit_b200_pre
     const int h = blockIdx.y;
     const int G = p.q_heads / p.kv_heads;
     const int row0 = blockIdx.x * PF_ROWS;              // first query row (token * G + head in group) of the block
-    const int rows_total = p.tokens * G;
-    const int64_t position = p.position_ptr ? *p.position_ptr : p.position;
+    const int seq = blockIdx.z;                         // one sequence of the launch
+    const int tok0 = p.sequences > 1 ? (p.starts ? p.starts[seq] : seq * p.tokens) : 0;
+    const int rows_total = (p.sequences > 1 && p.starts ? p.starts[seq + 1] - tok0 : p.tokens) * G;
+    if (row0 >= rows_total) return;                     // a shorter sequence of a ragged launch
+    const int32_t* table = p.table + (p.sequences > 1 ? (int64_t)seq * p.table_stride : 0);
+    const int64_t position = p.sequences > 1 ? p.positions[seq] : (p.position_ptr ? *p.position_ptr : p.position);
     const int pos32 = (int)position;
 
     // -- queries into shared memory ----------------------------------------------------------------------------------
@@ -57,7 +61,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const crit_b200_pre
             uint4 v = make_uint4(0, 0, 0, 0);
             if (flat < rows_total) {
                 const int tok = flat / G, gq = flat - tok * G;
-                const char* src = (const char*)p.q + ((int64_t)tok * p.q_stride_token + (int64_t)(h * G + gq) * p.q_stride_head + c * 8) * 2;
+                const char* src = (const char*)p.q + ((int64_t)(tok0 + tok) * p.q_stride_token + (int64_t)(h * G + gq) * p.q_stride_head + c * 8) * 2;
                 v = *reinterpret_cast<const uint4*>(src);
             }
             if constexpr (ES == 2) {
@@ -133,7 +137,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const crit_b200_pre
                 const uint32_t pidx = tile16 / tiles_per_page;
                 const int pos = i * PF_BN + row;
                 const bool ok = pos < end;
-                const int64_t slot = ok ? (int64_t)p.table[pidx] * p.page + ((tile16 - pidx * tiles_per_page) << 4) + (row & 15) : 0;
+                const int64_t slot = ok ? (int64_t)table[pidx] * p.page + ((tile16 - pidx * tiles_per_page) << 4) + (row & 15) : 0;
                 const int kc = ES == 2 ? swz16(c, row) : kswz8<D>(row, c);
                 const int vc = ES == 2 ? swz16(c, row) : vswz8<D>(row, c);
                 cp_async16(ks + row * C::ROWB + kc * 16, kbase + slot * row_stride + c * 16, ok);
@@ -144,7 +148,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const crit_b200_pre
                 const uint32_t tile16 = (uint32_t)(i * pages_per_tile + (row >> 4));
                 const uint32_t pidx = tile16 / tiles_per_page;
                 const bool ok = i * PF_BN + row < end;
-                const int64_t pg = ok ? p.table[pidx] : 0;
+                const int64_t pg = ok ? table[pidx] : 0;
                 const int64_t slot = pg * p.page + ((tile16 - pidx * tiles_per_page) << 4) + (row & 15);
                 const float* src = tid < 64 ? p.key_scales : p.value_scales;
                 cp_async4(sc + tid * 4, src + (smode == 2 ? pg * p.kv_heads + h : slot * p.kv_heads + h), ok);
@@ -319,7 +323,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const crit_b200_pre
         if (flat >= rows_total) continue;
         const int tok = flat / G, gq = flat - tok * G, head = h * G + gq;
         const float inv = l > 0.f ? vmul / l : 0.f;
-        char* dst = (char*)p.out + ((int64_t)tok * p.out_stride_token + (int64_t)head * p.out_stride_head) * 2;
+        char* dst = (char*)p.out + ((int64_t)(tok0 + tok) * p.out_stride_token + (int64_t)head * p.out_stride_head) * 2;
 #pragma unroll
         for (int n = 0; n < D / 8; ++n) {
             const float a = acc[n][2 * hf] * inv, b = acc[n][2 * hf + 1] * inv;
@@ -337,7 +341,7 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const crit_b200_pre
                 }
             }
         }
-        if (p.lse && t == 0) p.lse[(int64_t)tok * p.q_heads + head] = l > 0.f ? m_run[hf] * LN2 + logf(l) : -INFINITY;
+        if (p.lse && t == 0) p.lse[(int64_t)(tok0 + tok) * p.q_heads + head] = l > 0.f ? m_run[hf] * LN2 + logf(l) : -INFINITY;
     }
 }
 
@@ -363,6 +367,8 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_prefill(const cr
     if (!p.q || !p.out || !p.key_pages || !p.value_pages || !p.table || p.tokens < 0 || p.q_heads < 1 || p.kv_heads < 1 ||
         p.q_heads % p.kv_heads)
         return CRIT_B200_EINVAL;
+    if (p.sequences < 0 || (p.sequences > 1 && (!p.positions || p.table_stride < 0 || p.sequences > 65535))) return CRIT_B200_EINVAL;
+    const unsigned nseq = p.sequences > 1 ? (unsigned)p.sequences : 1u;
     if (p.page < 16 || p.page % 16 || p.head_dim != p.value_dim) return CRIT_B200_EUNSUPPORTED;
     if (p.q_dtype != CRIT_B200_DTYPE_BF16 && p.q_dtype != CRIT_B200_DTYPE_FP16) return CRIT_B200_EUNSUPPORTED;
     if (p.kind == CRIT_B200_KIND_16BIT && p.page_dtype != p.q_dtype) return CRIT_B200_EUNSUPPORTED;
@@ -383,7 +389,7 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_prefill(const cr
             auto tc = bf16 ? prefill_tc_kernel<true> : prefill_tc_kernel<false>;
             cudaError_t ce = cudaFuncSetAttribute((const void*)tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
             if (ce != cudaSuccess) return (int)ce;
-            dim3 grid((unsigned)((p.tokens * G + TC_ROWS - 1) / TC_ROWS), (unsigned)p.kv_heads);
+            dim3 grid((unsigned)((p.tokens * G + TC_ROWS - 1) / TC_ROWS), (unsigned)p.kv_heads, nseq);
             tc<<<grid, TC_THREADS, TC_SMEM, (cudaStream_t)stream>>>(p, kmap, vmap, p.status);
             CRIT_CHECK_LAUNCH();
             return 0;
@@ -399,7 +405,7 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_prefill(const cr
     if (e) return e;
     cudaError_t ce = cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (ce != cudaSuccess) return (int)ce;
-    dim3 grid((unsigned)((p.tokens * G + PF_ROWS - 1) / PF_ROWS), (unsigned)p.kv_heads);
+    dim3 grid((unsigned)((p.tokens * G + PF_ROWS - 1) / PF_ROWS), (unsigned)p.kv_heads, nseq);
     fn<<<grid, PF_THREADS, smem, (cudaStream_t)stream>>>(p, smode);
     CRIT_CHECK_LAUNCH();
     return 0;

@@ -75,8 +75,12 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
     const int h = blockIdx.y;
     const int G = p.q_heads / p.kv_heads;
     const int row0 = blockIdx.x * TC_ROWS;
-    const int rows_total = p.tokens * G;
-    const int pos32 = (int)(p.position_ptr ? *p.position_ptr : p.position);
+    const int seq = blockIdx.z;                 // one sequence of the launch
+    const int tok0 = p.sequences > 1 ? (p.starts ? p.starts[seq] : seq * p.tokens) : 0;
+    const int rows_total = (p.sequences > 1 && p.starts ? p.starts[seq + 1] - tok0 : p.tokens) * G;
+    if (row0 >= rows_total) return;             // a shorter sequence of a ragged launch (the whole block leaves, before any allocation)
+    const int32_t* table = p.table + (p.sequences > 1 ? (int64_t)seq * p.table_stride : 0);
+    const int pos32 = (int)(p.sequences > 1 ? p.positions[seq] : (p.position_ptr ? *p.position_ptr : p.position));
 
     if (smem_addr(smem) & 1023u) {              // never seen; the operand layouts would be wrong: say so and leave
         if (tid == 0 && status) atomicExch(status, 0x1ff);
@@ -102,7 +106,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
         uint4 v = make_uint4(0, 0, 0, 0);
         if (flat < rows_total) {
             const int tok = flat / G, gq = flat - tok * G;
-            const char* src = (const char*)p.q + ((int64_t)tok * p.q_stride_token + (int64_t)(h * G + gq) * p.q_stride_head + c * 8) * 2;
+            const char* src = (const char*)p.q + ((int64_t)(tok0 + tok) * p.q_stride_token + (int64_t)(h * G + gq) * p.q_stride_head + c * 8) * 2;
             v = *reinterpret_cast<const uint4*>(src);
         }
         *reinterpret_cast<uint4*>(qs + (c >> 3) * (TC_ROWS * 128) + rr * 128 + (((c & 7) ^ (rr & 7)) << 4)) = v;
@@ -125,7 +129,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
         const int nboxes = (end + 15) >> 4;
         auto fetch = [&](int batch) {
             const int box = batch * 32 + lane;
-            return box < nboxes ? p.table[(uint32_t)box / tiles_per_page] : 0;
+            return box < nboxes ? table[(uint32_t)box / tiles_per_page] : 0;
         };
         int cur = fetch(0), nxt = fetch(1);
         bool ok = true;
@@ -324,7 +328,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
             tc_fence_after();
             const int tok = flat / G, gq = flat - tok * G, head = h * G + gq;
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            char* dst = (char*)p.out + ((int64_t)tok * p.out_stride_token + (int64_t)head * p.out_stride_head) * 2;
+            char* dst = (char*)p.out + ((int64_t)(tok0 + tok) * p.out_stride_token + (int64_t)head * p.out_stride_head) * 2;
 #pragma unroll
             for (int c = 0; c < TC_D / 32; ++c) {
                 float o[32];
@@ -339,7 +343,7 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
                     }
                 }
             }
-            if (has_row && p.lse) p.lse[(int64_t)tok * p.q_heads + head] = l_run > 0.f ? m_run * LN2 + logf(l_run) : -INFINITY;
+            if (has_row && p.lse) p.lse[(int64_t)(tok0 + tok) * p.q_heads + head] = l_run > 0.f ? m_run * LN2 + logf(l_run) : -INFINITY;
         } else {
             where = 0x140;
         }

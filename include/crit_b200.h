@@ -355,6 +355,13 @@ typedef struct crit_b200_prefill_params {
     int32_t kind, page_dtype, q_dtype;
     int32_t flags;               /* CRIT_B200_PREFILL_* */
     float scale, key_multiplier, value_multiplier;
+    /* several sequences' chunks in one launch (sequences > 1): table is [sequences][table_stride], positions holds
+     * each sequence's first new position, tokens is the most tokens a sequence brings, and lse is indexed like out */
+    const int32_t* starts;       /* or NULL. [sequences + 1] on the device: sequence s's tokens are rows
+                                    starts[s] .. starts[s + 1] of q and out (NULL: rows s * tokens .. of each) */
+    const int64_t* positions;    /* [sequences] on the device; required when sequences > 1 */
+    int32_t sequences;           /* 0 or 1: one sequence (table, position and position_ptr as above) */
+    int32_t table_stride;        /* ints between two sequences' tables */
 } crit_b200_prefill_params;
 
 int crit_b200_prefill(const crit_b200_prefill_params* params, void* stream);

@@ -498,6 +498,39 @@ def test_prompt_chunks_on_tcgen05_tiles_match_the_oracle(pk, kind, hq, hkv, posi
     torch.testing.assert_close(out.float(), other.float(), atol=1e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("kind,engine", [("bf16", "tcgen05"), ("bf16", "mma.sync"), ("fp8:row", None), ("fp8:page", None)])
+@pytest.mark.parametrize("counts", [[150, 150, 150], [150, 1, 300, 37]])
+def test_several_sequences_chunks_in_one_launch_give_each_sequences_own_launchs_bits(pk, kind, engine, counts):
+    """One prefill launch over several sequences (a table a sequence, a position a sequence, equal counts or ragged
+    ones through `starts`): every sequence's rows carry the bits of a launch of its own, and match the oracle."""
+    from helpers import Cache, assert_attention_close, queries
+    firsts = [333, 0, 1000, 64][:len(counts)]
+    cache = Cache(kind, 2, 128, 128, 16, [a + n for a, n in zip(firsts, counts)], spare=20)
+    T = sum(counts)
+    q = queries(T, 8, 128, 21)
+    scales = dict(key_scales=cache.ks, value_scales=cache.vs)
+    lse = torch.full((T, 8), 7.0, device="cuda")
+    starts = [0]
+    for n in counts:
+        starts.append(starts[-1] + n)
+    ragged = len(set(counts)) > 1
+    out = pk.prefill(q, cache.k, cache.v, kind, cache.tables.contiguous(), firsts, 16, lse=lse, engine=engine,
+                     starts=starts if ragged else None, **scales)
+    assert pk.status() == 0
+    for s, n in enumerate(counts):
+        span = slice(starts[s], starts[s + 1])
+        own_lse = torch.empty(n, 8, device="cuda")
+        own = pk.prefill(q[span], cache.k, cache.v, kind, cache.tables[s].contiguous(), firsts[s], 16, lse=own_lse,
+                         engine=engine, **scales)
+        assert torch.equal(out[span], own) and torch.equal(lse[span], own_lse), s
+    want, want_lse = cache.oracle(q, list(range(len(counts))), starts[:-1], firsts, max(counts), counts=counts)
+    assert_attention_close(out, lse, want, want_lse, list(range(T)))
+    with pytest.raises(ValueError):
+        pk.prefill(q, cache.k, cache.v, kind, cache.tables.contiguous(), firsts[:-1], 16, **scales)
+    with pytest.raises(ValueError):
+        pk.prefill(q, cache.k, cache.v, kind, cache.tables.contiguous(), firsts, 16, starts=[0] * len(counts) + [T + 1], **scales)
+
+
 def test_tcgen05_tiles_refuse_what_they_do_not_serve(pk):
     from helpers import Cache, queries
     cache = Cache("fp8:row", 2, 128, 128, 16, [100], spare=4)
