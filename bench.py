@@ -755,7 +755,7 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the comparison with the CPU oracle after the timing")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--staging", default=None, choices=["tma", "cp.async"])
-    ap.add_argument("--engine", default=None, choices=["mma.sync", "tcgen05", "tcgen05t", "tcgen05p"], help="the attention kernel instead of the library's choice")
+    ap.add_argument("--engine", default=None, choices=["mma.sync", "tcgen05", "tcgen05t", "tcgen05p", "tcgen05:single", "tcgen05:pair"], help="the attention kernel instead of the library's choice")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
                     help="how the KV-range shards' partials cross the GPUs (c3 on N > 1): stores into peer memory or NCCL's all-gather")
     ap.add_argument("--chunk", type=int, default=None, help="positions per split instead of the library's choice")

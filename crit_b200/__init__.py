@@ -678,7 +678,7 @@ def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scale
     p.q_stride_token, p.q_stride_head = q.stride(0), q.stride(1)
     p.out_stride_token, p.out_stride_head = out.stride(0), out.stride(1)
     p.slots = key_pages.numel() // (hkv * d)
-    p.flags = {None: 0, "mma.sync": 1, "tcgen05": 2}[engine]
+    p.flags = {None: 0, "mma.sync": 1, "tcgen05": 2, "tcgen05:single": 2 | 4, "tcgen05:pair": 2 | 8}[engine]
     p.status = _ptr(_status_word(q.device))
     p.tokens, p.q_heads, p.kv_heads, p.head_dim, p.value_dim, p.page = T, hq, hkv, d, d, int(page)
     p.kind, p.page_dtype, p.q_dtype = k_kind, _page_dtype(kind, key_pages), _DTYPES[q.dtype]

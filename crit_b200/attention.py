@@ -224,6 +224,22 @@ class DeviceAttention:
             pages = pool.layer_pages(layer)
             scaled = len(pages) == 4
             multipliers = pool.scale_values[pool.layers[layer]] if pool.dtype == "fp8" else (1.0, 1.0)
+            spans = [batch.row(r) for r in rows]
+            joined = all(a[1] + a[2] == b[1] for a, b in zip(spans, spans[1:]))
+            if len(spans) > 1 and joined and hasattr(pool, "block_tables") and hasattr(pool, "row_of") and \
+                    hasattr(self.kernels, "engine_for"):          # (crit_b200's own kernels and pool)
+                # the rows' chunks follow one another in q: one launch over all of them, a table row and a position each
+                import torch
+                pool._flush()
+                ids = torch.tensor([pool.row_of[sequence] for sequence, _, _, _ in spans], device=q.device)
+                span = slice(spans[0][1], spans[-1][1] + spans[-1][2])
+                starts = [first - spans[0][1] for _, first, _, _ in spans] + [span.stop - span.start]
+                self.kernels.prefill(q[span], pages[0], pages[1], pool.dtype, pool.block_tables[ids],
+                                     [position for _, _, _, position in spans], pool.page,
+                                     key_scales=pages[2] if scaled else None, value_scales=pages[3] if scaled else None,
+                                     multipliers=multipliers, scale=scale, out=out[span],
+                                     lse=found[span] if found is not None else None, starts=starts)
+                return
             for r in rows:
                 sequence, first, count, position = batch.row(r)
                 span = slice(first, first + count)

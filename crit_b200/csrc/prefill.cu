@@ -9,6 +9,7 @@
 // Reference: paged_kv_attention/_kernels.py:610-726 (_prefill_kernel), __init__.py:1245-1332 (prefill); the reference
 // runs one program per (64 queries, query head), re-reading a kv head's pages once per query head of its group.
 #include "decode_kernel.cuh"
+#include "prefill_pair.cuh"
 #include "prefill_tc.cuh"
 #include "tensor_map.cuh"
 
@@ -386,6 +387,22 @@ extern "C" __attribute__((visibility("default"))) int crit_b200_prefill(const cr
         CUtensorMap kmap, vmap;
         if (page_map(&kmap, p.key_pages, bf16 ? 0 : 1, p.head_dim, p.kv_heads, p.slots) &&
             page_map(&vmap, p.value_pages, bf16 ? 0 : 1, p.value_dim, p.kv_heads, p.slots)) {
+            // blocks of 256 rows (one an SM) once the launch has one for every SM; below that the blocks of 128 fill more SMs
+            const int64_t pairs = (int64_t)((p.tokens * G + TP_ROWS - 1) / TP_ROWS) * p.kv_heads * nseq;
+            int device = 0, sms = 0;
+            if (cudaGetDevice(&device) != cudaSuccess ||
+                cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+                sms = 0;
+            const bool pair = !(p.flags & CRIT_B200_PREFILL_SINGLE) && ((p.flags & CRIT_B200_PREFILL_PAIR) || (sms > 0 && pairs >= sms));
+            if (pair) {
+                auto tp = bf16 ? prefill_pair_kernel<true> : prefill_pair_kernel<false>;
+                cudaError_t ce = cudaFuncSetAttribute((const void*)tp, cudaFuncAttributeMaxDynamicSharedMemorySize, TP_SMEM);
+                if (ce != cudaSuccess) return (int)ce;
+                dim3 grid((unsigned)((p.tokens * G + TP_ROWS - 1) / TP_ROWS), (unsigned)p.kv_heads, nseq);
+                tp<<<grid, TP_THREADS, TP_SMEM, (cudaStream_t)stream>>>(p, kmap, vmap, p.status);
+                CRIT_CHECK_LAUNCH();
+                return 0;
+            }
             auto tc = bf16 ? prefill_tc_kernel<true> : prefill_tc_kernel<false>;
             cudaError_t ce = cudaFuncSetAttribute((const void*)tc, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM);
             if (ce != cudaSuccess) return (int)ce;

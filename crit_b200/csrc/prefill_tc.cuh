@@ -133,6 +133,24 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
         };
         int cur = fetch(0), nxt = fetch(1);
         bool ok = true;
+        // The keys of tile i are asked for before the values of tile i - 1: a key buffer is free after the first
+        // product of the tile two back, long before the value buffer of the tile before is (after ITS second product),
+        // and the first products are what the softmax warps wait for.
+        int v_slot0 = 0, v_boxes = 0;
+        auto values = [&](int t) {          // the values of tile t (its slot and boxes kept from the keys' turn)
+            const int s = t & 1;
+            const uint32_t vs = smem_addr(stages + s * TC_STAGE) + TC_K_BYTES;
+            ok = tc_wait(bar(TC_VEMPTY + s), (uint32_t)((t >> 1) & 1) ^ 1u, abort_flag);
+            ok = __all_sync(FULLMASK, ok);
+            if (!ok) return;
+            if (lane == 0) mbar_expect_tx(bar(TC_VFULL + s), (uint32_t)v_boxes * 2u * 2048u);
+            __syncwarp();
+            if (lane < v_boxes) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half)
+                    tma_load_3d(vs + half * (TC_BN * 128) + lane * 2048, &vmap, half * 64, h, v_slot0, bar(TC_VFULL + s));
+            }
+        };
         for (int i = 0; i < ntiles; ++i) {
             if (i > 0 && (i & 7) == 0) cur = nxt, nxt = fetch((i >> 3) + 1);
             const int s = i & 1;
@@ -141,9 +159,8 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
             const int pg = __shfl_sync(FULLMASK, cur, ((i & 7) << 2) + (lane & 3));
             const uint32_t tile16 = (uint32_t)(i * (TC_BN / 16) + (lane & 3));
             const int slot0 = (int)((int64_t)pg * p.page + ((tile16 % tiles_per_page) << 4));
-            const uint32_t ks = smem_addr(stages + s * TC_STAGE), vs = ks + TC_K_BYTES;
-            const uint32_t free_parity = (uint32_t)((i >> 1) & 1) ^ 1u;
-            ok = tc_wait(bar(TC_KEMPTY + s), free_parity, abort_flag);
+            const uint32_t ks = smem_addr(stages + s * TC_STAGE);
+            ok = tc_wait(bar(TC_KEMPTY + s), (uint32_t)((i >> 1) & 1) ^ 1u, abort_flag);
             ok = __all_sync(FULLMASK, ok);
             if (!ok) break;
             if (lane == 0) mbar_expect_tx(bar(TC_KFULL + s), (uint32_t)boxes * 2u * 2048u);
@@ -153,17 +170,13 @@ __global__ void __launch_bounds__(TC_THREADS, 2) prefill_tc_kernel(const crit_b2
                 for (int half = 0; half < 2; ++half)
                     tma_load_3d(ks + half * (TC_BN * 128) + lane * 2048, &kmap, half * 64, h, slot0, bar(TC_KFULL + s));
             }
-            ok = tc_wait(bar(TC_VEMPTY + s), free_parity, abort_flag);
-            ok = __all_sync(FULLMASK, ok);
-            if (!ok) break;
-            if (lane == 0) mbar_expect_tx(bar(TC_VFULL + s), (uint32_t)boxes * 2u * 2048u);
-            __syncwarp();
-            if (lane < boxes) {
-#pragma unroll
-                for (int half = 0; half < 2; ++half)
-                    tma_load_3d(vs + half * (TC_BN * 128) + lane * 2048, &vmap, half * 64, h, slot0, bar(TC_VFULL + s));
+            if (i > 0) {
+                values(i - 1);
+                if (!ok) break;
             }
+            v_slot0 = slot0, v_boxes = boxes;
         }
+        if (ok && ntiles > 0) values(ntiles - 1);
         if (!ok) where = 0x110;
     } else if (warp == 5) {
         // -- the first products, S = Q K^T of every tile ------------------------------------------------------------------------

@@ -336,6 +336,10 @@ int crit_b200_exchange_merge(const crit_b200_attend_params* attend, const crit_b
 #define CRIT_B200_PREFILL_MMA_SYNC 1   /* the m16n8k16 kernel even where the tcgen05 kernel serves the geometry (0: tcgen05
                                           tiles for 16-bit pages of 128-wide heads, m16n8k16 tiles otherwise) */
 #define CRIT_B200_PREFILL_TCGEN05  2   /* the tcgen05 kernel or CRIT_B200_EUNSUPPORTED */
+#define CRIT_B200_PREFILL_SINGLE   4   /* with tcgen05 tiles: blocks of 128 query rows, two an SM, even for a launch large
+                                          enough for the blocks of 256 rows (two halves over one ring of key and value
+                                          tiles, one block an SM), which are the default from one such block an SM on */
+#define CRIT_B200_PREFILL_PAIR     8   /* with tcgen05 tiles: the blocks of 256 rows however small the launch */
 
 typedef struct crit_b200_prefill_params {
     const void* q;

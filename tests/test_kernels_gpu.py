@@ -498,7 +498,8 @@ def test_prompt_chunks_on_tcgen05_tiles_match_the_oracle(pk, kind, hq, hkv, posi
     torch.testing.assert_close(out.float(), other.float(), atol=1e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("kind,engine", [("bf16", "tcgen05"), ("bf16", "mma.sync"), ("fp8:row", None), ("fp8:page", None)])
+@pytest.mark.parametrize("kind,engine", [("bf16", "tcgen05:single"), ("bf16", "tcgen05:pair"), ("bf16", "mma.sync"),
+                                         ("fp8:row", None), ("fp8:page", None)])
 @pytest.mark.parametrize("counts", [[150, 150, 150], [150, 1, 300, 37]])
 def test_several_sequences_chunks_in_one_launch_give_each_sequences_own_launchs_bits(pk, kind, engine, counts):
     """One prefill launch over several sequences (a table a sequence, a position a sequence, equal counts or ragged
@@ -529,6 +530,29 @@ def test_several_sequences_chunks_in_one_launch_give_each_sequences_own_launchs_
         pk.prefill(q, cache.k, cache.v, kind, cache.tables.contiguous(), firsts[:-1], 16, **scales)
     with pytest.raises(ValueError):
         pk.prefill(q, cache.k, cache.v, kind, cache.tables.contiguous(), firsts, 16, starts=[0] * len(counts) + [T + 1], **scales)
+
+
+@pytest.mark.parametrize("kind", ["bf16", "fp16"])
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (32, 8), (5, 1), (16, 16)])
+@pytest.mark.parametrize("position,tokens", [(0, 70), (333, 150), (1000, 1), (64, 64), (0, 32), (4090, 300), (100, 129)])
+def test_prompt_chunks_on_paired_tcgen05_blocks_match_the_oracle(pk, kind, hq, hkv, position, tokens):
+    """Blocks of 256 query rows (two halves over one ring of key and value tiles): half-filled blocks, a second half
+    without rows, one tile and many, more tiles than the ring holds."""
+    from helpers import Cache, assert_attention_close, queries
+    cache = Cache(kind, hkv, 128, 128, 16, [position + tokens, 40], spare=20)
+    dtype = torch.float16 if kind == "fp16" else torch.bfloat16
+    q = queries(tokens, hq, 128, 13, dtype)
+    lse = torch.empty(tokens, hq, device="cuda")
+    table = cache.tables[0].contiguous()
+    out = pk.prefill(q, cache.k, cache.v, kind, table, position, 16, lse=lse, engine="tcgen05:pair")
+    assert pk.status() == 0
+    want, want_lse = cache.oracle(q, [0], [0], [position], tokens)
+    assert_attention_close(out, lse, want, want_lse, list(range(tokens)))
+    # a row's arithmetic is that of the blocks of 128 rows: the same tiles, the same lazy maximum
+    other_lse = torch.empty_like(lse)
+    other = pk.prefill(q, cache.k, cache.v, kind, table, position, 16, lse=other_lse, engine="tcgen05:single")
+    torch.testing.assert_close(out.float(), other.float(), atol=1e-2, rtol=2e-2)
+    torch.testing.assert_close(lse, other_lse, atol=1e-4, rtol=0)
 
 
 def test_tcgen05_tiles_refuse_what_they_do_not_serve(pk):

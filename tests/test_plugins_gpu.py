@@ -217,6 +217,29 @@ def test_a_prompt_row_past_the_window_is_causal_over_its_own_chunk():
     assert_attention_close(out, lse, want, want_lse, list(range(100)))
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp8:row"])
+def test_a_steps_prompt_rows_take_one_launch_and_match_the_oracle(dtype, monkeypatch):
+    """Three sequences' chunks of different lengths (and a decode row between the steps): the prompt rows, which follow
+    one another in q, go to the prefill kernel in ONE launch, and every row matches the oracle over its own sequence."""
+    import crit_b200
+    from helpers import assert_attention_close
+    kv, attention = parts()
+    pool = kv.pool([0], 2, 128, 16 * 96, "cuda", dtype)
+    for name in "abc":
+        pool.open(name)
+    step(pool, [("a", 0, 150), ("b", 0, 40)], seed=1)
+    pool.keep("a", 150), pool.keep("b", 40)
+    batch, _, _ = step(pool, [("a", 150, 100), ("b", 40, 33), ("c", 0, 70)], seed=2)
+    q = torch.randn(203, 8, 128, generator=torch.Generator().manual_seed(6)).bfloat16().cuda()
+    calls = []
+    real = crit_b200.prefill
+    monkeypatch.setattr(crit_b200, "prefill", lambda *a, **k: (calls.append(a[4].dim()), real(*a, **k))[1])
+    out, lse = attention.forward(0, q, pool, batch, lse=True)
+    assert calls == [2]                                   # one launch, a table of three rows
+    want, want_lse = oracle_rows(pool, batch, q)
+    assert_attention_close(out, lse, want, want_lse, list(range(203)))
+
+
 def test_merged_shards_equal_attention_over_the_whole_sequence():
     """inference/partitioned-attention/tests/test_device.py:44-68, on this pool and attention."""
     from crit_b200.batch import StepBatch
