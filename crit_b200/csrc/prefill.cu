@@ -46,11 +46,11 @@ __global__ void __launch_bounds__(PF_THREADS) prefill_kernel(const crit_b200_pre
     const int G = p.q_heads / p.kv_heads;
     const int row0 = blockIdx.x * PF_ROWS;              // first query row (token * G + head in group) of the block
     const int seq = blockIdx.z;                         // one sequence of the launch
-    const int tok0 = p.sequences > 1 ? (p.starts ? p.starts[seq] : seq * p.tokens) : 0;
-    const int rows_total = (p.sequences > 1 && p.starts ? p.starts[seq + 1] - tok0 : p.tokens) * G;
+    const int tok0 = p.starts ? p.starts[seq] : seq * p.tokens;
+    const int rows_total = (p.starts ? p.starts[seq + 1] - tok0 : p.tokens) * G;
     if (row0 >= rows_total) return;                     // a shorter sequence of a ragged launch
-    const int32_t* table = p.table + (p.sequences > 1 ? (int64_t)seq * p.table_stride : 0);
-    const int64_t position = p.sequences > 1 ? p.positions[seq] : (p.position_ptr ? *p.position_ptr : p.position);
+    const int32_t* table = p.table + (int64_t)seq * p.table_stride;
+    const int64_t position = p.positions ? p.positions[seq] : (p.position_ptr ? *p.position_ptr : p.position);
     const int pos32 = (int)position;
 
     // -- queries into shared memory ----------------------------------------------------------------------------------

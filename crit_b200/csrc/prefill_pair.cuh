@@ -43,11 +43,11 @@ __global__ void __launch_bounds__(TP_THREADS, 1) prefill_pair_kernel(const crit_
     const int G = p.q_heads / p.kv_heads;
     const int row0 = blockIdx.x * TP_ROWS;
     const int seq = blockIdx.z;                 // one sequence of the launch
-    const int tok0 = p.sequences > 1 ? (p.starts ? p.starts[seq] : seq * p.tokens) : 0;
-    const int rows_total = (p.sequences > 1 && p.starts ? p.starts[seq + 1] - tok0 : p.tokens) * G;
+    const int tok0 = p.starts ? p.starts[seq] : seq * p.tokens;
+    const int rows_total = (p.starts ? p.starts[seq + 1] - tok0 : p.tokens) * G;
     if (row0 >= rows_total) return;             // a shorter sequence of a ragged launch (the whole block leaves, before any allocation)
-    const int32_t* table = p.table + (p.sequences > 1 ? (int64_t)seq * p.table_stride : 0);
-    const int pos32 = (int)(p.sequences > 1 ? p.positions[seq] : (p.position_ptr ? *p.position_ptr : p.position));
+    const int32_t* table = p.table + (int64_t)seq * p.table_stride;
+    const int pos32 = (int)(p.positions ? p.positions[seq] : (p.position_ptr ? *p.position_ptr : p.position));
 
     if (smem_addr(smem) & 1023u) {              // never seen; the operand layouts would be wrong: say so and leave
         if (tid == 0 && status) atomicExch(status, 0x1ff);

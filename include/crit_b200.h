@@ -363,8 +363,9 @@ typedef struct crit_b200_prefill_params {
      * each sequence's first new position, tokens is the most tokens a sequence brings, and lse is indexed like out */
     const int32_t* starts;       /* or NULL. [sequences + 1] on the device: sequence s's tokens are rows
                                     starts[s] .. starts[s + 1] of q and out (NULL: rows s * tokens .. of each) */
-    const int64_t* positions;    /* [sequences] on the device; required when sequences > 1 */
-    int32_t sequences;           /* 0 or 1: one sequence (table, position and position_ptr as above) */
+    const int64_t* positions;    /* [sequences] on the device; required when sequences > 1; when not NULL it wins over
+                                    position_ptr and position for one sequence too */
+    int32_t sequences;           /* 0 or 1: one sequence */
     int32_t table_stride;        /* ints between two sequences' tables */
 } crit_b200_prefill_params;
 

@@ -500,7 +500,7 @@ def test_prompt_chunks_on_tcgen05_tiles_match_the_oracle(pk, kind, hq, hkv, posi
 
 @pytest.mark.parametrize("kind,engine", [("bf16", "tcgen05:single"), ("bf16", "tcgen05:pair"), ("bf16", "mma.sync"),
                                          ("fp8:row", None), ("fp8:page", None)])
-@pytest.mark.parametrize("counts", [[150, 150, 150], [150, 1, 300, 37]])
+@pytest.mark.parametrize("counts", [[150, 150, 150], [150, 1, 300, 37], [150]])
 def test_several_sequences_chunks_in_one_launch_give_each_sequences_own_launchs_bits(pk, kind, engine, counts):
     """One prefill launch over several sequences (a table a sequence, a position a sequence, equal counts or ragged
     ones through `starts`): every sequence's rows carry the bits of a launch of its own, and match the oracle."""
