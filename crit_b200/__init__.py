@@ -622,8 +622,10 @@ def prefill(q, key_pages, value_pages, kind, table, position, page, *, key_scale
     table [pages] int32 (or int64) -> out [T][heads][dim] in q's dtype (and lse [T][heads] FP32 when given), causal.  position: an
     int, or a one-element int64 device tensor read on the device.  Several sequences' chunks in ONE launch: table
     [S][pages], position a list of S ints or an int64 device tensor [S], q the sequences' tokens one after another
-    (equal counts, or `starts`: S + 1 ints, sequence s's tokens being rows starts[s]..starts[s+1]).  engine: None (tcgen05.mma tiles with TMEM accumulators
-    for 16-bit pages of 128-wide heads, m16n8k16 tiles otherwise), "mma.sync" or "tcgen05" (refused where not served).
+    (equal counts, or `starts`: S + 1 ints, sequence s's tokens being rows starts[s]..starts[s+1]).  engine: None
+    (tcgen05.mma tiles with TMEM accumulators for 16-bit pages of 128-wide heads, m16n8k16 tiles otherwise), "mma.sync"
+    or "tcgen05" (refused where not served); "tcgen05:single" / "tcgen05:pair" also name the block shape (128 query rows
+    two blocks an SM / 256 rows over one ring of key and value tiles, which "tcgen05" picks by the launch's size).
     Reference: paged_kv_attention/__init__.py:1245-1332."""
     _refuse(int8_qk=int8_qk, fresh=fresh, sinks=sinks, sliding=sliding, derive=derive)
     k_kind = _check_kind(kind, key_scales)
