@@ -33,22 +33,28 @@ __device__ __forceinline__ int states_of(const crit_b200_attend_params& p, int64
     return (p.flags & CRIT_B200_ATTEND_TCGEN05P) ? 2 * n : n;
 }
 
-// The fold of a row's splits in split order (warp w takes splits w, w + 8, ...; the eight warps' states are folded in
-// warp order).  Block = (window token, query head).  m is in base-2 units, o and l are relative to it.
+// The fold of a row's many splits.  Block = (window token, query head).  First every split's maximum (one load a
+// thread, the block's maximum through shared memory), then warp w sums splits w, w + 8, ... with weights that are fixed
+// by then, so its loads do not wait for one another (a hundred splits cost a few round trips, not a dozen dependent
+// ones), and the eight warps' sums are added in warp order.  m is in base-2 units, o and l are relative to it.
 __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200_attend_params p) {
     __shared__ float sm[MERGE_WARPS], sl[MERGE_WARPS];
     __shared__ float so[MERGE_WARPS][256];
     const int head = blockIdx.x;
     const int r = blockIdx.y / p.columns, col = blockIdx.y - r * p.columns;
+    // the row's facts in one round trip (the loads do not wait for one another's branches)
     int count = p.counts ? p.counts[r] : p.columns;
+    const int64_t first = p.firsts[r];
+    const int offset = p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns;
+    const int start = p.starts[r];
     count = count > p.columns ? p.columns : count;
     if (col >= count) return;
-    const int64_t L = p.firsts[r] + ((p.flags & CRIT_B200_ATTEND_CONTEXT) ? 0 : count);
+    const int64_t L = first + ((p.flags & CRIT_B200_ATTEND_CONTEXT) ? 0 : count);
     const int nsplit = states_of(p, L);
     if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS) && !p.sinks)) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int DV = p.value_dim, per = DV >> 5;
-    const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
+    const int prow = offset + col;
     if (nsplit > p.max_splits || prow < 0 || prow >= p.partial_rows) {      // a plan too small for this row: nothing is read
         if (p.status && threadIdx.x == 0) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
         return;
@@ -60,27 +66,40 @@ __global__ void __launch_bounds__(MERGE_WARPS * 32) merge_kernel(const crit_b200
     float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    for (int s = threadIdx.x; s < nsplit; s += MERGE_WARPS * 32) m = fmaxf(m, pm[base + s]);
+    m = warp_max(m);
+    if (lane == 0) sm[warp] = m;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < MERGE_WARPS; ++w) m = fmaxf(m, sm[w]);
+    __syncthreads();                        // (sm is written again below)
+    const float sub0 = m == -INFINITY ? 0.f : m;
+#pragma unroll 4
     for (int s = warp; s < nsplit; s += MERGE_WARPS) {
         const float ms = pm[base + s], ls = pl[base + s];
         if (ms == -INFINITY && ls == 0.f) continue;         // a state that holds nothing (a NaN row's sum is not 0)
         const float* o = p.workspace + (base + s) * DV + lane * per;
-        float v[8];
+        const float take = ex2(ms - sub0);
+        l += ls * take;
+        if (per == 8) {                     // (a lane's values are 16-byte aligned: DV is a multiple of 32 floats)
+            const float4 v = *reinterpret_cast<const float4*>(o), u = *reinterpret_cast<const float4*>(o + 4);
+            acc[0] += v.x * take, acc[1] += v.y * take, acc[2] += v.z * take, acc[3] += v.w * take;
+            acc[4] += u.x * take, acc[5] += u.y * take, acc[6] += u.z * take, acc[7] += u.w * take;
+        } else if (per == 4) {
+            const float4 v = *reinterpret_cast<const float4*>(o);
+            acc[0] += v.x * take, acc[1] += v.y * take, acc[2] += v.z * take, acc[3] += v.w * take;
+        } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = i < per ? o[i] : 0.f;
-        const float top = fmaxf(m, ms);
-        const float sub = top == -INFINITY ? 0.f : top;
-        const float keep = ex2(m - sub), take = ex2(ms - sub);
-        l = l * keep + ls * take;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = acc[i] * keep + v[i] * take;
-        m = top;
+            for (int i = 0; i < 8; ++i)
+                if (i < per) acc[i] += o[i] * take;
+        }
     }
     if (lane == 0) sm[warp] = m, sl[warp] = l;
 #pragma unroll
     for (int i = 0; i < 8; ++i)
         if (i < per) so[warp][lane * per + i] = acc[i];
     __syncthreads();
-    const int token = p.starts[r] + col;
+    const int token = start + col;
     float top = -INFINITY;
 #pragma unroll
     for (int w = 0; w < MERGE_WARPS; ++w) top = fmaxf(top, sm[w]);
@@ -116,13 +135,17 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
     const int head = (int)(item % p.q_heads);
     const int rc = (int)(item / p.q_heads);
     const int r = rc / p.columns, col = rc - r * p.columns;
+    // the row's facts in one round trip (the loads do not wait for one another's branches)
     int count = p.counts ? p.counts[r] : p.columns;
+    const int64_t first = p.firsts[r];
+    const int offset = p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns;
+    const int start = p.starts[r];
     count = count > p.columns ? p.columns : count;
     if (col >= count) return;
-    const int64_t L = p.firsts[r] + ((p.flags & CRIT_B200_ATTEND_CONTEXT) ? 0 : count);
+    const int64_t L = first + ((p.flags & CRIT_B200_ATTEND_CONTEXT) ? 0 : count);
     const int nsplit = states_of(p, L);
     if (nsplit < 1 || (nsplit == 1 && !(p.flags & CRIT_B200_ATTEND_PARTIALS) && !p.sinks)) return;
-    const int prow = (p.offsets ? p.offsets[r] - p.offsets[0] : r * p.columns) + col;
+    const int prow = offset + col;
     if (nsplit > p.max_splits || prow < 0 || prow >= p.partial_rows) {      // a plan too small for this row: nothing is read
         if (p.status && lane == 0) atomicExch(p.status, CRIT_B200_STATUS_PLAN);
         return;
@@ -160,7 +183,7 @@ __global__ void __launch_bounds__(128) merge_warp_kernel(const crit_b200_attend_
     float shrink = 1.f;                     // the head's sink, last: one position more without a value
     if (p.sinks) sink_fold(p.sinks[head], top, total, shrink);
     const float inv = total > 0.f ? shrink / total : 0.f;
-    const int token = p.starts[r] + col;
+    const int token = start + col;
     const int64_t at = (int64_t)token * p.out_stride_token + (int64_t)head * p.out_stride_head + lane * PER;
 #pragma unroll
     for (int i = 0; i < PER; i += 2) {
