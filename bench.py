@@ -564,8 +564,13 @@ def measure(name, w, args, device, rank, world, local, primary):
         flops = pairs * 4 * d * hq
         tf = flops / decode_s / 1e12
         found["tflops"] = flops / seconds / 1e12
-        found["roofline"] = {"bound": "tensor", "kernel": "chunked prefill over paged KV (prefill_tc_kernel: tcgen05 / TMEM)"
-                             if args.engine != "mma.sync" else "chunked prefill over paged KV (prefill_kernel: m16n8k16)",
+        # the library's own choice between its two tcgen05 block shapes: 256-row blocks from one a multiprocessor on
+        pairs = -(-cols * (hq // w["hkv"]) // 256) * w["hkv"] * len(state["live"])
+        paired = args.engine == "tcgen05:pair" or (args.engine in (None, "tcgen05") and
+                                                  pairs >= torch.cuda.get_device_properties(device).multi_processor_count)
+        found["roofline"] = {"bound": "tensor", "kernel": "chunked prefill over paged KV (prefill_kernel: m16n8k16)"
+                             if args.engine == "mma.sync" else "chunked prefill over paged KV (%s: tcgen05 / TMEM)"
+                             % ("prefill_pair_kernel" if paired else "prefill_tc_kernel"),
                              "achieved": tf, "peak": tensor_peak, "unit": "TFLOP/s", "frac": tf / tensor_peak,
                              "peak_source": peak_source, "us_per_launch": decode_s * 1e6,
                              "algorithmic_flops_per_step": flops, "traffic": None}
